@@ -1,0 +1,85 @@
+/* C ABI of libmuse_proj.so: the sm_100a kernels behind the `muse_bf16_proj` hot path
+ * (out = x @ W[:n].T for the qkv_gate / o / pooler / unpooler BF16 weights and the FP32 router).
+ *
+ * Conventions: every pointer named W, x, out, ws, cnt, status is a DEVICE pointer on the current
+ * CUDA device; `stream` is a cudaStream_t passed as void*; tensor maps are 128-byte HOST blobs
+ * (CUtensorMap) filled by muse_tmap_encode_2d. Every entry point returns 0 on success, a negative
+ * value for an argument it rejects (nothing was launched) or a positive cudaError_t / CUresult.
+ * Nothing here allocates device memory or synchronises; launches go to `stream` and can be
+ * captured in a CUDA graph. Thread-compatible: concurrent calls are fine as long as they do not
+ * share a workspace (ws / cnt), which belongs to one stream at a time.
+ *
+ * The reference for this path is a Python submission (best_submissions/muse_bf16_proj.py) whose
+ * native boundary is a pybind function around gemv1_launch (bf16_proj/gemv1.cu:122-125) plus Triton
+ * launchers; each entry point cites what it replaces.
+ */
+#ifndef MUSE_PROJ_H
+#define MUSE_PROJ_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MUSE_PROJ_ABI_VERSION 1
+
+/* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
+#define MUSE_ST_PRODUCER_TIMEOUT 1
+#define MUSE_ST_MMA_TIMEOUT 2
+#define MUSE_ST_EPILOGUE_TIMEOUT 4
+#define MUSE_ST_X_TIMEOUT 8
+#define MUSE_ST_DRAIN_TIMEOUT 16
+
+/* ABI version of the loaded library (MUSE_PROJ_ABI_VERSION at build time). */
+int muse_abi_version(void);
+
+/* Device facts the host-side planner needs. what: 0 = SM count, 1 = opt-in shared memory per
+ * block (bytes), 2 = compute capability major*10+minor, 3 = L2 size (bytes). Negative on error.
+ * Replaces nothing in the reference (its configs are hard-coded for one H200,
+ * best_submissions/muse_bf16_proj.py:56-62, :205-212). */
+int muse_query(int what);
+
+/* y[N] = W[N,K] . x[K], one token. W BF16 (out BF16) or FP32 when w_is_f32 (out FP32); x BF16,
+ * 16-byte aligned; K % 8 == 0; wpr in {1,2,4,8} warps share a row, K % wpr == 0 and each K / wpr
+ * segment a whole number of 16-byte vectors; unroll in {1,2,4,8} 16-byte loads in flight per lane
+ * per batch. Replaces gemv1_launch (bf16_proj/gemv1.cu:122-125; pybind wrapper
+ * best_submissions/muse_bf16_proj.py:193-196). */
+int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int* status,
+               void* stream);
+
+/* Fill a 128-byte tensor map for a row-major BF16 matrix [rows, cols] at `base` (device pointer,
+ * 16-byte aligned) with `row_stride_bytes` between rows (multiple of 16), delivering boxes of
+ * [box_rows, 64 columns] with the 128-byte shared-memory swizzle and zero fill outside the matrix.
+ * Replaces TensorDescriptor.from_tensor (best_submissions/muse_bf16_proj.py:334, :357). */
+int muse_tmap_encode_2d(void* tmap_out128, const void* base, long long rows, long long cols,
+                        long long row_stride_bytes, int box_rows);
+
+/* Floats of workspace and ints of counters muse_skinny_tc needs for (m, n, ntok) when split > 1.
+ * Replaces the capacity rule of _workspace (best_submissions/muse_bf16_proj.py:302-307). */
+long long muse_skinny_ws_floats(int m, int n, int ntok);
+int muse_skinny_tiles(int m, int n, int ntok);
+
+/* Bytes of shared memory one pipeline stage takes (W box [+ lo box] + x box). */
+int muse_skinny_stage_bytes(int ntok, int hilo);
+
+/* out[m, n] = x[m, K] . W[n, K]^T through TMA + tcgen05 (swap-AB, split-K).
+ *   tmap_w      tensor map of W[:n] with box_rows = 128 (muse_tmap_encode_2d)
+ *   tmap_w_lo   NULL for a BF16 weight; for the router the map of the "lo" half, in which case
+ *               tmap_w is the "hi" half and both accumulate into one FP32 accumulator
+ *   x           BF16 [m, K], 16-byte aligned, ld_x elements between rows (ld_x % 8 == 0)
+ *   out         BF16, or FP32 when out_is_f32; ld_out elements between token rows (>= n)
+ *   ws, cnt     zeroed workspace (muse_skinny_ws_floats floats) and counters (muse_skinny_tiles
+ *               ints); left zeroed again when the kernel finishes; may be NULL when split == 1
+ *   ntok        tokens per tile = MMA N: 16, 32, 64, 128 or 256
+ *   split       K slices per tile, 1 .. ceil(K/64); stages: pipeline depth 1 .. 12
+ * Replaces _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337, :236-257), _router /
+ * _router_kernel (:310-320, :260-287), _finish (:215-233) and the cuBLAS call for m > 32 (:390). */
+int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
+                   int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int split, int stages,
+                   int out_is_f32, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUSE_PROJ_H */

@@ -1,0 +1,82 @@
+"""ctypes binding of libmuse_proj.so (declarations: include/muse_proj.h).
+
+The library is the only compute path: if it is missing and cannot be built, loading raises and so
+does every call that needs it. There is no PyTorch or CPU fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from . import build as _build
+
+_LIB = None
+
+# name -> (restype, argtypes); kept in one place so that the symbol-export test can walk it.
+SIGNATURES = {
+    "muse_abi_version": (C.c_int, []),
+    "muse_query": (C.c_int, [C.c_int]),
+    "muse_gemv1": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                             C.c_void_p, C.c_void_p]),
+    "muse_tmap_encode_2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong, C.c_int]),
+    "muse_skinny_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
+    "muse_skinny_tiles": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "muse_skinny_stage_bytes": (C.c_int, [C.c_int, C.c_int]),
+    "muse_skinny_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                 C.c_void_p]),
+}
+
+ABI_VERSION = 1
+
+
+class MuseError(RuntimeError):
+    """A C-ABI call returned non-zero (negative: rejected argument; positive: CUDA error)."""
+
+
+def lib_path() -> Path:
+    return _build.LIB_PATH
+
+
+def load(build_if_missing: bool = True):
+    """Load (building first if needed) and type the library. Raises if that is impossible."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = lib_path()
+    if not path.exists():
+        if not build_if_missing:
+            raise MuseError(f"{path} is missing: run `python -m llm_inference_engine_b200.build`")
+        _build.build()
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = the library does not export the symbol
+        fn.restype = res
+        fn.argtypes = args
+    if lib.muse_abi_version() != ABI_VERSION:
+        raise MuseError(f"{path}: ABI {lib.muse_abi_version()} != expected {ABI_VERSION}; rebuild")
+    _LIB = lib
+    return lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        kind = "rejected argument" if rc < 0 else "CUDA error"
+        raise MuseError(f"{what}: {kind} {rc}")
+
+
+class TensorMap:
+    """A 128-byte CUtensorMap blob in host memory, 64-byte aligned as the driver requires."""
+
+    def __init__(self):
+        self._raw = C.create_string_buffer(128 + 64)
+        base = C.addressof(self._raw)
+        self.ptr = (base + 63) & ~63
+
+    @classmethod
+    def for_matrix(cls, data_ptr: int, rows: int, cols: int, row_stride_bytes: int, box_rows: int) -> "TensorMap":
+        tm = cls()
+        check(load().muse_tmap_encode_2d(tm.ptr, data_ptr, rows, cols, row_stride_bytes, box_rows),
+              f"muse_tmap_encode_2d(rows={rows}, cols={cols}, box_rows={box_rows})")
+        return tm

@@ -1,0 +1,114 @@
+// extern "C" boundary of libmuse_proj.so: argument checks, tensor-map encoding, launches.
+// Declarations and the contract of every entry point are in include/muse_proj.h.
+#include <cudaTypedefs.h>
+#include <string.h>
+
+#include "../../include/muse_proj.h"
+#include "common.cuh"
+
+namespace muse {
+int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
+                   int* status, cudaStream_t stream);
+int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
+                       int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int split, int stages,
+                       int out_f32, cudaStream_t stream);
+int skinny_stage_bytes(int ntok, int hilo);
+
+// cuTensorMapEncodeTiled is a driver entry point; fetching it through the runtime keeps the
+// library free of a link-time dependency on libcuda (it must load on machines without a driver).
+static PFN_cuTensorMapEncodeTiled encode_fn() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+  }
+  return fn;
+}
+
+static int encode_2d(CUtensorMap* tm, const void* base, long long rows, long long cols, long long row_stride_bytes,
+                     int box_rows) {
+  if (!tm || !base || rows <= 0 || cols <= 0 || box_rows <= 0 || box_rows > 256) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) || row_stride_bytes < cols * 2) return -2;
+  PFN_cuTensorMapEncodeTiled fn = encode_fn();
+  if (!fn) return -8;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride_bytes)};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return static_cast<int>(r);
+}
+}  // namespace muse
+
+extern "C" {
+
+int muse_abi_version(void) { return MUSE_PROJ_ABI_VERSION; }
+
+int muse_query(int what) {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  cudaError_t e = cudaSuccess;
+  switch (what) {
+    case 0: e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); break;
+    case 1: e = cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev); break;
+    case 2: {
+      int mj = 0, mn = 0;
+      e = cudaDeviceGetAttribute(&mj, cudaDevAttrComputeCapabilityMajor, dev);
+      if (e == cudaSuccess) e = cudaDeviceGetAttribute(&mn, cudaDevAttrComputeCapabilityMinor, dev);
+      v = mj * 10 + mn;
+      break;
+    }
+    case 3: e = cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev); break;
+    default: return -2;
+  }
+  return e == cudaSuccess ? v : -1;
+}
+
+int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int* status,
+               void* stream) {
+  return muse::gemv1_dispatch(W, x, out, N, K, w_is_f32, wpr, unroll, status, static_cast<cudaStream_t>(stream));
+}
+
+int muse_tmap_encode_2d(void* tmap_out128, const void* base, long long rows, long long cols,
+                        long long row_stride_bytes, int box_rows) {
+  CUtensorMap tm;
+  const int r = muse::encode_2d(&tm, base, rows, cols, row_stride_bytes, box_rows);
+  if (r == 0) memcpy(tmap_out128, &tm, sizeof(tm));
+  return r;
+}
+
+int muse_skinny_tiles(int m, int n, int ntok) {
+  if (m <= 0 || n <= 0 || ntok <= 0) return -1;
+  return ((n + 127) / 128) * ((m + ntok - 1) / ntok);
+}
+
+long long muse_skinny_ws_floats(int m, int n, int ntok) {
+  const int t = muse_skinny_tiles(m, n, ntok);
+  return t < 0 ? -1 : static_cast<long long>(t) * 128 * ntok;
+}
+
+int muse_skinny_stage_bytes(int ntok, int hilo) { return muse::skinny_stage_bytes(ntok, hilo); }
+
+int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
+                   int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int split, int stages,
+                   int out_is_f32, void* stream) {
+  if (!tmap_w || !x) return -1;
+  if (ld_x < k || ld_x % 8 != 0) return -2;
+  // x moves between calls (a fresh activation tensor each time), so its map is encoded per call; the
+  // map travels in the kernel's parameters, which is what makes a captured launch replayable.
+  CUtensorMap tx;
+  const int r = muse::encode_2d(&tx, x, m, k, static_cast<long long>(ld_x) * 2, ntok);
+  if (r != 0) return r;
+  CUtensorMap tw, twlo;
+  memcpy(&tw, tmap_w, sizeof(tw));
+  if (tmap_w_lo) memcpy(&twlo, tmap_w_lo, sizeof(twlo));
+  return muse::skinny_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
+                                  split, stages, out_is_f32, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,159 @@
+// One-token projection y[N] = W[N,K] . x[K] as a streaming GEMV (no tensor cores: at m = 1 the
+// weight bytes are the whole cost). Replaces bf16_proj/gemv1.cu:27-125 of the reference.
+//
+// A CTA is 8 warps. WPR warps share one weight row (each owns a contiguous K segment), so a CTA
+// covers 8 / WPR rows. Each lane streams its segment with 16-byte no-allocate loads, U loads per
+// batch, the next batch in flight in registers while the current one is multiplied. x is brought
+// into shared memory by one bulk (TMA 1-D) copy that overlaps the first weight batch. Lanes reduce
+// by shuffle, the warps of a row through shared memory. One launch, no workspace.
+//
+// W is BF16 (output BF16, round-to-nearest) or FP32 (router: output FP32); x is BF16; the
+// accumulation is FP32. Requires K % 8 == 0 (BF16 W) or K % 4 == 0 (FP32 W), K % WPR == 0 with
+// each segment a whole number of 16-byte vectors, and x 16-byte aligned.
+#include "common.cuh"
+
+namespace muse {
+
+template <int U>
+__device__ __forceinline__ void load_batch(uint4 (&w)[U], const uint4* wp, int v0, int nvec) {
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int v = v0 + u * 32;
+    w[u] = v < nvec ? ldg_stream16(wp + v) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+template <int WPR, int U, bool F32W>
+__global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, const __nv_bfloat16* __restrict__ x,
+                                                    void* __restrict__ out, int N, int K, int* __restrict__ status) {
+  constexpr int RPC = 8 / WPR;        // rows per CTA
+  constexpr int EPV = F32W ? 4 : 8;   // weights per 16-byte vector
+  constexpr int WB = F32W ? 4 : 2;    // bytes per weight
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t xbar;
+  __shared__ float part[8];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * RPC + warp / WPR;
+  const int seg = warp % WPR;
+  const int ks = K / WPR;             // elements in one warp's segment
+  const int nvec = ks / EPV;
+  const bool live = row < N;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&xbar), 1);
+    fence_mbar_init();
+    mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u);
+    bulk_load_1d(smem_u32(smem), x, static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
+  }
+
+  const uint4* wp = reinterpret_cast<const uint4*>(
+      reinterpret_cast<const char*>(W) + (static_cast<size_t>(live ? row : 0) * K + static_cast<size_t>(seg) * ks) * WB);
+  uint4 w[U], wn[U];
+  const int nb = live ? (nvec + 32 * U - 1) / (32 * U) : 0;
+  if (nb > 0) load_batch<U>(w, wp, lane, nvec);
+
+  __syncthreads();  // barrier initialised for everyone
+  if (!mbar_wait(smem_u32(&xbar), 0)) {
+    if (threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
+    return;
+  }
+
+  const uint8_t* xseg = smem + static_cast<size_t>(seg) * ks * 2;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  for (int b = 0; b < nb; ++b) {
+    if (b + 1 < nb) load_batch<U>(wn, wp, (b + 1) * 32 * U + lane, nvec);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = b * 32 * U + u * 32 + lane;
+      if (v < nvec) {
+        if constexpr (F32W) {
+          const uint2 xv = *reinterpret_cast<const uint2*>(xseg + static_cast<size_t>(v) * 8);
+          a0 = fmaf(__uint_as_float(w[u].x), bf16lo_f32(xv.x), a0);
+          a1 = fmaf(__uint_as_float(w[u].y), bf16hi_f32(xv.x), a1);
+          a2 = fmaf(__uint_as_float(w[u].z), bf16lo_f32(xv.y), a2);
+          a3 = fmaf(__uint_as_float(w[u].w), bf16hi_f32(xv.y), a3);
+        } else {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xseg + static_cast<size_t>(v) * 16);
+          a0 = fmaf(bf16lo_f32(w[u].x), bf16lo_f32(xv.x), a0);
+          a1 = fmaf(bf16hi_f32(w[u].x), bf16hi_f32(xv.x), a1);
+          a2 = fmaf(bf16lo_f32(w[u].y), bf16lo_f32(xv.y), a2);
+          a3 = fmaf(bf16hi_f32(w[u].y), bf16hi_f32(xv.y), a3);
+          a0 = fmaf(bf16lo_f32(w[u].z), bf16lo_f32(xv.z), a0);
+          a1 = fmaf(bf16hi_f32(w[u].z), bf16hi_f32(xv.z), a1);
+          a2 = fmaf(bf16lo_f32(w[u].w), bf16lo_f32(xv.w), a2);
+          a3 = fmaf(bf16hi_f32(w[u].w), bf16hi_f32(xv.w), a3);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) w[u] = wn[u];
+  }
+  float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if constexpr (WPR > 1) {
+    if (lane == 0) part[warp] = acc;
+    __syncthreads();
+    if (lane == 0 && seg == 0) {
+#pragma unroll
+      for (int s = 1; s < WPR; ++s) acc += part[warp + s];
+    }
+  }
+  if (live && lane == 0 && seg == 0) {
+    if constexpr (F32W) reinterpret_cast<float*>(out)[row] = acc;
+    else reinterpret_cast<__nv_bfloat16*>(out)[row] = __float2bfloat16_rn(acc);
+  }
+}
+
+template <int WPR, int U, bool F32W>
+static cudaError_t launch(const void* W, const void* x, void* out, int N, int K, int* status, cudaStream_t s) {
+  constexpr int RPC = 8 / WPR;
+  const int smem = K * 2;
+  auto kern = gemv1_kernel<WPR, U, F32W>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+  }
+  kern<<<(N + RPC - 1) / RPC, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status);
+  return cudaGetLastError();
+}
+
+template <int WPR, bool F32W>
+static cudaError_t pick_u(const void* W, const void* x, void* out, int N, int K, int u, int* st, cudaStream_t s) {
+  switch (u) {
+    case 1: return launch<WPR, 1, F32W>(W, x, out, N, K, st, s);
+    case 2: return launch<WPR, 2, F32W>(W, x, out, N, K, st, s);
+    case 4: return launch<WPR, 4, F32W>(W, x, out, N, K, st, s);
+    case 8: return launch<WPR, 8, F32W>(W, x, out, N, K, st, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+template <bool F32W>
+static cudaError_t pick_wpr(const void* W, const void* x, void* out, int N, int K, int wpr, int u, int* st,
+                            cudaStream_t s) {
+  switch (wpr) {
+    case 1: return pick_u<1, F32W>(W, x, out, N, K, u, st, s);
+    case 2: return pick_u<2, F32W>(W, x, out, N, K, u, st, s);
+    case 4: return pick_u<4, F32W>(W, x, out, N, K, u, st, s);
+    case 8: return pick_u<8, F32W>(W, x, out, N, K, u, st, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+// Argument checks live here so that the C-ABI wrapper stays a one-liner. Negative = argument error.
+int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
+                   int* status, cudaStream_t stream) {
+  if (!W || !x || !out || !status || N <= 0 || K <= 0) return -1;
+  const int epv = w_is_f32 ? 4 : 8;
+  if (K % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
+  if (wpr != 1 && wpr != 2 && wpr != 4 && wpr != 8) return -3;
+  if (K % wpr != 0 || (K / wpr) % epv != 0) return -4;
+  if (K * 2 > 200 * 1024) return -5;
+  const cudaError_t e = w_is_f32 ? pick_wpr<true>(W, x, out, N, K, wpr, unroll, status, stream)
+                                 : pick_wpr<false>(W, x, out, N, K, wpr, unroll, status, stream);
+  return static_cast<int>(e);
+}
+
+}  // namespace muse

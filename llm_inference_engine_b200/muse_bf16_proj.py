@@ -1,0 +1,197 @@
+"""Drop-in for the reference's `muse_bf16_proj` submission: `prepare(weights)` once, then
+`kernel_fn(data, state)` per call, same tensors, same meaning (best_submissions/muse_bf16_proj.py:340-390).
+
+    out = x @ W[:n].T      BF16 for qkv_gate / o / pooler / unpooler, FP32 for the router
+
+`weights` maps layer name -> [N, K] tensor on a CUDA device (BF16; FP32 for "router"); `data` is
+`{"x": BF16 [m, K], "config": {"m", "n", "k", "layer"}}`; the result is a new [m, n] tensor. `n` may be
+smaller than W's row count (the unpooler's per-GPU slice at up to 8 tokens, bf16_proj/reference.py:37-41).
+
+Dispatch (shape-only, so a call is CUDA-graph capturable and replays identically):
+  m == 1   streaming GEMV (csrc/gemv1.cu); the router reads its FP32 weights as they are
+  m >= 2   swap-AB split-K TMA + tcgen05 kernel (csrc/skinny_tc.cu); the router runs its BF16
+           hi + lo pair (split once here, as the reference does at :346-349) into one FP32 accumulator
+Every path is hand-written sm_100a CUDA reached through the C ABI (include/muse_proj.h); there is no
+cuBLAS, Triton, PyTorch-matmul or CPU fallback: a non-CUDA tensor or a missing library raises.
+"""
+
+from __future__ import annotations
+
+from typing import TypedDict
+
+import torch
+
+from . import _capi
+from .plan import DeviceFacts, GemvPlan, SkinnyPlan, gemv_plan, gemv_valid, skinny_plan
+
+FP32_LAYERS = {"router"}
+# Workspace rule: sized once in prepare() so that every layer at up to this many tokens can split K;
+# beyond it a shape runs with a single K slice rather than allocating during a call.
+WS_MAX_TOKENS = 256
+CNT_INTS = 4096
+WARMUP_TOKENS = (1, 2, 16, 32, 64, 128, 256)
+
+
+class Config(TypedDict):
+    m: int
+    n: int
+    k: int
+    layer: str
+
+
+class Inputs(TypedDict):
+    x: torch.Tensor
+    config: Config
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} is on {t.device}: this path runs on a CUDA device only (no CPU fallback)")
+
+
+def split_hi_lo(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """FP32 -> BF16 hi + BF16 lo with hi = bf16(w), lo = bf16(w - fp32(hi)); hi + lo carries ~16
+    mantissa bits of w (best_submissions/muse_bf16_proj.py:346-349; bf16_proj/baseline.py:49-50)."""
+    hi = w.to(torch.bfloat16)
+    lo = (w - hi.float()).to(torch.bfloat16)
+    return hi.contiguous(), lo.contiguous()
+
+
+def _stream_workspace(state, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """The split-K workspace of the current stream. A workspace is mid-reduction while a call runs,
+    so calls that may overlap on the GPU (different streams) must not share one; the reference's
+    decode layer keeps a second one for its side-stream router for this reason
+    (best_submissions/muse_decode_layer.py:226-233)."""
+    key = torch.cuda.current_stream(device).cuda_stream
+    pool = state["_ws_by_stream"]
+    if key not in pool:
+        pool[key] = (torch.zeros(state["_ws_floats"], device=device, dtype=torch.float32),
+                     torch.zeros(CNT_INTS, device=device, dtype=torch.int32))
+    return pool[key]
+
+
+def prepare(weights: dict[str, torch.Tensor], warmup: bool = True):
+    """Weights as given (kept alive, never modified), the router's BF16 hi + lo halves, a zeroed
+    split-K workspace with its tile counters, a device status word, and every kernel variant
+    launched once so that no call configures anything later (mirrors
+    best_submissions/muse_bf16_proj.py:340-366)."""
+    lib = _capi.load()
+    state: dict = {}
+    device = None
+    for name, w in weights.items():
+        _require_cuda(w, f"weights[{name!r}]")
+        if w.dim() != 2:
+            raise ValueError(f"weights[{name!r}] must be [N, K], got {tuple(w.shape)}")
+        want = torch.float32 if name in FP32_LAYERS else torch.bfloat16
+        if w.dtype != want:
+            raise TypeError(f"weights[{name!r}] must be {want}, got {w.dtype}")
+        state[name] = w.contiguous()
+        device = w.device
+    if device is None:
+        raise ValueError("prepare() needs at least one weight")
+    with torch.cuda.device(device):
+        cc = lib.muse_query(2)
+        if cc < 100:
+            raise RuntimeError(f"compute capability {cc / 10:.1f}: these kernels are sm_100a only")
+        state["_dev"] = DeviceFacts(sms=lib.muse_query(0), smem_optin=lib.muse_query(1))
+        for name in FP32_LAYERS & set(weights):
+            hi, lo = split_hi_lo(state[name])
+            state[f"_{name}_hi"], state[f"_{name}_lo"] = hi, lo
+        n_max = max(-(-w.shape[0] // 128) * 128 for w in weights.values())
+        state["_ws_floats"] = n_max * WS_MAX_TOKENS
+        state["_ws_by_stream"] = {}
+        state["_status"] = torch.zeros(1, device=device, dtype=torch.int32)
+        state["_tmaps"] = {}
+        state["_plans"] = {}
+        state["_override"] = {}
+        _stream_workspace(state, device)
+        if warmup:
+            for layer, w in weights.items():
+                n, k = w.shape
+                for m in WARMUP_TOKENS:
+                    x = torch.zeros((m, k), device=device, dtype=torch.bfloat16)
+                    kernel_fn({"x": x, "config": {"m": m, "n": n, "k": k, "layer": layer}}, state)
+            check_status(state)
+    return state
+
+
+def check_status(state) -> None:
+    """Synchronise and raise if any kernel since the last check gave up on one of its bounded waits.
+    Not for use inside a stream capture."""
+    word = int(state["_status"].item())
+    if word:
+        state["_status"].zero_()
+        raise _capi.MuseError(f"a kernel reported a timed-out wait: status bits {word:#x} (see MUSE_ST_* in muse_proj.h)")
+
+
+def _weight_maps(state, layer: str, n: int):
+    """TMA maps of W[:n] (hi and lo for FP32 layers), encoded once per (layer, n)."""
+    key = (layer, n)
+    maps = state["_tmaps"].get(key)
+    if maps is None:
+        if layer in FP32_LAYERS:
+            srcs = (state[f"_{layer}_hi"], state[f"_{layer}_lo"])
+        else:
+            srcs = (state[layer],)
+        maps = tuple(_capi.TensorMap.for_matrix(t.data_ptr(), n, t.shape[1], t.stride(0) * 2, 128) for t in srcs)
+        state["_tmaps"][key] = maps
+    return maps
+
+
+def plan_for(state, layer: str, m: int, n: int, k: int) -> GemvPlan | SkinnyPlan:
+    """The (cached) launch plan of a shape; `state["_override"][(layer, m)]` = dict(split=, stages=) or
+    dict(wpr=, unroll=) forces values for tuning sweeps."""
+    key = (layer, m, n, k)
+    ov = state["_override"].get((layer, m))
+    if ov is None and key in state["_plans"]:
+        return state["_plans"][key]
+    f32 = layer in FP32_LAYERS
+    dev = state["_dev"]
+    if m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):
+        plan = GemvPlan(**ov) if ov else gemv_plan(n, k, f32, dev)
+    else:
+        plan = skinny_plan(m, n, k, f32, dev, ws_floats_cap=state["_ws_floats"], cnt_cap=CNT_INTS, **(ov or {}))
+    if ov is None:
+        state["_plans"][key] = plan
+    return plan
+
+
+def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x @ W[:n].T as a new tensor: BF16, or FP32 for the router. `out` (optional, beyond the
+    reference's signature) is a preallocated [m, >= n] destination whose row stride is honoured."""
+    x, cfg = data["x"], data["config"]
+    layer, n = cfg["layer"], int(cfg["n"])
+    if layer not in state or layer.startswith("_"):
+        raise KeyError(f"unknown layer {layer!r}")
+    _require_cuda(x, "x")
+    w = state[layer]
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise TypeError(f"x must be BF16 [m, K], got {x.dtype} {tuple(x.shape)}")
+    m, k = x.shape
+    if k != w.shape[1] or not 0 < n <= w.shape[0] or m < 1:
+        raise ValueError(f"{layer}: x {tuple(x.shape)} / n={n} do not fit W {tuple(w.shape)}")
+    if x.stride(1) != 1 or x.data_ptr() % 16 or (m > 1 and (x.stride(0) % 8 or x.stride(0) < k)):
+        x = x.contiguous().clone()  # same rule as the reference (:373-374)
+    f32 = layer in FP32_LAYERS
+    if out is None:
+        out = torch.empty((m, n), device=x.device, dtype=torch.float32 if f32 else torch.bfloat16)
+    elif out.shape[0] != m or out.shape[1] < n or out.stride(1) != 1 or out.dtype != (torch.float32 if f32 else torch.bfloat16):
+        raise ValueError("out must be [m, >= n], unit column stride, BF16 (FP32 for the router)")
+    lib = state.get("_lib") or _capi.load()
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    plan = plan_for(state, layer, m, n, k)
+    status = state["_status"].data_ptr()
+    if isinstance(plan, GemvPlan):
+        _capi.check(lib.muse_gemv1(w.data_ptr(), x.data_ptr(), out.data_ptr(), n, k, int(f32), plan.wpr, plan.unroll,
+                                   status, stream), f"muse_gemv1({layer}, n={n}, k={k})")
+        return out
+    maps = _weight_maps(state, layer, n)
+    ws_ptr = cnt_ptr = None
+    if plan.split > 1:
+        ws, cnt = _stream_workspace(state, x.device)
+        ws_ptr, cnt_ptr = ws.data_ptr(), cnt.data_ptr()
+    _capi.check(lib.muse_skinny_tc(maps[0].ptr, maps[1].ptr if f32 else None, x.data_ptr(), out.data_ptr(), ws_ptr,
+                                   cnt_ptr, status, m, n, k, x.stride(0) if m > 1 else k, out.stride(0), plan.ntok,
+                                   plan.split, plan.stages, int(f32), stream),
+                f"muse_skinny_tc({layer}, m={m}, n={n}, k={k}, {plan})")
+    return out
