@@ -79,6 +79,11 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
                    int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int split, int stages,
                    int out_is_f32, void* stream);
 
+/* Launches an empty kernel on `stream`: the calibration point for the fixed cost of replaying a
+ * one-kernel CUDA graph, which the benchmark reports beside every per-call time. Replaces the `nop`
+ * graph of the reference's timing harness (bf16_proj/tune.py:79-98). */
+int muse_nop(void* stream);
+
 #ifdef __cplusplus
 }
 #endif

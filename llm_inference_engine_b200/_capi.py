@@ -26,6 +26,7 @@ SIGNATURES = {
     "muse_skinny_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                  C.c_void_p]),
+    "muse_nop": (C.c_int, [C.c_void_p]),
 }
 
 ABI_VERSION = 1

@@ -43,9 +43,15 @@ static int encode_2d(CUtensorMap* tm, const void* base, long long rows, long lon
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return static_cast<int>(r);
 }
+__global__ void nop_kernel() {}
 }  // namespace muse
 
 extern "C" {
+
+int muse_nop(void* stream) {
+  muse::nop_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>();
+  return static_cast<int>(cudaGetLastError());
+}
 
 int muse_abi_version(void) { return MUSE_PROJ_ABI_VERSION; }
 

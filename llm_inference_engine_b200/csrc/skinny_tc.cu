@@ -233,17 +233,22 @@ static cudaError_t launch(const CUtensorMap* tw, const CUtensorMap* twlo, const 
                           int ld_out, cudaStream_t stream) {
   using Cfg = SkinnyCfg<NTOK, HILO>;
   auto kern = skinny_tc_kernel<NTOK, HILO>;
-  static int smem_set[64] = {0};  // per device: the opt-in shared-memory ceiling has been raised
+  static int dyn_max[64] = {0};  // per device: opt-in ceiling for dynamic shared memory, once raised
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (dev < 64 && !smem_set[dev]) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    smem_set[dev] = 1;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!dyn_max[dev]) {
+    cudaFuncAttributes fa;
+    int optin = 0;
+    if ((e = cudaFuncGetAttributes(&fa, kern)) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
+    const int room = optin - static_cast<int>(fa.sharedSizeBytes);  // static shared memory counts against the limit
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, room)) != cudaSuccess) return e;
+    dyn_max[dev] = room;
   }
   const size_t smem = static_cast<size_t>(stages) * Cfg::STAGE_BYTES + 1024;
-  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  if (smem > static_cast<size_t>(dyn_max[dev])) return cudaErrorInvalidValue;
   const dim3 grid((n + TILE_ROWS - 1) / TILE_ROWS, split, (m + NTOK - 1) / NTOK);
   kern<<<grid, 128, smem, stream>>>(*tw, HILO ? *twlo : *tw, *tx, out, ws, cnt, status, m, n, chunks, split, stages,
                                     out_f32, ld_out);

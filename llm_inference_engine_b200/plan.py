@@ -17,7 +17,7 @@ MAX_STAGES = 12
 NTOK_CHOICES = (16, 32, 64, 128, 256)
 SMEM_PER_SM = 228 * 1024     # B200: shared memory per SM
 SMEM_PER_CTA_MAX = 227 * 1024
-CTA_RESERVED = 1024 + 1024   # per-CTA driver reservation + our 1 KB alignment slack
+CTA_RESERVED = 1024 + 1024 + 512   # per-CTA driver reservation + 1 KB alignment slack + static shared memory
 
 
 @dataclass(frozen=True)
@@ -116,5 +116,5 @@ def skinny_plan(m: int, n: int, k: int, hilo: bool, dev: DeviceFacts = DeviceFac
     if stages is None:
         stages = tuned[1] if tuned else budget // sb
     longest = -(-chunks // split)
-    stages = max(1, min(stages, MAX_STAGES, longest, (SMEM_PER_CTA_MAX - 1024) // sb))
+    stages = max(1, min(stages, MAX_STAGES, longest, (SMEM_PER_CTA_MAX - 1024 - 512) // sb))
     return SkinnyPlan(ntok=ntok, split=split, stages=stages, tiles=tiles, ws_floats=ws_floats)

@@ -1,0 +1,82 @@
+"""Column-parallel projections: each rank holds a contiguous block of W's output rows, computes its
+slice of `out` with the single-GPU kernels, and the slices are all-gathered (NCCL over NVLink on
+GPUs) into the full [m, N] on every rank.
+
+The reference runs on one GPU and only carries the per-GPU shapes of such a split ("the sliced
+unpooler's all-gather is not run", bf16_proj/baseline.py:11); this is the exchange step it leaves out.
+One process per GPU, `torch.distributed` for the plumbing. The local compute is injected so that
+the sharding / gather / layout logic can be exercised with CPU ranks over gloo.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [start, stop) of an N-row weight owned by `rank`; equal blocks (all-gather needs them)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of world {world}")
+    if n % world:
+        raise ValueError(f"N={n} does not split into {world} equal row blocks")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_weights(weights: dict[str, torch.Tensor], world: int, rank: int) -> dict[str, torch.Tensor]:
+    """This rank's row block of every weight, as an independent tensor (the full weight can be freed)."""
+    out = {}
+    for name, w in weights.items():
+        a, b = shard_bounds(w.shape[0], world, rank)
+        out[name] = w[a:b].clone()
+    return out
+
+
+class ColumnParallelProjection:
+    """prepare()/kernel_fn() with the same meaning as the single-GPU entry points, over a group.
+
+    `local_prepare(weights) -> state` and `local_kernel_fn(data, state) -> Tensor` are the
+    single-device implementation (llm_inference_engine_b200.muse_bf16_proj on GPUs).
+    """
+
+    def __init__(self, local_prepare: Callable, local_kernel_fn: Callable, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._prepare = local_prepare
+        self._kernel_fn = local_kernel_fn
+        self.rows: dict[str, int] = {}
+
+    def prepare(self, weights: dict[str, torch.Tensor], already_sharded: bool = False):
+        if already_sharded:
+            shards = weights
+            self.rows = {k: v.shape[0] * self.world for k, v in weights.items()}
+        else:
+            shards = shard_weights(weights, self.world, self.rank)
+            self.rows = {k: v.shape[0] for k, v in weights.items()}
+        return self._prepare(shards)
+
+    def local_config(self, cfg: dict) -> dict:
+        n = int(cfg["n"])
+        if n != self.rows[cfg["layer"]]:
+            raise ValueError(f"column-parallel calls take the whole weight: n={n} != {self.rows[cfg['layer']]}")
+        return dict(cfg, n=n // self.world)
+
+    def kernel_fn_local(self, data: dict, state) -> torch.Tensor:
+        """This rank's [m, N / world] slice only (what the roofline of one GPU is measured on)."""
+        return self._kernel_fn({"x": data["x"], "config": self.local_config(data["config"])}, state)
+
+    def gather(self, part: torch.Tensor) -> torch.Tensor:
+        """[m, N/world] per rank -> [m, N] on every rank, rank r's block at columns r*N/world."""
+        m, n_loc = part.shape
+        buf = torch.empty((self.world * m, n_loc), device=part.device, dtype=part.dtype)
+        dist.all_gather_into_tensor(buf, part.contiguous(), group=self.group)
+        if m == 1:
+            return buf.reshape(1, self.world * n_loc)  # already in place: no copy
+        return buf.view(self.world, m, n_loc).permute(1, 0, 2).reshape(m, self.world * n_loc)
+
+    def kernel_fn(self, data: dict, state) -> torch.Tensor:
+        return self.gather(self.kernel_fn_local(data, state))

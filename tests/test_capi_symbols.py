@@ -1,0 +1,71 @@
+"""The C-ABI library builds, loads without a GPU, and exports every symbol include/muse_proj.h
+declares (no compute call is made here)."""
+
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "muse_proj.h").read_text()
+
+
+def declared_symbols() -> list[str]:
+    body = re.sub(r"/\*.*?\*/", "", HEADER, flags=re.S)
+    return sorted(set(re.findall(r"\b(muse_[a-z0-9_]+)\s*\(", body)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for must in ("muse_gemv1", "muse_skinny_tc", "muse_tmap_encode_2d", "muse_query", "muse_abi_version"):
+        assert must in names
+
+
+def test_library_builds_loads_and_exports_every_declared_symbol():
+    from llm_inference_engine_b200 import _capi, build
+
+    path = build.build()
+    assert path.exists()
+    raw = ctypes.CDLL(str(path))
+    for name in declared_symbols():
+        assert hasattr(raw, name), f"{name} declared in muse_proj.h but not exported"
+    lib = _capi.load()
+    assert set(_capi.SIGNATURES) == set(declared_symbols()), "ctypes table and header disagree"
+    assert lib.muse_abi_version() == int(re.search(r"MUSE_PROJ_ABI_VERSION\s+(\d+)", HEADER).group(1))
+
+
+def test_pure_host_entry_points_without_a_gpu():
+    from llm_inference_engine_b200 import _capi, plan
+
+    lib = _capi.load()
+    assert lib.muse_skinny_tiles(32, 12288, 32) == 96
+    assert lib.muse_skinny_tiles(300, 200, 256) == 4
+    assert lib.muse_skinny_ws_floats(32, 12288, 32) == 96 * 128 * 32
+    assert lib.muse_skinny_tiles(0, 1, 16) < 0
+    for ntok in plan.NTOK_CHOICES:
+        for hilo in (False, True):
+            assert lib.muse_skinny_stage_bytes(ntok, int(hilo)) == plan.stage_bytes(ntok, hilo)
+
+
+def test_status_bits_match_between_header_and_kernels():
+    common = (ROOT / "llm_inference_engine_b200" / "csrc" / "common.cuh").read_text()
+    for name, value in re.findall(r"#define MUSE_(ST_[A-Z_]+)\s+(\d+)", HEADER):
+        assert re.search(rf"{name}\s*=\s*{value}\b", common), f"{name} differs between header and common.cuh"
+
+
+def test_product_package_never_imports_the_oracle():
+    for py in (ROOT / "llm_inference_engine_b200").rglob("*.py"):
+        text = py.read_text()
+        assert "oracle" not in re.sub(r'""".*?"""', "", text, flags=re.S), f"{py.name} refers to the oracle"
+
+
+def test_no_cpu_fallback_when_given_cpu_tensors():
+    import torch
+
+    from llm_inference_engine_b200 import muse_bf16_proj
+
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        muse_bf16_proj.prepare({"o": torch.zeros((128, 64), dtype=torch.bfloat16)})

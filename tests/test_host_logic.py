@@ -1,0 +1,121 @@
+"""Host-side logic that needs no GPU: launch planning, the hi/lo split, shard bounds, and a CPU
+model of the tensor-core kernel's tiling + split-K + hi/lo arithmetic checked against the oracle."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from llm_inference_engine_b200 import plan, tp
+from llm_inference_engine_b200.muse_bf16_proj import split_hi_lo
+
+SHAPES = {"qkv_gate": (12288, 4096, False), "o": (4096, 4096, False), "pooler": (1024, 4096, False),
+          "unpooler": (4096, 1024, False), "router": (256, 4096, True),
+          "ref_qkv": (2304, 8192, False), "ref_o": (8192, 1024, False), "ref_router": (256, 8192, True)}
+
+
+@pytest.mark.parametrize("name", SHAPES)
+def test_gemv_plan_is_launchable(name):
+    n, k, f32 = SHAPES[name]
+    p = plan.gemv_plan(n, k, f32)
+    assert p.wpr in (1, 2, 4, 8) and p.unroll in (1, 2, 4, 8)
+    assert plan.gemv_valid(k, f32, p.wpr)
+
+
+def test_gemv_plan_rejects_unaligned_k():
+    with pytest.raises(ValueError):
+        plan.gemv_plan(128, 100, False)
+
+
+@pytest.mark.parametrize("name", SHAPES)
+@pytest.mark.parametrize("m", [2, 5, 16, 17, 32, 33, 64, 100, 128, 256, 257, 1000])
+def test_skinny_plan_respects_every_kernel_limit(name, m):
+    n, k, hilo = SHAPES[name]
+    cap = 12288 * 256
+    p = plan.skinny_plan(m, n, k, hilo, ws_floats_cap=cap, cnt_cap=4096)
+    chunks = -(-k // plan.BK)
+    assert p.ntok in plan.NTOK_CHOICES and (p.ntok >= m or p.ntok == 256)
+    assert 1 <= p.split <= chunks
+    assert 1 <= p.stages <= plan.MAX_STAGES
+    assert p.stages * plan.stage_bytes(p.ntok, hilo) + 1024 + 512 <= plan.SMEM_PER_CTA_MAX
+    assert p.tiles == -(-n // 128) * -(-m // p.ntok)
+    if p.split > 1:
+        assert p.ws_floats == p.tiles * 128 * p.ntok <= cap and p.tiles <= 4096
+    else:
+        assert p.ws_floats == 0
+    # every K slice is non-empty under the kernel's balanced split
+    bounds = [s * chunks // p.split for s in range(p.split + 1)]
+    assert all(b > a for a, b in zip(bounds, bounds[1:]))
+
+
+def test_skinny_plan_never_outgrows_the_workspace():
+    p = plan.skinny_plan(256, 12288, 4096, False, ws_floats_cap=1000, cnt_cap=4096)
+    assert p.split == 1 and p.ws_floats == 0
+    p = plan.skinny_plan(32, 12288, 4096, False, ws_floats_cap=1 << 40, cnt_cap=8)
+    assert p.split == 1
+
+
+def test_plan_overrides_are_clamped():
+    p = plan.skinny_plan(8, 1024, 4096, False, split=1000, stages=99)
+    assert p.split == 64 and p.stages == 1
+
+
+def test_hi_lo_split_recovers_fp32_weights_to_16_bits():
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn((256, 512), generator=g) * 0.02
+    hi, lo = split_hi_lo(w)
+    assert hi.dtype == lo.dtype == torch.bfloat16
+    assert torch.equal(hi, w.to(torch.bfloat16))
+    assert torch.equal(lo, (w - hi.float()).to(torch.bfloat16))
+    rel = ((hi.double() + lo.double()) - w.double()).abs() / w.double().abs().clamp(min=1e-30)
+    assert float(rel.max()) < 2.0 ** -16
+
+
+def _tile_model(x, mats, ntok, split):
+    """What the tensor-core kernel computes, in torch on the CPU: 128-row tiles, 64-wide K chunks
+    split into balanced slices, FP32 accumulation per slice (all matrices into one accumulator),
+    FP32 sum of the slices."""
+    m, k = x.shape
+    n = mats[0].shape[0]
+    chunks = -(-k // 64)
+    out = torch.zeros((m, n), dtype=torch.float32)
+    for t0 in range(0, m, ntok):
+        xs = x[t0:t0 + ntok].float()
+        for r0 in range(0, n, 128):
+            acc = torch.zeros((xs.shape[0], min(128, n - r0)), dtype=torch.float32)
+            for s in range(split):
+                c0, c1 = s * chunks // split, (s + 1) * chunks // split
+                part = torch.zeros_like(acc)
+                for mat in mats:
+                    part += xs[:, c0 * 64:c1 * 64] @ mat[r0:r0 + 128, c0 * 64:c1 * 64].float().T
+                acc += part
+            out[t0:t0 + ntok, r0:r0 + 128] = acc
+    return out
+
+
+@pytest.mark.parametrize("m,layer,split", [(5, "o", 3), (16, "qkv_gate", 7), (33, "unpooler", 2), (8, "router", 16),
+                                           (32, "router", 33)])
+def test_tiling_and_split_k_model_meets_the_reference_check(oracle, m, layer, split):
+    small = {"qkv_gate": (384, 1024), "o": (256, 512), "unpooler": (200, 768), "router": (256, 1024)}
+    w = oracle.generate_weights(7, layers=small)
+    data = oracle.generate_input(m, layer, 100 + m, layers=small)
+    data["config"]["n"] = small[layer][0]
+    ntok = plan.pick_ntok(m)
+    if layer == "router":
+        got = _tile_model(data["x"], split_hi_lo(w[layer]), ntok, split)
+    else:
+        got = _tile_model(data["x"], (w[layer],), ntok, split).to(torch.bfloat16)
+    ok, msg = oracle.check_implementation(data, got, w)
+    assert ok, msg
+
+
+def test_shard_bounds_partition_the_rows():
+    for n, world in ((12288, 8), (4096, 4), (256, 2), (1024, 1)):
+        spans = [tp.shard_bounds(n, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert len({b - a for a, b in spans}) == 1
+    with pytest.raises(ValueError):
+        tp.shard_bounds(1000, 3, 0)
+    with pytest.raises(ValueError):
+        tp.shard_bounds(1024, 4, 4)
