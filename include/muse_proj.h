@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 1
+#define MUSE_PROJ_ABI_VERSION 3
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -60,24 +60,41 @@ int muse_tmap_encode_2d(void* tmap_out128, const void* base, long long rows, lon
 long long muse_skinny_ws_floats(int m, int n, int ntok);
 int muse_skinny_tiles(int m, int n, int ntok);
 
-/* Bytes of shared memory one pipeline stage takes (W box [+ lo box] + x box). */
+/* Bytes of shared memory one pipeline stage takes (W box [+ lo box] + x box), and the dynamic shared
+ * memory a launch with `stages` stages asks for (the ring, or the parked accumulator if larger). */
 int muse_skinny_stage_bytes(int ntok, int hilo);
+int muse_skinny_smem_bytes(int ntok, int hilo, int stages, int cluster, int m);
 
-/* out[m, n] = x[m, K] . W[n, K]^T through TMA + tcgen05 (swap-AB, split-K).
+/* How many thread-block clusters of `cluster` CTAs of this launch shape the current device can hold
+ * at once (0: the shape does not fit; negative: bad argument). The planner keeps a launch within one
+ * wave with it. No counterpart in the reference. */
+int muse_skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster);
+
+/* out[m, n] = x[m, K] . W[n, K]^T through TMA + tcgen05 (swap-AB, split-K = cluster x groups).
  *   tmap_w      tensor map of W[:n] with box_rows = 128 (muse_tmap_encode_2d)
  *   tmap_w_lo   NULL for a BF16 weight; for the router the map of the "lo" half, in which case
  *               tmap_w is the "hi" half and both accumulate into one FP32 accumulator
  *   x           BF16 [m, K], 16-byte aligned, ld_x elements between rows (ld_x % 8 == 0)
  *   out         BF16, or FP32 when out_is_f32; ld_out elements between token rows (>= n)
  *   ws, cnt     zeroed workspace (muse_skinny_ws_floats floats) and counters (muse_skinny_tiles
- *               ints); left zeroed again when the kernel finishes; may be NULL when split == 1
+ *               ints); left zeroed again when the kernel finishes; may be NULL when groups == 1
  *   ntok        tokens per tile = MMA N: 16, 32, 64, 128 or 256
- *   split       K slices per tile, 1 .. ceil(K/64); stages: pipeline depth 1 .. 12
+ *   cluster     K slices reduced on chip: CTAs per thread-block cluster (1 .. 16), summed through
+ *               distributed shared memory in a fixed order
+ *   groups      clusters per tile (>= 1); their sums meet in ws through FP32 atomics, so results are
+ *               bit-reproducible only when groups == 1. cluster * groups <= ceil(K/64)
+ *   stages      pipeline depth 1 .. 12
  * Replaces _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337, :236-257), _router /
  * _router_kernel (:310-320, :260-287), _finish (:215-233) and the cuBLAS call for m > 32 (:390). */
 int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
-                   int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int split, int stages,
+                   int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
                    int out_is_f32, void* stream);
+
+/* Diagnostics: while `device_buffer` is non-NULL every CTA of the following muse_skinny_tc launches
+ * writes 16 unsigned 64-bit phase stamps (SM cycle counter; slot 15 = global nanosecond timer at
+ * entry) at device_buffer[16 * linear CTA index]; the caller sizes it for the largest grid. NULL
+ * (the default) turns stamping off. No counterpart in the reference. */
+void muse_skinny_set_trace(void* device_buffer);
 
 /* Launches an empty kernel on `stream`: the calibration point for the fixed cost of replaying a
  * one-kernel CUDA graph, which the benchmark reports beside every per-call time. Replaces the `nop`

@@ -24,12 +24,15 @@ SIGNATURES = {
     "muse_skinny_tiles": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "muse_skinny_stage_bytes": (C.c_int, [C.c_int, C.c_int]),
     "muse_skinny_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                 C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                 C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                  C.c_void_p]),
+    "muse_skinny_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "muse_skinny_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_nop": (C.c_int, [C.c_void_p]),
+    "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 1
+ABI_VERSION = 3
 
 
 class MuseError(RuntimeError):

@@ -10,9 +10,12 @@ namespace muse {
 int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
                    int* status, cudaStream_t stream);
 int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
-                       int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int split, int stages,
-                       int out_f32, cudaStream_t stream);
+                       int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
+                       int stages, int out_f32, cudaStream_t stream);
 int skinny_stage_bytes(int ntok, int hilo);
+int skinny_smem_bytes(int ntok, int hilo, int stages, int cluster, int m);
+int skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster);
+void skinny_set_trace(unsigned long long* device_buffer);
 
 // cuTensorMapEncodeTiled is a driver entry point; fetching it through the runtime keeps the
 // library free of a link-time dependency on libcuda (it must load on machines without a driver).
@@ -100,8 +103,20 @@ long long muse_skinny_ws_floats(int m, int n, int ntok) {
 
 int muse_skinny_stage_bytes(int ntok, int hilo) { return muse::skinny_stage_bytes(ntok, hilo); }
 
+void muse_skinny_set_trace(void* device_buffer) {
+  muse::skinny_set_trace(static_cast<unsigned long long*>(device_buffer));
+}
+
+int muse_skinny_smem_bytes(int ntok, int hilo, int stages, int cluster, int m) {
+  return muse::skinny_smem_bytes(ntok, hilo, stages, cluster, m);
+}
+
+int muse_skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster) {
+  return muse::skinny_max_clusters(ntok, hilo, m, stages, cluster);
+}
+
 int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
-                   int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int split, int stages,
+                   int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
                    int out_is_f32, void* stream) {
   if (!tmap_w || !x) return -1;
   if (ld_x < k || ld_x % 8 != 0) return -2;
@@ -114,7 +129,7 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
   memcpy(&tw, tmap_w, sizeof(tw));
   if (tmap_w_lo) memcpy(&twlo, tmap_w_lo, sizeof(twlo));
   return muse::skinny_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
-                                  split, stages, out_is_f32, static_cast<cudaStream_t>(stream));
+                                  cluster, groups, stages, out_is_f32, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -9,8 +9,9 @@ smaller than W's row count (the unpooler's per-GPU slice at up to 8 tokens, bf16
 
 Dispatch (shape-only, so a call is CUDA-graph capturable and replays identically):
   m == 1   streaming GEMV (csrc/gemv1.cu); the router reads its FP32 weights as they are
-  m >= 2   swap-AB split-K TMA + tcgen05 kernel (csrc/skinny_tc.cu); the router runs its BF16
-           hi + lo pair (split once here, as the reference does at :346-349) into one FP32 accumulator
+  m >= 2   swap-AB split-K TMA + tcgen05 kernel (csrc/skinny_tc.cu), K slices reduced inside thread-block
+           clusters through distributed shared memory; the router runs its BF16 hi + lo pair (split
+           once here, as the reference does at :346-349) into one FP32 accumulator
 Every path is hand-written sm_100a CUDA reached through the C ABI (include/muse_proj.h); there is no
 cuBLAS, Triton, PyTorch-matmul or CPU fallback: a non-CUDA tensor or a missing library raises.
 """
@@ -139,7 +140,7 @@ def _weight_maps(state, layer: str, n: int):
 
 
 def plan_for(state, layer: str, m: int, n: int, k: int) -> GemvPlan | SkinnyPlan:
-    """The (cached) launch plan of a shape; `state["_override"][(layer, m)]` = dict(split=, stages=) or
+    """The (cached) launch plan of a shape; `state["_override"][(layer, m)]` = dict(cluster=, groups=, stages=) or
     dict(wpr=, unroll=) forces values for tuning sweeps."""
     key = (layer, m, n, k)
     ov = state["_override"].get((layer, m))
@@ -150,7 +151,10 @@ def plan_for(state, layer: str, m: int, n: int, k: int) -> GemvPlan | SkinnyPlan
     if m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):
         plan = GemvPlan(**ov) if ov else gemv_plan(n, k, f32, dev)
     else:
-        plan = skinny_plan(m, n, k, f32, dev, ws_floats_cap=state["_ws_floats"], cnt_cap=CNT_INTS, **(ov or {}))
+        lib = _capi.load()
+        fit = lambda ntok, hilo, m_, stages, cluster: lib.muse_skinny_max_clusters(ntok, int(hilo), m_, stages, cluster)
+        plan = skinny_plan(m, n, k, f32, dev, ws_floats_cap=state["_ws_floats"], cnt_cap=CNT_INTS, max_clusters=fit,
+                           **(ov or {}))
     if ov is None:
         state["_plans"][key] = plan
     return plan
@@ -187,11 +191,11 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Ten
         return out
     maps = _weight_maps(state, layer, n)
     ws_ptr = cnt_ptr = None
-    if plan.split > 1:
+    if plan.groups > 1:
         ws, cnt = _stream_workspace(state, x.device)
         ws_ptr, cnt_ptr = ws.data_ptr(), cnt.data_ptr()
     _capi.check(lib.muse_skinny_tc(maps[0].ptr, maps[1].ptr if f32 else None, x.data_ptr(), out.data_ptr(), ws_ptr,
                                    cnt_ptr, status, m, n, k, x.stride(0) if m > 1 else k, out.stride(0), plan.ntok,
-                                   plan.split, plan.stages, int(f32), stream),
+                                   plan.cluster, plan.groups, plan.stages, int(f32), stream),
                 f"muse_skinny_tc({layer}, m={m}, n={n}, k={k}, {plan})")
     return out

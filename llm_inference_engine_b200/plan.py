@@ -14,6 +14,7 @@ from dataclasses import dataclass
 TILE_ROWS = 128          # weight rows per CTA of the tensor-core kernel (MMA M)
 BK = 64                  # K elements per pipeline stage
 MAX_STAGES = 12
+MAX_CLUSTER = 16         # 8 is the portable limit; 9..16 need the non-portable opt-in (set by the library)
 NTOK_CHOICES = (16, 32, 64, 128, 256)
 SMEM_PER_SM = 228 * 1024     # B200: shared memory per SM
 SMEM_PER_CTA_MAX = 227 * 1024
@@ -34,21 +35,60 @@ class GemvPlan:
 
 @dataclass(frozen=True)
 class SkinnyPlan:
-    ntok: int     # tokens per tile (MMA N)
-    split: int    # K slices per weight-row tile
-    stages: int   # shared-memory pipeline depth
-    tiles: int    # weight-row tiles x token tiles
-    ws_floats: int  # workspace floats needed when split > 1 (0 otherwise)
+    ntok: int       # tokens per tile (MMA N)
+    cluster: int    # K slices reduced on chip (CTAs per thread-block cluster)
+    groups: int     # clusters per tile; > 1 means their sums meet in the global workspace
+    stages: int     # shared-memory pipeline depth
+    tiles: int      # weight-row tiles x token tiles
+    ws_floats: int  # workspace floats needed when groups > 1 (0 otherwise)
+
+    @property
+    def split(self) -> int:
+        return self.cluster * self.groups
 
     @property
     def ctas(self) -> int:
         return self.tiles * self.split
 
 
-# Measured on B200 (CUDA-graph replay, cold L2): (n, k, w_is_f32) -> (wpr, unroll).
-TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int]] = {}
-# (n, k, hilo, ntok) -> (split, stages).
-TUNED_SKINNY: dict[tuple[int, int, bool, int], tuple[int, int]] = {}
+# Measured on B200 (CUDA-graph replay, cold L2, in-stream): (n, k, w_is_f32) -> (wpr, unroll).
+TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int]] = {
+    (12288, 4096, False): (1, 2),   # qkv_gate 19.8 us
+    (4096, 4096, False): (1, 4),    # o 8.6 us
+    (1024, 4096, False): (4, 4),    # pooler 3.6 us
+    (4096, 1024, False): (1, 4),    # unpooler 3.5 us
+    (256, 4096, True): (8, 4),      # router 2.8 us
+}
+# Same protocol: (n, k, hilo, token bucket) -> (ntok, cluster, groups, stages). The bucket is the
+# smallest of NTOK_CHOICES holding m; ntok may be smaller (several token tiles: small weights gain
+# more from extra tiles than they lose re-reading W through L2).
+TUNED_SKINNY: dict[tuple[int, int, bool, int], tuple[int, int, int, int]] = {
+    (12288, 4096, False, 16): (16, 3, 1, 3),     # qkv_gate 20.1 us
+    (12288, 4096, False, 32): (32, 2, 1, 4),     # 23.0
+    (12288, 4096, False, 64): (64, 1, 1, 6),     # 26.5
+    (12288, 4096, False, 128): (128, 1, 1, 6),   # 27.7
+    (12288, 4096, False, 256): (256, 1, 1, 4),   # 32.4
+    (4096, 4096, False, 16): (16, 8, 1, 3),      # o 9.9
+    (4096, 4096, False, 32): (32, 8, 1, 4),      # 10.5
+    (4096, 4096, False, 64): (64, 4, 1, 6),      # 15.5
+    (4096, 4096, False, 128): (64, 2, 1, 4),     # 19.4
+    (4096, 4096, False, 256): (128, 2, 1, 4),    # 24.7
+    (1024, 4096, False, 16): (16, 16, 1, 4),     # pooler 6.9
+    (1024, 4096, False, 32): (32, 16, 1, 3),     # 7.4
+    (1024, 4096, False, 64): (64, 16, 1, 3),     # 9.0
+    (1024, 4096, False, 128): (64, 6, 1, 4),     # 11.8
+    (1024, 4096, False, 256): (128, 6, 1, 4),    # 17.2
+    (4096, 1024, False, 16): (16, 6, 1, 4),      # unpooler 6.2
+    (4096, 1024, False, 32): (32, 8, 1, 2),      # 7.3
+    (4096, 1024, False, 64): (64, 1, 1, 4),      # 9.6
+    (4096, 1024, False, 128): (64, 1, 1, 4),     # 9.7
+    (4096, 1024, False, 256): (128, 1, 1, 4),    # 10.8
+    (256, 4096, True, 16): (16, 1, 64, 2),       # router 6.7
+    (256, 4096, True, 32): (32, 1, 37, 2),       # 10.2
+    (256, 4096, True, 64): (64, 16, 1, 3),       # 8.1
+    (256, 4096, True, 128): (64, 16, 1, 4),      # 8.0
+    (256, 4096, True, 256): (128, 12, 1, 2),     # 14.7
+}
 
 
 def _pow2_floor(v: int) -> int:
@@ -85,36 +125,88 @@ def stage_bytes(ntok: int, hilo: bool) -> int:
     return TILE_ROWS * BK * 2 * (2 if hilo else 1) + ntok * BK * 2
 
 
+def owner_block(mvalid: int, cluster: int) -> int:
+    """Tokens per owner CTA when a tile's tokens are dealt to the CTAs of a cluster (whole fours)."""
+    return (-(-mvalid // cluster) + 3) & ~3
+
+
+def smem_bytes(ntok: int, hilo: bool, stages: int, cluster: int = 1, m: int | None = None) -> int:
+    """Dynamic shared memory of a launch: the ring, the receive slots of a clustered launch, 1 KB slack."""
+    mvalid = ntok if m is None else min(m, ntok)
+    rx = cluster * TILE_ROWS * owner_block(mvalid, cluster) * 4 if cluster > 1 else 0
+    ring = stages * stage_bytes(ntok, hilo)
+    staged_tokens = owner_block(mvalid, cluster) if cluster > 1 else (mvalid + 3) & ~3
+    staged = staged_tokens * TILE_ROWS * 4 if staged_tokens > 16 else 0   # vector-store staging overlays the ring
+    return max(ring, staged) + rx + 1024
+
+
 def skinny_plan(m: int, n: int, k: int, hilo: bool, dev: DeviceFacts = DeviceFacts(),
                 ws_floats_cap: int = 1 << 62, cnt_cap: int = 1 << 30,
-                split: int | None = None, stages: int | None = None) -> SkinnyPlan:
+                ntok: int | None = None, cluster: int | None = None, groups: int | None = None,
+                stages: int | None = None, max_clusters=None) -> SkinnyPlan:
     """Units (row tile x K slice x token tile) sized to fill the SMs in one wave.
 
-    Two CTAs share an SM when four stages of each fit in half its shared memory (more loads in
-    flight while the other CTA is in its prologue or epilogue); otherwise one CTA takes the SM.
-    `split` / `stages` override the derived values (tuning sweeps).
+    Shapes that were swept on a B200 take their measured best (TUNED_SKINNY). Otherwise: the K slices
+    of a tile form one cluster of up to 8 CTAs (16 when there are few tiles) that reduces on chip,
+    sized so that all CTAs are resident at once with two CTAs per SM; small weights at many tokens
+    use half-size token tiles to get more units. `max_clusters(ntok, hilo, m, stages, cluster)`, when
+    given (the device's occupancy query), shrinks the cluster until the launch fits in one wave.
+    `ntok` / `cluster` / `groups` / `stages` override everything (tuning sweeps).
     """
     if k % 8 != 0:
         raise ValueError(f"K={k}: the kernels need K % 8 == 0 (16-byte aligned rows for TMA)")
-    ntok = pick_ntok(m)
-    sb = stage_bytes(ntok, hilo)
-    tiles = -(-n // TILE_ROWS) * -(-m // ntok)
     chunks = -(-k // BK)
-    half = SMEM_PER_SM // 2 - CTA_RESERVED
-    per_sm = 2 if 4 * sb <= half else 1
-    budget = min(dev.smem_optin, SMEM_PER_SM // per_sm) - CTA_RESERVED
-    tuned = TUNED_SKINNY.get((n, k, hilo, ntok))
-    if split is None:
-        if tuned:
-            split = tuned[0]
-        else:
-            split = max(1, (dev.sms * per_sm) // tiles)
-    split = max(1, min(split, chunks))
-    ws_floats = tiles * TILE_ROWS * ntok if split > 1 else 0
-    if split > 1 and (ws_floats > ws_floats_cap or tiles > cnt_cap):
-        split, ws_floats = 1, 0   # never allocate behind the caller's back: fall back to one slice
+    n_tiles = -(-n // TILE_ROWS)
+    bucket = pick_ntok(m)
+    forced = ntok is not None or cluster is not None or groups is not None
+    tuned = None if forced else TUNED_SKINNY.get((n, k, hilo, bucket))
+    if tuned:
+        ntok, cluster, groups = tuned[0], tuned[1], tuned[2]
+        if stages is None:
+            stages = tuned[3]
+    if ntok is None:
+        ntok = bucket
+        if m > 64 and n_tiles * -(-m // ntok) * 4 <= dev.sms:
+            ntok = max(64, ntok // 2)
+    if ntok not in NTOK_CHOICES:
+        raise ValueError(f"ntok={ntok}: must be one of {NTOK_CHOICES}")
+    sb = stage_bytes(ntok, hilo)
+    tiles = n_tiles * -(-m // ntok)
+    limit = SMEM_PER_CTA_MAX - 512
+
+    def deepest(cap: int, cl: int) -> int:
+        """Most stages whose launch fits in `cap` bytes of dynamic shared memory (0: not even one)."""
+        best = 0
+        for st in range(1, MAX_STAGES + 1):
+            if smem_bytes(ntok, hilo, st, cl, m) <= cap:
+                best = st
+        return best
+
+    if cluster is None:
+        want = max(1, min((dev.sms * 2) // tiles, chunks))
+        cluster = min(want, 16 if tiles <= 16 else 8)
+    if groups is None:
+        groups = 1
+    cluster = max(1, min(cluster, MAX_CLUSTER, chunks))
+    while cluster > 1 and deepest(limit, cluster) < 2:
+        cluster -= 1   # the receive slots must leave room for at least a two-stage ring
+    groups = max(1, min(groups, chunks // cluster))
+    longest = -(-chunks // (cluster * groups))
     if stages is None:
-        stages = tuned[1] if tuned else budget // sb
-    longest = -(-chunks // split)
-    stages = max(1, min(stages, MAX_STAGES, longest, (SMEM_PER_CTA_MAX - 1024 - 512) // sb))
-    return SkinnyPlan(ntok=ntok, split=split, stages=stages, tiles=tiles, ws_floats=ws_floats)
+        two_per_sm = SMEM_PER_SM // 2 - 1024 - 512
+        want_two = tiles * cluster * groups > dev.sms
+        shared = deepest(two_per_sm, cluster) if want_two else 0
+        stages = min(6, shared if shared >= 3 else deepest(limit, cluster))
+    stages = max(1, min(stages, longest, deepest(limit, cluster)))
+    if max_clusters is not None and not forced and not tuned:
+        while cluster > 1:
+            per_sm = max(1, SMEM_PER_SM // (smem_bytes(ntok, hilo, stages, cluster, m) + 1024 + 512))
+            fit = max_clusters(ntok, hilo, m, stages, cluster)
+            if fit <= 0 or tiles * groups <= fit * per_sm:
+                break
+            cluster -= 1
+            stages = max(1, min(stages, deepest(limit, cluster)))
+    ws_floats = tiles * TILE_ROWS * ntok if groups > 1 else 0
+    if groups > 1 and (ws_floats > ws_floats_cap or tiles > cnt_cap):
+        groups, ws_floats = 1, 0   # never allocate behind the caller's back: one cluster per tile instead
+    return SkinnyPlan(ntok=ntok, cluster=cluster, groups=groups, stages=stages, tiles=tiles, ws_floats=ws_floats)

@@ -48,6 +48,9 @@ def test_pure_host_entry_points_without_a_gpu():
     for ntok in plan.NTOK_CHOICES:
         for hilo in (False, True):
             assert lib.muse_skinny_stage_bytes(ntok, int(hilo)) == plan.stage_bytes(ntok, hilo)
+            for stages, cluster, m in ((1, 1, 1), (4, 3, 32), (12, 8, 5), (3, 16, 300)):
+                assert (lib.muse_skinny_smem_bytes(ntok, int(hilo), stages, cluster, m)
+                        == plan.smem_bytes(ntok, hilo, stages, cluster, m))
 
 
 def test_status_bits_match_between_header_and_kernels():

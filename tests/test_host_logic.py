@@ -34,12 +34,13 @@ def test_skinny_plan_respects_every_kernel_limit(name, m):
     cap = 12288 * 256
     p = plan.skinny_plan(m, n, k, hilo, ws_floats_cap=cap, cnt_cap=4096)
     chunks = -(-k // plan.BK)
-    assert p.ntok in plan.NTOK_CHOICES and (p.ntok >= m or p.ntok == 256)
-    assert 1 <= p.split <= chunks
+    assert p.ntok in plan.NTOK_CHOICES
+    assert 1 <= p.split <= chunks and p.split == p.cluster * p.groups
+    assert 1 <= p.cluster <= plan.MAX_CLUSTER
     assert 1 <= p.stages <= plan.MAX_STAGES
-    assert p.stages * plan.stage_bytes(p.ntok, hilo) + 1024 + 512 <= plan.SMEM_PER_CTA_MAX
+    assert plan.smem_bytes(p.ntok, hilo, p.stages, p.cluster, m) + 512 <= plan.SMEM_PER_CTA_MAX
     assert p.tiles == -(-n // 128) * -(-m // p.ntok)
-    if p.split > 1:
+    if p.groups > 1:
         assert p.ws_floats == p.tiles * 128 * p.ntok <= cap and p.tiles <= 4096
     else:
         assert p.ws_floats == 0
@@ -49,15 +50,31 @@ def test_skinny_plan_respects_every_kernel_limit(name, m):
 
 
 def test_skinny_plan_never_outgrows_the_workspace():
-    p = plan.skinny_plan(256, 12288, 4096, False, ws_floats_cap=1000, cnt_cap=4096)
-    assert p.split == 1 and p.ws_floats == 0
-    p = plan.skinny_plan(32, 12288, 4096, False, ws_floats_cap=1 << 40, cnt_cap=8)
-    assert p.split == 1
+    p = plan.skinny_plan(32, 256, 4096, True, ws_floats_cap=1000, cnt_cap=4096)
+    assert p.groups == 1 and p.ws_floats == 0
+    p = plan.skinny_plan(32, 256, 4096, True, ws_floats_cap=1 << 40, cnt_cap=1)
+    assert p.groups == 1
+    p = plan.skinny_plan(32, 256, 4096, True)
+    assert p.groups > 1 and p.ws_floats == p.tiles * 128 * 32
 
 
 def test_plan_overrides_are_clamped():
-    p = plan.skinny_plan(8, 1024, 4096, False, split=1000, stages=99)
-    assert p.split == 64 and p.stages == 1
+    p = plan.skinny_plan(8, 1024, 4096, False, cluster=1000, groups=1000, stages=99)
+    assert p.cluster == 16 and p.groups == 4 and p.stages == 1
+    p = plan.skinny_plan(200, 1024, 4096, False, ntok=64, cluster=2)
+    assert p.ntok == 64 and p.tiles == 8 * 4 and p.cluster == 2 and p.groups == 1
+
+
+def test_tuned_entries_are_launchable():
+    for (n, k, hilo, bucket), (ntok, cluster, groups, stages) in plan.TUNED_SKINNY.items():
+        assert bucket in plan.NTOK_CHOICES and ntok in plan.NTOK_CHOICES and ntok <= bucket
+        assert cluster * groups <= -(-k // plan.BK) and 1 <= cluster <= plan.MAX_CLUSTER
+        assert plan.smem_bytes(ntok, hilo, stages, cluster, bucket) + 512 <= plan.SMEM_PER_CTA_MAX
+        p = plan.skinny_plan(bucket, n, k, hilo)
+        longest = -(-(-(-k // plan.BK)) // (cluster * groups))   # no more stages than chunks in a K slice
+        assert (p.ntok, p.cluster, p.groups, p.stages) == (ntok, cluster, groups, min(stages, longest))
+    for (n, k, f32), (wpr, unroll) in plan.TUNED_GEMV.items():
+        assert plan.gemv_valid(k, f32, wpr) and unroll in (1, 2, 4, 8)
 
 
 def test_hi_lo_split_recovers_fp32_weights_to_16_bits():
