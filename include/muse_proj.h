@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 3
+#define MUSE_PROJ_ABI_VERSION 4
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -43,10 +43,12 @@ int muse_query(int what);
 /* y[N] = W[N,K] . x[K], one token. W BF16 (out BF16) or FP32 when w_is_f32 (out FP32); x BF16,
  * 16-byte aligned; K % 8 == 0; wpr in {1,2,4,8} warps share a row, K % wpr == 0 and each K / wpr
  * segment a whole number of 16-byte vectors; unroll in {1,2,4,8} 16-byte loads in flight per lane
- * per batch. Replaces gemv1_launch (bf16_proj/gemv1.cu:122-125; pybind wrapper
+ * per batch. persistent != 0 (wpr must be 1): a grid that is resident all at once, each warp
+ * walking rows g, g + G, ... with its loads double-buffered across row boundaries (tall weights).
+ * Replaces gemv1_launch (bf16_proj/gemv1.cu:122-125; pybind wrapper
  * best_submissions/muse_bf16_proj.py:193-196). */
-int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int* status,
-               void* stream);
+int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,
+               int* status, void* stream);
 
 /* Fill a 128-byte tensor map for a row-major BF16 matrix [rows, cols] at `base` (device pointer,
  * 16-byte aligned) with `row_stride_bytes` between rows (multiple of 16), delivering boxes of

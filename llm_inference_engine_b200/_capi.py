@@ -17,7 +17,7 @@ _LIB = None
 SIGNATURES = {
     "muse_abi_version": (C.c_int, []),
     "muse_query": (C.c_int, [C.c_int]),
-    "muse_gemv1": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+    "muse_gemv1": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                              C.c_void_p, C.c_void_p]),
     "muse_tmap_encode_2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong, C.c_int]),
     "muse_skinny_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
@@ -32,7 +32,7 @@ SIGNATURES = {
     "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 class MuseError(RuntimeError):

@@ -8,7 +8,7 @@
 
 namespace muse {
 int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
-                   int* status, cudaStream_t stream);
+                   int persistent, int* status, cudaStream_t stream);
 int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                        int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                        int stages, int out_f32, cudaStream_t stream);
@@ -78,9 +78,10 @@ int muse_query(int what) {
   return e == cudaSuccess ? v : -1;
 }
 
-int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int* status,
-               void* stream) {
-  return muse::gemv1_dispatch(W, x, out, N, K, w_is_f32, wpr, unroll, status, static_cast<cudaStream_t>(stream));
+int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,
+               int* status, void* stream) {
+  return muse::gemv1_dispatch(W, x, out, N, K, w_is_f32, wpr, unroll, persistent, status,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int muse_tmap_encode_2d(void* tmap_out128, const void* base, long long rows, long long cols,

@@ -106,6 +106,128 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
   }
 }
 
+// Whole-row variant for tall weights: a persistent grid (every CTA resident at once), warp g of the
+// grid takes rows g, g + G, g + 2G, ... . The (row, batch) steps of a warp form one stream that stays
+// double-buffered across row boundaries, x is fetched once per CTA instead of once per 8 rows, and
+// every SM ends up with the same number of rows to within one, so the grid drains together.
+template <int U, bool F32W>
+__global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict__ W, const __nv_bfloat16* __restrict__ x,
+                                                         void* __restrict__ out, int N, int K, int* __restrict__ status) {
+  constexpr int EPV = F32W ? 4 : 8;
+  constexpr int WB = F32W ? 4 : 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t xbar;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_warps = gridDim.x * 8;
+  const int gw = blockIdx.x * 8 + warp;
+  const int nvec = K / EPV;
+  const int nb = (nvec + 32 * U - 1) / (32 * U);            // batches per row
+  const int my_rows = gw < N ? (N - gw + total_warps - 1) / total_warps : 0;
+  const int steps = my_rows * nb;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&xbar), 1);
+    fence_mbar_init();
+    mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u);
+    bulk_load_1d(smem_u32(smem), x, static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
+  }
+  auto row_ptr = [&](int r) {
+    return reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(W) +
+                                          static_cast<size_t>(gw + r * total_warps) * K * WB);
+  };
+  uint4 w[U], wn[U];
+  if (steps > 0) load_batch<U>(w, row_ptr(0), lane, nvec);
+  __syncthreads();
+  if (!mbar_wait(smem_u32(&xbar), 0)) {
+    if (threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
+    return;
+  }
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int r = 0, b = 0;
+  for (int s = 0; s < steps; ++s) {
+    int rn = r, bn = b + 1;
+    if (bn == nb) { bn = 0; ++rn; }
+    if (s + 1 < steps) load_batch<U>(wn, row_ptr(rn), bn * 32 * U + lane, nvec);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = b * 32 * U + u * 32 + lane;
+      if (v < nvec) {
+        if constexpr (F32W) {
+          const uint2 xv = *reinterpret_cast<const uint2*>(smem + static_cast<size_t>(v) * 8);
+          a0 = fmaf(__uint_as_float(w[u].x), bf16lo_f32(xv.x), a0);
+          a1 = fmaf(__uint_as_float(w[u].y), bf16hi_f32(xv.x), a1);
+          a2 = fmaf(__uint_as_float(w[u].z), bf16lo_f32(xv.y), a2);
+          a3 = fmaf(__uint_as_float(w[u].w), bf16hi_f32(xv.y), a3);
+        } else {
+          const uint4 xv = *reinterpret_cast<const uint4*>(smem + static_cast<size_t>(v) * 16);
+          a0 = fmaf(bf16lo_f32(w[u].x), bf16lo_f32(xv.x), a0);
+          a1 = fmaf(bf16hi_f32(w[u].x), bf16hi_f32(xv.x), a1);
+          a2 = fmaf(bf16lo_f32(w[u].y), bf16lo_f32(xv.y), a2);
+          a3 = fmaf(bf16hi_f32(w[u].y), bf16hi_f32(xv.y), a3);
+          a0 = fmaf(bf16lo_f32(w[u].z), bf16lo_f32(xv.z), a0);
+          a1 = fmaf(bf16hi_f32(w[u].z), bf16hi_f32(xv.z), a1);
+          a2 = fmaf(bf16lo_f32(w[u].w), bf16lo_f32(xv.w), a2);
+          a3 = fmaf(bf16hi_f32(w[u].w), bf16hi_f32(xv.w), a3);
+        }
+      }
+    }
+    if (b == nb - 1) {  // row finished: reduce across the warp and store
+      float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) {
+        const int row = gw + r * total_warps;
+        if constexpr (F32W) reinterpret_cast<float*>(out)[row] = acc;
+        else reinterpret_cast<__nv_bfloat16*>(out)[row] = __float2bfloat16_rn(acc);
+      }
+      a0 = a1 = a2 = a3 = 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) w[u] = wn[u];
+    r = rn;
+    b = bn;
+  }
+}
+
+template <int U, bool F32W>
+static cudaError_t launch_rows(const void* W, const void* x, void* out, int N, int K, int* status, cudaStream_t s) {
+  auto kern = gemv1_rows_kernel<U, F32W>;
+  static int per_sm[64] = {0}, sms[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  const int smem = K * 2;
+  if (!per_sm[dev]) {
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    int nblk = 0;
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nblk, kern, 256, 16 * 1024)) != cudaSuccess) return e;
+    per_sm[dev] = nblk > 0 ? nblk : 1;
+  }
+  int resident = per_sm[dev];
+  if (smem > 16 * 1024) {  // long rows: recompute residency for this K
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, 256, smem)) != cudaSuccess) return e;
+    if (resident < 1) resident = 1;
+  }
+  int grid = sms[dev] * resident;
+  const int need = (N + 7) / 8;
+  if (grid > need) grid = need;
+  kern<<<grid, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status);
+  return cudaGetLastError();
+}
+
+template <bool F32W>
+static cudaError_t pick_rows(const void* W, const void* x, void* out, int N, int K, int u, int* st, cudaStream_t s) {
+  switch (u) {
+    case 1: return launch_rows<1, F32W>(W, x, out, N, K, st, s);
+    case 2: return launch_rows<2, F32W>(W, x, out, N, K, st, s);
+    case 4: return launch_rows<4, F32W>(W, x, out, N, K, st, s);
+    case 8: return launch_rows<8, F32W>(W, x, out, N, K, st, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
 template <int WPR, int U, bool F32W>
 static cudaError_t launch(const void* W, const void* x, void* out, int N, int K, int* status, cudaStream_t s) {
   constexpr int RPC = 8 / WPR;
@@ -144,13 +266,18 @@ static cudaError_t pick_wpr(const void* W, const void* x, void* out, int N, int 
 
 // Argument checks live here so that the C-ABI wrapper stays a one-liner. Negative = argument error.
 int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
-                   int* status, cudaStream_t stream) {
+                   int persistent, int* status, cudaStream_t stream) {
   if (!W || !x || !out || !status || N <= 0 || K <= 0) return -1;
   const int epv = w_is_f32 ? 4 : 8;
   if (K % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
   if (wpr != 1 && wpr != 2 && wpr != 4 && wpr != 8) return -3;
   if (K % wpr != 0 || (K / wpr) % epv != 0) return -4;
   if (K * 2 > 200 * 1024) return -5;
+  if (persistent) {
+    if (wpr != 1) return -6;  // whole rows per warp only
+    return static_cast<int>(w_is_f32 ? pick_rows<true>(W, x, out, N, K, unroll, status, stream)
+                                     : pick_rows<false>(W, x, out, N, K, unroll, status, stream));
+  }
   const cudaError_t e = w_is_f32 ? pick_wpr<true>(W, x, out, N, K, wpr, unroll, status, stream)
                                  : pick_wpr<false>(W, x, out, N, K, wpr, unroll, status, stream);
   return static_cast<int>(e);

@@ -187,7 +187,7 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Ten
     status = state["_status"].data_ptr()
     if isinstance(plan, GemvPlan):
         _capi.check(lib.muse_gemv1(w.data_ptr(), x.data_ptr(), out.data_ptr(), n, k, int(f32), plan.wpr, plan.unroll,
-                                   status, stream), f"muse_gemv1({layer}, n={n}, k={k})")
+                                   int(plan.persistent), status, stream), f"muse_gemv1({layer}, n={n}, k={k})")
         return out
     maps = _weight_maps(state, layer, n)
     ws_ptr = cnt_ptr = None

@@ -31,6 +31,7 @@ class DeviceFacts:
 class GemvPlan:
     wpr: int      # warps sharing one weight row
     unroll: int   # 16-byte loads in flight per lane per batch
+    persistent: bool = False   # whole rows per warp on a grid that is resident all at once (wpr == 1)
 
 
 @dataclass(frozen=True)
@@ -51,13 +52,13 @@ class SkinnyPlan:
         return self.tiles * self.split
 
 
-# Measured on B200 (CUDA-graph replay, cold L2, in-stream): (n, k, w_is_f32) -> (wpr, unroll).
-TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int]] = {
-    (12288, 4096, False): (1, 2),   # qkv_gate 19.8 us
-    (4096, 4096, False): (1, 4),    # o 8.6 us
-    (1024, 4096, False): (4, 4),    # pooler 3.6 us
-    (4096, 1024, False): (1, 4),    # unpooler 3.5 us
-    (256, 4096, True): (8, 4),      # router 2.8 us
+# Measured on B200 (CUDA-graph replay, cold L2, in-stream): (n, k, w_is_f32) -> (wpr, unroll, persistent).
+TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int, bool]] = {
+    (12288, 4096, False): (1, 4, True),    # qkv_gate 18.3 us (19.8 non-persistent)
+    (4096, 4096, False): (1, 4, True),     # o 8.0 us (8.8)
+    (1024, 4096, False): (4, 4, False),    # pooler 3.7 us
+    (4096, 1024, False): (1, 4, False),    # unpooler 3.5 us
+    (256, 4096, True): (8, 4, False),      # router 2.8 us
 }
 # Same protocol: (n, k, hilo, token bucket) -> (ntok, cluster, groups, stages). The bucket is the
 # smallest of NTOK_CHOICES holding m; ntok may be smaller (several token tiles: small weights gain
@@ -83,8 +84,8 @@ TUNED_SKINNY: dict[tuple[int, int, bool, int], tuple[int, int, int, int]] = {
     (4096, 1024, False, 64): (64, 1, 1, 4),      # 9.6
     (4096, 1024, False, 128): (64, 1, 1, 4),     # 9.7
     (4096, 1024, False, 256): (128, 1, 1, 4),    # 10.8
-    (256, 4096, True, 16): (16, 1, 64, 2),       # router 6.7
-    (256, 4096, True, 32): (32, 1, 37, 2),       # 10.2
+    (256, 4096, True, 16): (16, 16, 1, 3),       # router 6.6
+    (256, 4096, True, 32): (32, 16, 1, 3),       # 7.0
     (256, 4096, True, 64): (64, 16, 1, 3),       # 8.1
     (256, 4096, True, 128): (64, 16, 1, 4),      # 8.0
     (256, 4096, True, 256): (128, 12, 1, 2),     # 14.7
@@ -114,7 +115,9 @@ def gemv_plan(n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) 
     want = 4 * dev.sms
     wpr = next((w for w in valid if -(-n // (8 // w)) >= want), valid[-1])
     vec_per_lane = max(1, (k // wpr // epv + 31) // 32)
-    return GemvPlan(wpr=wpr, unroll=min(4, _pow2_floor(vec_per_lane)))
+    # Tall weights (several rows per resident warp slot) drain more evenly on the persistent grid.
+    persistent = wpr == 1 and n >= 16 * dev.sms and k * 2 <= 64 * 1024
+    return GemvPlan(wpr=wpr, unroll=min(4, _pow2_floor(vec_per_lane)), persistent=persistent)
 
 
 def pick_ntok(m: int) -> int:

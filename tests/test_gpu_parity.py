@@ -123,9 +123,14 @@ def test_gemv_is_bit_identical_across_row_slices(oracle, proj, dev, target_setup
     reproduces the single-GPU GEMV bit for bit."""
     w_cpu, state = target_setup
     data = oracle.target_input(1, "o", 99, device="cpu")
-    full = _run(proj, state, data, dev)
     half = dict(data, config=dict(data["config"], n=2048))
-    assert torch.equal(_run(proj, state, half, dev), full[:, :2048])
+    for pinned in (dict(wpr=1, unroll=4, persistent=True), dict(wpr=2, unroll=2, persistent=False)):
+        state["_override"][("o", 1)] = pinned   # same K split and batch order on both sides
+        try:
+            full = _run(proj, state, data, dev)
+            assert torch.equal(_run(proj, state, half, dev), full[:, :2048])
+        finally:
+            del state["_override"][("o", 1)]
 
 
 def test_linearity_at_full_size(oracle, proj, dev, target_setup):
@@ -142,33 +147,61 @@ def test_linearity_at_full_size(oracle, proj, dev, target_setup):
     assert float(err) < 8e-3
 
 
-def test_graph_replays_are_stable_and_leave_workspace_clean(oracle, proj, dev, target_setup):
+# (layer, m, forced plan or None for the planner's own choice). The forced plans cover what the planner
+# rarely picks on its own: sums meeting in the global workspace (groups > 1), with and without clusters.
+REPLAY_CASES = [
+    ("qkv_gate", 32, None), ("pooler", 8, None), ("router", 32, None), ("router", 256, None), ("unpooler", 128, None),
+    ("qkv_gate", 32, dict(cluster=1, groups=3, stages=4)),
+    ("pooler", 8, dict(cluster=2, groups=9, stages=3)),
+    ("pooler", 100, dict(ntok=128, cluster=4, groups=2, stages=3)),
+    ("router", 32, dict(cluster=1, groups=37, stages=2)),
+    ("router", 16, dict(cluster=8, groups=8, stages=1)),
+    ("o", 5, dict(cluster=16, groups=1, stages=3)),
+]
+
+
+@pytest.mark.parametrize("layer,m,forced", REPLAY_CASES, ids=lambda v: str(v).replace(" ", ""))
+def test_graph_replays_are_stable_and_leave_workspace_clean(oracle, proj, dev, target_setup, layer, m, forced):
     """The split-K hand-off under replay (the reference's stress pattern, bf16_proj/stress.py:122-169):
-    many cold-L2 replays, no bad output, workspace and counters back to zero afterwards."""
+    many cold-L2 replays, no bad output, workspace and counters back to zero afterwards; plans without
+    the global workspace (groups == 1) must also reproduce their output bit for bit."""
     from llm_inference_engine_b200.graph_timer import ColdReplayTimer
 
     w_cpu, state = target_setup
     timer = ColdReplayTimer(dev, flush_bytes=256 << 20)
-    for layer, m in (("qkv_gate", 32), ("pooler", 8), ("router", 32), ("router", 256), ("unpooler", 128)):
-        data = oracle.target_input(m, layer, 4242 + m, device="cpu")
-        x = data["x"].to(dev)
-        ref = (data["x"].double() @ w_cpu[layer].double().T).to(dev)
-        rn = ref.norm(dim=1).clamp(min=1e-6)
-        holder = {}
+    data = oracle.target_input(m, layer, 4242 + m, device="cpu")
+    x = data["x"].to(dev)
+    ref = (data["x"].double() @ w_cpu[layer].double().T).to(dev)
+    rn = ref.norm(dim=1).clamp(min=1e-6)
+    holder = {}
+    if forced:
+        state["_override"][(layer, m)] = forced
+    try:
+        plan = proj.plan_for(state, layer, m, *w_cpu[layer].shape)
         with torch.cuda.stream(timer.stream):
             graph = timer.capture(lambda: holder.__setitem__("out", proj.kernel_fn({"x": x, "config": data["config"]}, state)))
             bad = torch.zeros((), device=dev, dtype=torch.int32)
+            changed = torch.zeros((), device=dev, dtype=torch.int32)
             limit = 2e-5 if layer == "router" else 5e-3
+            first = None
             for i in range(300):
                 if i % 2 == 0:
                     timer.flush.fill_(i & 0xFF)
                 graph.replay()
                 err = ((holder["out"].double() - ref).norm(dim=1) / rn).max()
                 bad += (err > limit).int()
+                if first is None:
+                    first = holder["out"].clone()
+                else:
+                    changed += (holder["out"] != first).any().int()
             timer.stream.synchronize()
-            assert int(bad) == 0, f"{layer} m={m}: {int(bad)}/300 bad replays"
+            assert int(bad) == 0, f"{layer} m={m} {plan}: {int(bad)}/300 bad replays"
+            if plan.groups == 1:
+                assert int(changed) == 0, f"{layer} m={m} {plan}: output changed between replays"
             ws, cnt = state["_ws_by_stream"][timer.stream.cuda_stream]
             assert float(ws.abs().max()) == 0.0 and int(cnt.abs().max()) == 0
+    finally:
+        state["_override"].pop((layer, m), None)
     proj.check_status(state)
 
 

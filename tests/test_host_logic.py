@@ -50,12 +50,12 @@ def test_skinny_plan_respects_every_kernel_limit(name, m):
 
 
 def test_skinny_plan_never_outgrows_the_workspace():
-    p = plan.skinny_plan(32, 256, 4096, True, ws_floats_cap=1000, cnt_cap=4096)
+    p = plan.skinny_plan(32, 256, 4096, True, cluster=2, groups=8, ws_floats_cap=1000, cnt_cap=4096)
     assert p.groups == 1 and p.ws_floats == 0
-    p = plan.skinny_plan(32, 256, 4096, True, ws_floats_cap=1 << 40, cnt_cap=1)
+    p = plan.skinny_plan(32, 256, 4096, True, cluster=2, groups=8, ws_floats_cap=1 << 40, cnt_cap=1)
     assert p.groups == 1
-    p = plan.skinny_plan(32, 256, 4096, True)
-    assert p.groups > 1 and p.ws_floats == p.tiles * 128 * 32
+    p = plan.skinny_plan(32, 256, 4096, True, cluster=2, groups=8)
+    assert p.groups == 8 and p.ws_floats == p.tiles * 128 * 32
 
 
 def test_plan_overrides_are_clamped():
@@ -73,8 +73,8 @@ def test_tuned_entries_are_launchable():
         p = plan.skinny_plan(bucket, n, k, hilo)
         longest = -(-(-(-k // plan.BK)) // (cluster * groups))   # no more stages than chunks in a K slice
         assert (p.ntok, p.cluster, p.groups, p.stages) == (ntok, cluster, groups, min(stages, longest))
-    for (n, k, f32), (wpr, unroll) in plan.TUNED_GEMV.items():
-        assert plan.gemv_valid(k, f32, wpr) and unroll in (1, 2, 4, 8)
+    for (n, k, f32), (wpr, unroll, persistent) in plan.TUNED_GEMV.items():
+        assert plan.gemv_valid(k, f32, wpr) and unroll in (1, 2, 4, 8) and (wpr == 1 or not persistent)
 
 
 def test_hi_lo_split_recovers_fp32_weights_to_16_bits():
