@@ -198,8 +198,9 @@ def test_graph_replays_are_stable_and_leave_workspace_clean(oracle, proj, dev, t
             assert int(bad) == 0, f"{layer} m={m} {plan}: {int(bad)}/300 bad replays"
             if plan.groups == 1:
                 assert int(changed) == 0, f"{layer} m={m} {plan}: output changed between replays"
-            ws, cnt = state["_ws_by_stream"][timer.stream.cuda_stream]
-            assert float(ws.abs().max()) == 0.0 and int(cnt.abs().max()) == 0
+            if plan.groups > 1:   # only these plans touch (and therefore create) the stream's workspace
+                ws, cnt = state["_ws_by_stream"][timer.stream.cuda_stream]
+                assert float(ws.abs().max()) == 0.0 and int(cnt.abs().max()) == 0
     finally:
         state["_override"].pop((layer, m), None)
     proj.check_status(state)
