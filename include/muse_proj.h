@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 4
+#define MUSE_PROJ_ABI_VERSION 5
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -91,6 +91,34 @@ int muse_skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster)
 int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
                    int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
                    int out_is_f32, void* stream);
+
+/* muse_skinny_tc for callers that must not allocate device memory. No counterpart in the reference.
+ *
+ * Some hosts of this library cannot hand it a workspace: an inference server that gave every byte
+ * of HBM to its own pool at start-up and forbids later cudaMalloc calls (they would fail, or
+ * stall every stream while the driver maps memory); a plug-in slot whose contract is "inputs and
+ * outputs only"; code running inside a latency-critical loop where an allocation is a
+ * device-wide synchronisation. For them the split-K scratch (partial sums + tile counters) lives in
+ * the library itself: a fixed array in device memory that exists on every GPU that loads the library,
+ * from load until the process exits. Its capacity is muse_static_scratch_floats() floats
+ * (1 Mi = 4 MiB) and muse_static_scratch_tiles() counters (4096): a launch needs
+ * muse_skinny_ws_floats(m, n, ntok) floats and muse_skinny_tiles(m, n, ntok) counters, and a shape
+ * that needs more is rejected with MUSE_ERR_STATIC_SCRATCH (-20) before anything is launched.
+ * The caller still passes x, out and the status word; everything else is as for muse_skinny_tc.
+ *
+ * The first call on a device looks up the array's device address (once per device, with that device
+ * current); make that first call outside any stream capture. The entry point itself never calls
+ * cudaMalloc, cudaFree or any allocating library routine. All calls in the process share the one
+ * array, and it keeps what the previous call left: when groups > 1 this entry point clears the part
+ * it is about to accumulate into (two stream-ordered memsets) before the kernel; with groups == 1 the
+ * array is not touched. Two calls that can overlap on the GPU (different streams, no ordering between
+ * them) race on it: order them, or give one of them its own workspace through muse_skinny_tc. */
+#define MUSE_ERR_STATIC_SCRATCH (-20)
+long long muse_static_scratch_floats(void);
+int muse_static_scratch_tiles(void);
+int muse_skinny_tc_noalloc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, int* status, int m, int n,
+                           int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages, int out_is_f32,
+                           void* stream);
 
 /* Diagnostics: while `device_buffer` is non-NULL every CTA of the following muse_skinny_tc launches
  * writes 16 unsigned 64-bit phase stamps (SM cycle counter; slot 15 = global nanosecond timer at

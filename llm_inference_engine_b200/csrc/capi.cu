@@ -15,6 +15,11 @@ int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUt
 int skinny_stage_bytes(int ntok, int hilo);
 int skinny_smem_bytes(int ntok, int hilo, int stages, int cluster, int m);
 int skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster);
+int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out,
+                              int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
+                              int stages, int out_f32, cudaStream_t stream);
+long long skinny_static_ws_floats();
+int skinny_static_cnt_ints();
 void skinny_set_trace(unsigned long long* device_buffer);
 
 // cuTensorMapEncodeTiled is a driver entry point; fetching it through the runtime keeps the
@@ -131,6 +136,24 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
   if (tmap_w_lo) memcpy(&twlo, tmap_w_lo, sizeof(twlo));
   return muse::skinny_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
                                   cluster, groups, stages, out_is_f32, static_cast<cudaStream_t>(stream));
+}
+
+long long muse_static_scratch_floats(void) { return muse::skinny_static_ws_floats(); }
+int muse_static_scratch_tiles(void) { return muse::skinny_static_cnt_ints(); }
+
+int muse_skinny_tc_noalloc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, int* status, int m, int n,
+                           int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages, int out_is_f32,
+                           void* stream) {
+  if (!tmap_w || !x) return -1;
+  if (ld_x < k || ld_x % 8 != 0) return -2;
+  CUtensorMap tx;
+  const int r = muse::encode_2d(&tx, x, m, k, static_cast<long long>(ld_x) * 2, ntok);
+  if (r != 0) return r;
+  CUtensorMap tw, twlo;
+  memcpy(&tw, tmap_w, sizeof(tw));
+  if (tmap_w_lo) memcpy(&twlo, tmap_w_lo, sizeof(twlo));
+  return muse::skinny_tc_static_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, status, m, n, k, ld_out, ntok,
+                                         cluster, groups, stages, out_is_f32, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -587,4 +587,58 @@ int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUt
   return -7;
 }
 
+// ---------------------------------------------------------------- launch without any allocation
+//
+// Split-K scratch that lives in the library image instead of in memory the caller allocates:
+// STATIC_WS_FLOATS floats of partial sums followed by STATIC_CNT_INTS tile counters. Every GPU that
+// loads the library carries these 4 MiB + 16 KiB until the process exits.
+constexpr long long STATIC_WS_FLOATS = 1ll << 20;
+constexpr int STATIC_CNT_INTS = 4096;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_WS_FLOATS * 4 + STATIC_CNT_INTS * 4];
+
+long long skinny_static_ws_floats() { return STATIC_WS_FLOATS; }
+int skinny_static_cnt_ints() { return STATIC_CNT_INTS; }
+
+// In host code `g_static_scratch` is only a handle for the symbol, not an address a kernel can use.
+// The device address is looked up once per device, with that device current, and cached.
+static cudaError_t static_scratch_address(unsigned char** out) {
+  static unsigned char* addr[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    addr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = addr[dev];
+  return cudaSuccess;
+}
+
+// Same launch as skinny_tc_dispatch with the workspace and counters taken from g_static_scratch.
+// -20: the shape needs more scratch than the library carries. Calls nothing that allocates.
+int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out,
+                              int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
+                              int stages, int out_f32, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || ntok <= 0) return -1;
+  const long long tiles = static_cast<long long>((n + TILE_ROWS - 1) / TILE_ROWS) * ((m + ntok - 1) / ntok);
+  const long long floats = tiles * TILE_ROWS * ntok;
+  if (floats > STATIC_WS_FLOATS || tiles > STATIC_CNT_INTS) return -20;
+  unsigned char* base = nullptr;
+  cudaError_t e = static_scratch_address(&base);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  float* ws = reinterpret_cast<float*>(base);
+  int* cnt = reinterpret_cast<int*>(base + STATIC_WS_FLOATS * 4);
+  if (groups > 1) {
+    // The array keeps whatever the previous call (of anyone in this process) left. A completed call
+    // leaves zeros, an aborted one may not: clear exactly what this launch will accumulate into.
+    if ((e = cudaMemsetAsync(ws, 0, static_cast<size_t>(floats) * 4, stream)) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaMemsetAsync(cnt, 0, static_cast<size_t>(tiles) * 4, stream)) != cudaSuccess) return static_cast<int>(e);
+  }
+  return skinny_tc_dispatch(tw, twlo, tx, out, ws, cnt, status, m, n, k, ld_out, ntok, cluster, groups, stages, out_f32,
+                            stream);
+}
+
 }  // namespace muse
