@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 5
+#define MUSE_PROJ_ABI_VERSION 6
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -30,6 +30,27 @@ extern "C" {
 #define MUSE_ST_EPILOGUE_TIMEOUT 4
 #define MUSE_ST_X_TIMEOUT 8
 #define MUSE_ST_DRAIN_TIMEOUT 16
+#define MUSE_ST_PEER_ENTER_TIMEOUT 32
+#define MUSE_ST_PEER_DONE_TIMEOUT 64
+
+/* Column-parallel output exchange (optional last-but-one argument of muse_gemv1 / muse_skinny_tc;
+ * NULL or world <= 1 = single GPU). The weight is sharded by output rows over `world` GPUs of one
+ * node, one process per GPU. With this descriptor the kernel ignores its `out` argument and stores
+ * its [m, n] slice at columns [col0, col0 + n) of EVERY rank's gathered output out[p] (row stride
+ * ld_out, the same on all ranks) through peer-mapped pointers, then exchanges flags with the peers,
+ * so that when the kernel completes the local out[rank] holds every rank's slice: the all-gather
+ * is part of the kernel. out[p] and flags[p] are device pointers valid in THIS process (peer-mapped
+ * memory, e.g. torch symmetric memory or CUDA IPC); flags[p] is rank p's array of 32 ints, zero
+ * before the first call and owned by these kernels afterwards. All ranks must make the same sequence
+ * of calls. Waits on peers are bounded (status bits above). Plain peer stores only: no multimem,
+ * no TMA to or from peer memory. No counterpart in the reference, which runs on one GPU and leaves
+ * the all-gather out (bf16_proj/baseline.py:11). */
+#define MUSE_MAX_WORLD 8
+typedef struct muse_peer_sync {
+  int world, rank, col0, reserved;
+  void* out[MUSE_MAX_WORLD];
+  int* flags[MUSE_MAX_WORLD];
+} muse_peer_sync_t;
 
 /* ABI version of the loaded library (MUSE_PROJ_ABI_VERSION at build time). */
 int muse_abi_version(void);
@@ -48,7 +69,7 @@ int muse_query(int what);
  * Replaces gemv1_launch (bf16_proj/gemv1.cu:122-125; pybind wrapper
  * best_submissions/muse_bf16_proj.py:193-196). */
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,
-               int* status, void* stream);
+               int* status, const muse_peer_sync_t* peers, void* stream);
 
 /* Fill a 128-byte tensor map for a row-major BF16 matrix [rows, cols] at `base` (device pointer,
  * 16-byte aligned) with `row_stride_bytes` between rows (multiple of 16), delivering boxes of
@@ -90,7 +111,7 @@ int muse_skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster)
  * _router_kernel (:310-320, :260-287), _finish (:215-233) and the cuBLAS call for m > 32 (:390). */
 int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
                    int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
-                   int out_is_f32, void* stream);
+                   int out_is_f32, const muse_peer_sync_t* peers, void* stream);
 
 /* muse_skinny_tc for callers that must not allocate device memory. No counterpart in the reference.
  *

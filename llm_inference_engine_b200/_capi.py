@@ -18,14 +18,14 @@ SIGNATURES = {
     "muse_abi_version": (C.c_int, []),
     "muse_query": (C.c_int, [C.c_int]),
     "muse_gemv1": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                             C.c_void_p, C.c_void_p]),
+                             C.c_void_p, C.c_void_p, C.c_void_p]),
     "muse_tmap_encode_2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong, C.c_int]),
     "muse_skinny_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "muse_skinny_tiles": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "muse_skinny_stage_bytes": (C.c_int, [C.c_int, C.c_int]),
     "muse_skinny_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                 C.c_void_p]),
+                                 C.c_void_p, C.c_void_p]),
     "muse_skinny_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_skinny_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_nop": (C.c_int, [C.c_void_p]),
@@ -37,7 +37,7 @@ SIGNATURES = {
     "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 class MuseError(RuntimeError):
@@ -73,6 +73,16 @@ def check(rc: int, what: str) -> None:
     if rc != 0:
         kind = "rejected argument" if rc < 0 else "CUDA error"
         raise MuseError(f"{what}: {kind} {rc}")
+
+
+MAX_WORLD = 8
+
+
+class PeerSync(C.Structure):
+    """muse_peer_sync_t: where a column-parallel kernel writes its slice on every rank (muse_proj.h)."""
+
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("col0", C.c_int), ("reserved", C.c_int),
+                ("out", C.c_void_p * MAX_WORLD), ("flags", C.c_void_p * MAX_WORLD)]
 
 
 class TensorMap:

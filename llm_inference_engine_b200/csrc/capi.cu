@@ -8,10 +8,10 @@
 
 namespace muse {
 int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
-                   int persistent, int* status, cudaStream_t stream);
+                   int persistent, int* status, const PeerSync* peers, cudaStream_t stream);
 int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                        int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
-                       int stages, int out_f32, cudaStream_t stream);
+                       int stages, int out_f32, const PeerSync* peers, cudaStream_t stream);
 int skinny_stage_bytes(int ntok, int hilo);
 int skinny_smem_bytes(int ntok, int hilo, int stages, int cluster, int m);
 int skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster);
@@ -83,10 +83,12 @@ int muse_query(int what) {
   return e == cudaSuccess ? v : -1;
 }
 
+static_assert(sizeof(muse_peer_sync_t) == sizeof(muse::PeerSync), "muse_peer_sync_t must mirror PeerSync");
+
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,
-               int* status, void* stream) {
+               int* status, const muse_peer_sync_t* peers, void* stream) {
   return muse::gemv1_dispatch(W, x, out, N, K, w_is_f32, wpr, unroll, persistent, status,
-                              static_cast<cudaStream_t>(stream));
+                              reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 
 int muse_tmap_encode_2d(void* tmap_out128, const void* base, long long rows, long long cols,
@@ -123,7 +125,7 @@ int muse_skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster)
 
 int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
                    int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
-                   int out_is_f32, void* stream) {
+                   int out_is_f32, const muse_peer_sync_t* peers, void* stream) {
   if (!tmap_w || !x) return -1;
   if (ld_x < k || ld_x % 8 != 0) return -2;
   // x moves between calls (a fresh activation tensor each time), so its map is encoded per call; the
@@ -135,7 +137,8 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
   memcpy(&tw, tmap_w, sizeof(tw));
   if (tmap_w_lo) memcpy(&twlo, tmap_w_lo, sizeof(twlo));
   return muse::skinny_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
-                                  cluster, groups, stages, out_is_f32, static_cast<cudaStream_t>(stream));
+                                  cluster, groups, stages, out_is_f32, reinterpret_cast<const muse::PeerSync*>(peers),
+                                  static_cast<cudaStream_t>(stream));
 }
 
 long long muse_static_scratch_floats(void) { return muse::skinny_static_ws_floats(); }

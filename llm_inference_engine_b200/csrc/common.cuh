@@ -201,4 +201,110 @@ __device__ __forceinline__ void red_add_f32(float* p, float v) {
 __device__ __forceinline__ float bf16lo_f32(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi_f32(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
+// ---------------------------------------------------------------- column-parallel output exchange
+//
+// With the weight sharded by output rows over `world` GPUs (one process each), a kernel writes its
+// [m, n] slice straight into the [m, N] output of EVERY rank (plain stores through peer-mapped
+// pointers over NVLink; no multimem, no TMA to or from peer memory), at column `col0`, so the
+// all-gather is part of the kernel. Two rounds of flags, living in a small peer-mapped int array per
+// rank, order it against the neighbours:
+//   enter[r]   written to every peer when rank r's kernel of call e starts. A rank stores into a
+//              peer only after that peer has entered call e: the peer's consumers of call e-1's
+//              output ran earlier on its stream. The wait sits in the epilogue, long after the flag
+//              was raised, and normally returns at once.
+//   done[r]    written to every peer by rank r's last CTA after all its stores (system-scope fence).
+//              The same CTA then waits for every peer's done[.] >= e, so when the kernel completes
+//              the local [m, N] holds every rank's slice.
+// Layout of a rank's flag array (int32): [0, 8) enter, [8, 16) done, [16] epoch of the last finished
+// call, [17] CTA arrival counter. All waits are bounded and report through the status word.
+constexpr int MAX_WORLD = 8;
+enum : int { ST_PEER_ENTER_TIMEOUT = 32, ST_PEER_DONE_TIMEOUT = 64 };
+
+struct PeerSync {
+  int world;   // 0 or 1: single GPU, nothing below is used
+  int rank;
+  int col0;    // first output column of this rank's slice in the gathered [m, N]
+  int pad_;
+  void* out[MAX_WORLD];    // every rank's gathered output (same shape and row stride everywhere)
+  int* flags[MAX_WORLD];   // every rank's flag array
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_volatile_s32(const int* p) {
+  int v;
+  asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool peer_active(const PeerSync& ps) { return ps.world > 1; }
+// The call number this launch represents (every rank makes the same sequence of calls). The word was
+// written by this GPU's previous kernel, so a plain load sees it. ONE thread per CTA reads it and
+// hands it to the others through shared memory: system-scope operations are kept to a handful per CTA.
+__device__ __forceinline__ int peer_epoch(const PeerSync& ps) { return ld_volatile_s32(ps.flags[ps.rank] + 16) + 1; }
+// One thread of the grid: tell every peer that this rank has entered call `e`.
+__device__ __forceinline__ void peer_announce_enter(const PeerSync& ps, int e) {
+  for (int p = 0; p < ps.world; ++p) st_release_sys(ps.flags[p] + ps.rank, e);
+}
+__device__ __forceinline__ bool peer_wait_flag(const int* flag, int e) {
+  if (ld_acquire_sys(flag) >= e) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (ld_volatile_s32(flag) >= e) return ld_acquire_sys(flag) >= e;
+    if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
+}
+// All threads of a CTA, before its first store to a peer: threads 0..world-1 each wait for one peer
+// to have entered call `e` (one acquire per peer per CTA), then the CTA synchronises.
+__device__ __forceinline__ void peer_wait_all_entered(const PeerSync& ps, int e, int* status) {
+  if (threadIdx.x < ps.world && !peer_wait_flag(ps.flags[ps.rank] + threadIdx.x, e))
+    atomicOr(status, ST_PEER_ENTER_TIMEOUT);
+  __syncthreads();
+}
+// All threads of every CTA call this after their last store (to peers or to the local output).
+// `s_flag` is a shared int. A CTA orders its stores before its arrival with a GPU-scope fence;
+// returns true (CTA-uniform) in the last CTA to arrive, which is then ordered after every other
+// CTA's stores.
+__device__ __forceinline__ bool peer_last_cta(const PeerSync& ps, int total_ctas, int* s_flag) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int last = atomicAdd(ps.flags[ps.rank] + 17, 1) == total_ctas - 1;
+    if (last) __threadfence();
+    *s_flag = last;
+  }
+  __syncthreads();
+  return *s_flag != 0;
+}
+// All threads of the last CTA, after any stores of its own: one system-scope fence, then done[rank]
+// goes to every peer (release/acquire chains are cumulative across scopes, so the peers see every
+// CTA's stores), then wait for every peer's done flag: the kernel completes only when the local
+// gathered output is complete. Finally the epoch advances and the arrival counter is reset.
+__device__ __forceinline__ void peer_publish(const PeerSync& ps, int e, int* status) {
+  int* mine = ps.flags[ps.rank];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mine[17] = 0;
+    __threadfence_system();
+    for (int p = 0; p < ps.world; ++p) st_release_sys(ps.flags[p] + 8 + ps.rank, e);
+  }
+  if (threadIdx.x < ps.world && !peer_wait_flag(mine + 8 + threadIdx.x, e)) atomicOr(status, ST_PEER_DONE_TIMEOUT);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mine[16] = e;
+    __threadfence();
+  }
+}
+__device__ __forceinline__ void peer_finish(const PeerSync& ps, int e, int total_ctas, int* status, int* s_flag) {
+  if (peer_last_cta(ps, total_ctas, s_flag)) peer_publish(ps, e, status);
+}
+
 }  // namespace muse

@@ -23,15 +23,53 @@ __device__ __forceinline__ void load_batch(uint4 (&w)[U], const uint4* wp, int v
   }
 }
 
+// One output feature goes to the caller's `out`, or, column-parallel, to column col0 + row of this
+// rank's OWN gathered output; the grid's last CTA then ships the whole slice to the peers.
+template <bool F32W>
+__device__ __forceinline__ void store_row(const PeerSync& ps, void* out, int row, float acc) {
+  void* dst = peer_active(ps) ? ps.out[ps.rank] : out;
+  const int col = peer_active(ps) ? ps.col0 + row : row;
+  if constexpr (F32W) reinterpret_cast<float*>(dst)[col] = acc;
+  else reinterpret_cast<__nv_bfloat16*>(dst)[col] = __float2bfloat16_rn(acc);
+}
+
+// All threads of every CTA, after their rows are stored locally. The last CTA copies this rank's
+// [col0, col0 + N) slice to every peer in 16-byte vectors (a few KB over NVLink instead of one tiny
+// remote store per row) once all peers have entered the call, then publishes and waits.
+template <bool F32W>
+__device__ __forceinline__ void gemv_peer_finish(const PeerSync& ps, int e, int N, int* status, int* s_flag) {
+  if (!peer_last_cta(ps, static_cast<int>(gridDim.x), s_flag)) return;
+  peer_wait_all_entered(ps, e, status);
+  constexpr int ES = F32W ? 4 : 2;
+  const char* src = reinterpret_cast<const char*>(ps.out[ps.rank]) + static_cast<size_t>(ps.col0) * ES;
+  const int bytes = N * ES;
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) | static_cast<unsigned>(bytes)) & 15) == 0;
+  for (int p = 0; p < ps.world; ++p) {
+    if (p == ps.rank) continue;
+    char* dst = reinterpret_cast<char*>(ps.out[p]) + static_cast<size_t>(ps.col0) * ES;
+    if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      for (int i = threadIdx.x * 16; i < bytes; i += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(dst + i) = __ldcg(reinterpret_cast<const uint4*>(src + i));
+    } else {
+      for (int i = threadIdx.x * 2; i < bytes; i += blockDim.x * 2)
+        *reinterpret_cast<unsigned short*>(dst + i) = __ldcg(reinterpret_cast<const unsigned short*>(src + i));
+    }
+  }
+  peer_publish(ps, e, status);
+}
+
 template <int WPR, int U, bool F32W>
 __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, const __nv_bfloat16* __restrict__ x,
-                                                    void* __restrict__ out, int N, int K, int* __restrict__ status) {
+                                                    void* __restrict__ out, int N, int K, int* __restrict__ status,
+                                                    const __grid_constant__ PeerSync ps) {
   constexpr int RPC = 8 / WPR;        // rows per CTA
   constexpr int EPV = F32W ? 4 : 8;   // weights per 16-byte vector
   constexpr int WB = F32W ? 4 : 2;    // bytes per weight
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t xbar;
   __shared__ float part[8];
+  __shared__ int s_last;
+  __shared__ int s_epoch;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * RPC + warp / WPR;
@@ -45,6 +83,10 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
     fence_mbar_init();
     mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u);
     bulk_load_1d(smem_u32(smem), x, static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
+    if (peer_active(ps)) {
+      s_epoch = peer_epoch(ps);
+      if (blockIdx.x == 0) peer_announce_enter(ps, s_epoch);
+    }
   }
 
   const uint4* wp = reinterpret_cast<const uint4*>(
@@ -100,10 +142,8 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
       for (int s = 1; s < WPR; ++s) acc += part[warp + s];
     }
   }
-  if (live && lane == 0 && seg == 0) {
-    if constexpr (F32W) reinterpret_cast<float*>(out)[row] = acc;
-    else reinterpret_cast<__nv_bfloat16*>(out)[row] = __float2bfloat16_rn(acc);
-  }
+  if (live && lane == 0 && seg == 0) store_row<F32W>(ps, out, row, acc);
+  if (peer_active(ps)) gemv_peer_finish<F32W>(ps, s_epoch, N, status, &s_last);
 }
 
 // Whole-row variant for tall weights: a persistent grid (every CTA resident at once), warp g of the
@@ -112,9 +152,12 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
 // every SM ends up with the same number of rows to within one, so the grid drains together.
 template <int U, bool F32W>
 __global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict__ W, const __nv_bfloat16* __restrict__ x,
-                                                         void* __restrict__ out, int N, int K, int* __restrict__ status) {
+                                                         void* __restrict__ out, int N, int K, int* __restrict__ status,
+                                                         const __grid_constant__ PeerSync ps) {
   constexpr int EPV = F32W ? 4 : 8;
   constexpr int WB = F32W ? 4 : 2;
+  __shared__ int s_last;
+  __shared__ int s_epoch;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t xbar;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -130,6 +173,10 @@ __global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict_
     fence_mbar_init();
     mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u);
     bulk_load_1d(smem_u32(smem), x, static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
+    if (peer_active(ps)) {
+      s_epoch = peer_epoch(ps);
+      if (blockIdx.x == 0) peer_announce_enter(ps, s_epoch);
+    }
   }
   auto row_ptr = [&](int r) {
     return reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(W) +
@@ -175,11 +222,7 @@ __global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict_
       float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane == 0) {
-        const int row = gw + r * total_warps;
-        if constexpr (F32W) reinterpret_cast<float*>(out)[row] = acc;
-        else reinterpret_cast<__nv_bfloat16*>(out)[row] = __float2bfloat16_rn(acc);
-      }
+      if (lane == 0) store_row<F32W>(ps, out, gw + r * total_warps, acc);
       a0 = a1 = a2 = a3 = 0.f;
     }
 #pragma unroll
@@ -187,10 +230,12 @@ __global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict_
     r = rn;
     b = bn;
   }
+  if (peer_active(ps)) gemv_peer_finish<F32W>(ps, s_epoch, N, status, &s_last);
 }
 
 template <int U, bool F32W>
-static cudaError_t launch_rows(const void* W, const void* x, void* out, int N, int K, int* status, cudaStream_t s) {
+static cudaError_t launch_rows(const void* W, const void* x, void* out, int N, int K, int* status, const PeerSync& ps,
+                               cudaStream_t s) {
   auto kern = gemv1_rows_kernel<U, F32W>;
   static int per_sm[64] = {0}, sms[64] = {0};
   int dev = 0;
@@ -213,23 +258,24 @@ static cudaError_t launch_rows(const void* W, const void* x, void* out, int N, i
   int grid = sms[dev] * resident;
   const int need = (N + 7) / 8;
   if (grid > need) grid = need;
-  kern<<<grid, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status);
+  kern<<<grid, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
   return cudaGetLastError();
 }
 
 template <bool F32W>
-static cudaError_t pick_rows(const void* W, const void* x, void* out, int N, int K, int u, int* st, cudaStream_t s) {
+static cudaError_t pick_rows(const void* W, const void* x, void* out, int N, int K, int u, int* st, const PeerSync& ps, cudaStream_t s) {
   switch (u) {
-    case 1: return launch_rows<1, F32W>(W, x, out, N, K, st, s);
-    case 2: return launch_rows<2, F32W>(W, x, out, N, K, st, s);
-    case 4: return launch_rows<4, F32W>(W, x, out, N, K, st, s);
-    case 8: return launch_rows<8, F32W>(W, x, out, N, K, st, s);
+    case 1: return launch_rows<1, F32W>(W, x, out, N, K, st, ps, s);
+    case 2: return launch_rows<2, F32W>(W, x, out, N, K, st, ps, s);
+    case 4: return launch_rows<4, F32W>(W, x, out, N, K, st, ps, s);
+    case 8: return launch_rows<8, F32W>(W, x, out, N, K, st, ps, s);
   }
   return cudaErrorInvalidValue;
 }
 
 template <int WPR, int U, bool F32W>
-static cudaError_t launch(const void* W, const void* x, void* out, int N, int K, int* status, cudaStream_t s) {
+static cudaError_t launch(const void* W, const void* x, void* out, int N, int K, int* status, const PeerSync& ps,
+                          cudaStream_t s) {
   constexpr int RPC = 8 / WPR;
   const int smem = K * 2;
   auto kern = gemv1_kernel<WPR, U, F32W>;
@@ -237,36 +283,44 @@ static cudaError_t launch(const void* W, const void* x, void* out, int N, int K,
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
   }
-  kern<<<(N + RPC - 1) / RPC, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status);
+  kern<<<(N + RPC - 1) / RPC, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
   return cudaGetLastError();
 }
 
 template <int WPR, bool F32W>
-static cudaError_t pick_u(const void* W, const void* x, void* out, int N, int K, int u, int* st, cudaStream_t s) {
+static cudaError_t pick_u(const void* W, const void* x, void* out, int N, int K, int u, int* st, const PeerSync& ps, cudaStream_t s) {
   switch (u) {
-    case 1: return launch<WPR, 1, F32W>(W, x, out, N, K, st, s);
-    case 2: return launch<WPR, 2, F32W>(W, x, out, N, K, st, s);
-    case 4: return launch<WPR, 4, F32W>(W, x, out, N, K, st, s);
-    case 8: return launch<WPR, 8, F32W>(W, x, out, N, K, st, s);
+    case 1: return launch<WPR, 1, F32W>(W, x, out, N, K, st, ps, s);
+    case 2: return launch<WPR, 2, F32W>(W, x, out, N, K, st, ps, s);
+    case 4: return launch<WPR, 4, F32W>(W, x, out, N, K, st, ps, s);
+    case 8: return launch<WPR, 8, F32W>(W, x, out, N, K, st, ps, s);
   }
   return cudaErrorInvalidValue;
 }
 
 template <bool F32W>
 static cudaError_t pick_wpr(const void* W, const void* x, void* out, int N, int K, int wpr, int u, int* st,
-                            cudaStream_t s) {
+                            const PeerSync& ps, cudaStream_t s) {
   switch (wpr) {
-    case 1: return pick_u<1, F32W>(W, x, out, N, K, u, st, s);
-    case 2: return pick_u<2, F32W>(W, x, out, N, K, u, st, s);
-    case 4: return pick_u<4, F32W>(W, x, out, N, K, u, st, s);
-    case 8: return pick_u<8, F32W>(W, x, out, N, K, u, st, s);
+    case 1: return pick_u<1, F32W>(W, x, out, N, K, u, st, ps, s);
+    case 2: return pick_u<2, F32W>(W, x, out, N, K, u, st, ps, s);
+    case 4: return pick_u<4, F32W>(W, x, out, N, K, u, st, ps, s);
+    case 8: return pick_u<8, F32W>(W, x, out, N, K, u, st, ps, s);
   }
   return cudaErrorInvalidValue;
 }
 
 // Argument checks live here so that the C-ABI wrapper stays a one-liner. Negative = argument error.
 int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
-                   int persistent, int* status, cudaStream_t stream) {
+                   int persistent, int* status, const PeerSync* peers, cudaStream_t stream) {
+  PeerSync ps = {};
+  if (peers && peers->world > 1) {
+    ps = *peers;
+    if (ps.world > MAX_WORLD || ps.rank < 0 || ps.rank >= ps.world || ps.col0 < 0) return -8;
+    for (int p = 0; p < ps.world; ++p)
+      if (!ps.out[p] || !ps.flags[p]) return -8;
+    out = ps.out[ps.rank];
+  }
   if (!W || !x || !out || !status || N <= 0 || K <= 0) return -1;
   const int epv = w_is_f32 ? 4 : 8;
   if (K % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
@@ -275,11 +329,11 @@ int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_
   if (K * 2 > 200 * 1024) return -5;
   if (persistent) {
     if (wpr != 1) return -6;  // whole rows per warp only
-    return static_cast<int>(w_is_f32 ? pick_rows<true>(W, x, out, N, K, unroll, status, stream)
-                                     : pick_rows<false>(W, x, out, N, K, unroll, status, stream));
+    return static_cast<int>(w_is_f32 ? pick_rows<true>(W, x, out, N, K, unroll, status, ps, stream)
+                                     : pick_rows<false>(W, x, out, N, K, unroll, status, ps, stream));
   }
-  const cudaError_t e = w_is_f32 ? pick_wpr<true>(W, x, out, N, K, wpr, unroll, status, stream)
-                                 : pick_wpr<false>(W, x, out, N, K, wpr, unroll, status, stream);
+  const cudaError_t e = w_is_f32 ? pick_wpr<true>(W, x, out, N, K, wpr, unroll, status, ps, stream)
+                                 : pick_wpr<false>(W, x, out, N, K, wpr, unroll, status, ps, stream);
   return static_cast<int>(e);
 }
 

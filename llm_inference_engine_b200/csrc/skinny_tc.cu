@@ -90,12 +90,13 @@ __device__ __forceinline__ void stg_cg_f32x4(float* p, float4 v) {
 }
 
 // Eight consecutive output features of one token, starting at feature n0 (a multiple of 8).
+// `col0` shifts the destination column (this rank's slice inside a gathered output); bounds use n0 < n.
 __device__ __forceinline__ void store_out8(void* out, int out_f32, bool vec_ok, size_t token, int ld_out, int n0, int n,
-                                           const float4& lo, const float4& hi) {
+                                           int col0, const float4& lo, const float4& hi) {
   if (n0 >= n) return;
   const float a[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
   if (out_f32) {
-    float* o = reinterpret_cast<float*>(out) + token * ld_out + n0;
+    float* o = reinterpret_cast<float*>(out) + token * ld_out + col0 + n0;
     if (vec_ok && n0 + 8 <= n) {
       *reinterpret_cast<float4*>(o) = lo;
       *reinterpret_cast<float4*>(o + 4) = hi;
@@ -105,7 +106,7 @@ __device__ __forceinline__ void store_out8(void* out, int out_f32, bool vec_ok, 
         if (n0 + i < n) o[i] = a[i];
     }
   } else {
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + token * ld_out + n0;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + token * ld_out + col0 + n0;
     if (vec_ok && n0 + 8 <= n) {
       __nv_bfloat162 p0 = __floats2bfloat162_rn(a[0], a[1]), p1 = __floats2bfloat162_rn(a[2], a[3]);
       __nv_bfloat162 p2 = __floats2bfloat162_rn(a[4], a[5]), p3 = __floats2bfloat162_rn(a[6], a[7]);
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(128)
 skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wlo,
                  const __grid_constant__ CUtensorMap tm_x, void* __restrict__ out, float* __restrict__ ws,
                  int* __restrict__ cnt, int* __restrict__ status, int m, int n, int chunks, int split, int stages,
-                 int out_f32, int ld_out, unsigned long long* __restrict__ trace) {
+                 int out_f32, int ld_out, unsigned long long* __restrict__ trace, const __grid_constant__ PeerSync ps) {
   using Cfg = SkinnyCfg<NTOK, HILO>;
   // Optional per-CTA phase stamps (SM cycle counter; slot 15 / 11 = global nanosecond timer at entry / exit).
   unsigned long long* const tr =
@@ -147,6 +148,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   __shared__ volatile int s_abort;
   __shared__ int s_last;
   __shared__ int s_issued;
+  __shared__ int s_epoch;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile_n = blockIdx.x, tile_m = blockIdx.z;
@@ -189,6 +191,10 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     for (int i = 0; i < pre; ++i) issue(i, i);
     s_abort = 0;
     s_issued = 0;
+    if (peer_active(ps)) {
+      s_epoch = peer_epoch(ps);
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) peer_announce_enter(ps, s_epoch);
+    }
     MUSE_STAMP(1);
   }
 
@@ -297,17 +303,30 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
   // Workspace of a tile: [row][NTOK tokens], so that four tokens of a row are one 16-byte vector.
   float* const ws_row = ws + static_cast<size_t>(tile_id) * (TILE_ROWS * NTOK) + static_cast<size_t>(r) * NTOK;
+  // Destinations: the caller's `out`, or every rank's gathered output (this rank's columns start at col0).
+  const int ndst = peer_active(ps) ? ps.world : 1;
+  const int col0 = peer_active(ps) ? ps.col0 : 0;
+  int pe = 0;
+  if (peer_active(ps)) {
+    // No store may reach a peer that has not entered this call: its previous output may still be in use.
+    pe = s_epoch;
+    peer_wait_all_entered(ps, pe, status);
+  }
+  auto dst = [&](int d) -> void* { return peer_active(ps) ? ps.out[d] : out; };
   auto store_tok = [&](int j, float f) {
     if (row_ok && j < mvalid) {
-      const size_t o = static_cast<size_t>(tok0 + j) * ld_out + n_idx;
-      if (out_f32) reinterpret_cast<float*>(out)[o] = f;
-      else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(f);
+      const size_t o = static_cast<size_t>(tok0 + j) * ld_out + col0 + n_idx;
+      for (int d = 0; d < ndst; ++d) {
+        if (out_f32) reinterpret_cast<float*>(dst(d))[o] = f;
+        else reinterpret_cast<__nv_bfloat16*>(dst(d))[o] = __float2bfloat16_rn(f);
+      }
     }
   };
 
   // Staging area for vector stores: [token][128 rows] FP32 over the ring, which is idle once bar_acc fired.
   float* const stage = reinterpret_cast<float*>(smem_raw + (smem_base - smem_u32(smem_raw)));
-  const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_out % (out_f32 ? 4 : 8) == 0;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(dst(0)) & 15) == 0 && ld_out % (out_f32 ? 4 : 8) == 0 &&
+                      col0 % (out_f32 ? 4 : 8) == 0;
   // All threads: tokens [first, first + cnt) of the tile wait in `stage`; write them as 8-feature vectors.
   auto staged_store = [&](int first, int cnt) {
     __syncthreads();
@@ -318,7 +337,9 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       const float4 lo = *reinterpret_cast<const float4*>(stage + t * TILE_ROWS + g8 * 8);
       const float4 hi = *reinterpret_cast<const float4*>(stage + t * TILE_ROWS + g8 * 8 + 4);
       if (first + t < mvalid)
-        store_out8(out, out_f32, vec_ok, static_cast<size_t>(tok0 + first + t), ld_out, tile_n * TILE_ROWS + g8 * 8, n, lo, hi);
+        for (int d = 0; d < ndst; ++d)
+          store_out8(dst(d), out_f32, vec_ok, static_cast<size_t>(tok0 + first + t), ld_out, tile_n * TILE_ROWS + g8 * 8, n,
+                     col0, lo, hi);
     }
   };
 
@@ -436,6 +457,9 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     }
   }
 
+  // Column-parallel: publish "this rank's slice is everywhere" and wait for the same from every peer.
+  if (peer_active(ps)) peer_finish(ps, pe, static_cast<int>(gridDim.x * gridDim.y * gridDim.z), status, &s_last);
+
   // ---- teardown
   if (tid == 0) MUSE_STAMP(9);
   tc_fence_before_sync();
@@ -512,7 +536,7 @@ static void fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int 
 template <int NTOK, bool HILO>
 static cudaError_t launch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                           int* cnt, int* status, int m, int n, int chunks, int cluster, int groups, int stages,
-                          int out_f32, int ld_out, cudaStream_t stream) {
+                          int out_f32, int ld_out, const PeerSync& ps, cudaStream_t stream) {
   int dev = 0, room = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
@@ -523,7 +547,7 @@ static cudaError_t launch(const CUtensorMap* tw, const CUtensorMap* twlo, const 
   cudaLaunchAttribute attr[1];
   fill_config<NTOK, HILO>(&cfg, attr, m, n, cluster, groups, smem, stream);
   return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<NTOK, HILO>, *tw, HILO ? *twlo : *tw, *tx, out, ws, cnt, status, m, n,
-                            chunks, cluster * groups, stages, out_f32, ld_out, g_trace);
+                            chunks, cluster * groups, stages, out_f32, ld_out, g_trace, ps);
 }
 
 // How many clusters of this shape the device can hold at once (0 = the shape cannot launch).
@@ -568,7 +592,15 @@ int skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster) {
 // Negative = argument error, positive = cudaError_t, 0 = launched.
 int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                        int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
-                       int stages, int out_f32, cudaStream_t stream) {
+                       int stages, int out_f32, const PeerSync* peers, cudaStream_t stream) {
+  PeerSync ps = {};
+  if (peers && peers->world > 1) {
+    ps = *peers;
+    if (ps.world > MAX_WORLD || ps.rank < 0 || ps.rank >= ps.world || ps.col0 < 0) return -8;
+    for (int p = 0; p < ps.world; ++p)
+      if (!ps.out[p] || !ps.flags[p]) return -8;
+    out = ps.out[ps.rank];
+  }
   if (!tw || !tx || !out || !status || m <= 0 || n <= 0 || k <= 0) return -1;
   if (k % 8 != 0) return -2;
   const int chunks = (k + BK - 1) / BK;
@@ -577,10 +609,10 @@ int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUt
   if (split > chunks || split > 65535 || chunks > 65535) return -3;
   if (groups > 1 && (!ws || !cnt)) return -4;
   if (stages < 1 || stages > MAX_STAGES) return -5;
-  if (ld_out < n) return -6;
+  if (ld_out < n + ps.col0) return -6;
   const bool hilo = twlo != nullptr;
-#define L_T(NT) static_cast<int>(launch<NT, true>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups, stages, out_f32, ld_out, stream))
-#define L_F(NT) static_cast<int>(launch<NT, false>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups, stages, out_f32, ld_out, stream))
+#define L_T(NT) static_cast<int>(launch<NT, true>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups, stages, out_f32, ld_out, ps, stream))
+#define L_F(NT) static_cast<int>(launch<NT, false>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups, stages, out_f32, ld_out, ps, stream))
   MUSE_FOR_NTOK(ntok, hilo, L_T, L_F)
 #undef L_T
 #undef L_F
@@ -638,7 +670,7 @@ int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, co
     if ((e = cudaMemsetAsync(cnt, 0, static_cast<size_t>(tiles) * 4, stream)) != cudaSuccess) return static_cast<int>(e);
   }
   return skinny_tc_dispatch(tw, twlo, tx, out, ws, cnt, status, m, n, k, ld_out, ntok, cluster, groups, stages, out_f32,
-                            stream);
+                            nullptr, stream);
 }
 
 }  // namespace muse

@@ -20,6 +20,8 @@ from __future__ import annotations
 
 from typing import TypedDict
 
+import ctypes
+
 import torch
 
 from . import _capi
@@ -116,6 +118,10 @@ def prepare(weights: dict[str, torch.Tensor], warmup: bool = True):
     return state
 
 
+def _peer_ptr(peers):
+    return None if peers is None else ctypes.addressof(peers)
+
+
 def check_status(state) -> None:
     """Synchronise and raise if any kernel since the last check gave up on one of its bounded waits.
     Not for use inside a stream capture."""
@@ -160,9 +166,12 @@ def plan_for(state, layer: str, m: int, n: int, k: int) -> GemvPlan | SkinnyPlan
     return plan
 
 
-def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Tensor:
+def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None, peers=None) -> torch.Tensor:
     """x @ W[:n].T as a new tensor: BF16, or FP32 for the router. `out` (optional, beyond the
-    reference's signature) is a preallocated [m, >= n] destination whose row stride is honoured."""
+    reference's signature) is a preallocated [m, >= n] destination whose row stride is honoured.
+    `peers` (optional, column-parallel use: see tp.FusedColumnParallel) is a ctypes muse_peer_sync_t:
+    the kernel then writes its slice into every rank's gathered output and `out` must be this
+    rank's gathered [m, N] tensor, which is returned."""
     x, cfg = data["x"], data["config"]
     layer, n = cfg["layer"], int(cfg["n"])
     if layer not in state or layer.startswith("_"):
@@ -179,7 +188,7 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Ten
     f32 = layer in FP32_LAYERS
     if out is None:
         out = torch.empty((m, n), device=x.device, dtype=torch.float32 if f32 else torch.bfloat16)
-    elif out.shape[0] != m or out.shape[1] < n or out.stride(1) != 1 or out.dtype != (torch.float32 if f32 else torch.bfloat16):
+    elif out.shape[0] != m or out.shape[1] < n + (peers.col0 if peers is not None else 0) or out.stride(1) != 1 or out.dtype != (torch.float32 if f32 else torch.bfloat16):
         raise ValueError("out must be [m, >= n], unit column stride, BF16 (FP32 for the router)")
     lib = state.get("_lib") or _capi.load()
     stream = torch.cuda.current_stream(x.device).cuda_stream
@@ -187,7 +196,7 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Ten
     status = state["_status"].data_ptr()
     if isinstance(plan, GemvPlan):
         _capi.check(lib.muse_gemv1(w.data_ptr(), x.data_ptr(), out.data_ptr(), n, k, int(f32), plan.wpr, plan.unroll,
-                                   int(plan.persistent), status, stream), f"muse_gemv1({layer}, n={n}, k={k})")
+                                   int(plan.persistent), status, _peer_ptr(peers), stream), f"muse_gemv1({layer}, n={n}, k={k})")
         return out
     maps = _weight_maps(state, layer, n)
     ws_ptr = cnt_ptr = None
@@ -196,6 +205,6 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Ten
         ws_ptr, cnt_ptr = ws.data_ptr(), cnt.data_ptr()
     _capi.check(lib.muse_skinny_tc(maps[0].ptr, maps[1].ptr if f32 else None, x.data_ptr(), out.data_ptr(), ws_ptr,
                                    cnt_ptr, status, m, n, k, x.stride(0) if m > 1 else k, out.stride(0), plan.ntok,
-                                   plan.cluster, plan.groups, plan.stages, int(f32), stream),
+                                   plan.cluster, plan.groups, plan.stages, int(f32), _peer_ptr(peers), stream),
                 f"muse_skinny_tc({layer}, m={m}, n={n}, k={k}, {plan})")
     return out

@@ -80,3 +80,79 @@ class ColumnParallelProjection:
 
     def kernel_fn(self, data: dict, state) -> torch.Tensor:
         return self.gather(self.kernel_fn_local(data, state))
+
+
+class FusedColumnParallel(ColumnParallelProjection):
+    """Column-parallel projections whose all-gather is part of the kernel (GPUs of one node).
+
+    Every rank owns, per layer, a gathered output buffer [max_tokens, N] in symmetric (peer-mapped)
+    memory. A call runs the single-GPU kernel with a muse_peer_sync_t descriptor: the epilogue stores
+    this rank's [m, N / world] slice at its columns of EVERY rank's buffer with plain stores over
+    NVLink, and two rounds of peer-mapped flags (entered / done) order the ranks, so when the kernel
+    completes the local buffer holds the whole [m, N]: no NCCL call, no re-layout copy.
+
+    The returned tensor is a view of that buffer; it is overwritten by the layer's next call, so
+    consume it in stream order before calling the layer again (every rank must make the same
+    sequence of calls). `torch.distributed._symmetric_memory` provides the peer mapping.
+    """
+
+    def __init__(self, local_prepare: Callable, local_kernel_fn: Callable, group=None, max_tokens: int = 256):
+        super().__init__(local_prepare, local_kernel_fn, group)
+        from . import _capi
+
+        if self.world > _capi.MAX_WORLD:
+            raise ValueError(f"world {self.world} > {_capi.MAX_WORLD}")
+        self.max_tokens = max_tokens
+        self._capi = _capi
+        self._bufs: dict[str, torch.Tensor] = {}
+        self._peers: dict[str, object] = {}
+        self._handles: list = []
+        self._flags = None
+        self._flag_ptrs = None
+
+    def _rendezvous(self, t: torch.Tensor):
+        import torch.distributed._symmetric_memory as symm
+
+        hdl = symm.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+        self._handles.append(hdl)
+        off = int(getattr(hdl, "offset", 0) or 0)
+        return [int(p) + off for p in hdl.buffer_ptrs]
+
+    def _symm_empty(self, shape, dtype, device):
+        import torch.distributed._symmetric_memory as symm
+
+        return symm.empty(shape, dtype=dtype, device=device)
+
+    def _ensure_layer(self, name: str, rows: int, dtype: torch.dtype, device) -> None:
+        if name in self._bufs:
+            return
+        if self._flags is None:
+            self._flags = self._symm_empty((32,), torch.int32, device)
+            self._flags.zero_()
+            self._flag_ptrs = self._rendezvous(self._flags)
+        buf = self._symm_empty((self.max_tokens, rows), dtype, device)
+        ptrs = self._rendezvous(buf)
+        ps = self._capi.PeerSync()
+        ps.world, ps.rank, ps.col0 = self.world, self.rank, self.rank * (rows // self.world)
+        for p in range(self.world):
+            ps.out[p] = ptrs[p]
+            ps.flags[p] = self._flag_ptrs[p]
+        self._bufs[name], self._peers[name] = buf, ps
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)   # every rank's flags are zero and mapped before anyone launches
+
+    def prepare(self, weights: dict[str, torch.Tensor], already_sharded: bool = False):
+        state = super().prepare(weights, already_sharded)
+        for name, w in weights.items():
+            dtype = torch.float32 if w.dtype == torch.float32 else torch.bfloat16
+            self._ensure_layer(name, self.rows[name], dtype, w.device)
+        return state
+
+    def kernel_fn(self, data: dict, state) -> torch.Tensor:
+        layer = data["config"]["layer"]
+        m = data["x"].shape[0]
+        if m > self.max_tokens:
+            raise ValueError(f"m={m} exceeds the gathered buffers ({self.max_tokens} tokens)")
+        out = self._bufs[layer][:m]
+        local = {"x": data["x"], "config": self.local_config(data["config"])}
+        return self._kernel_fn(local, state, out=out, peers=self._peers[layer])

@@ -66,7 +66,7 @@ def test_noalloc_matches_ordinary_entry_point_twice_in_a_row(case):
     cnt = torch.zeros(lib.muse_skinny_tiles(m, n, ntok), device=dev, dtype=torch.int32)
     want = torch.full((m, n), float("nan"), device=dev, dtype=odt)
     _capi.check(lib.muse_skinny_tc(maps[0].ptr, lo_ptr, x.data_ptr(), want.data_ptr(), ws.data_ptr(), cnt.data_ptr(),
-                                   status.data_ptr(), m, n, k, k, n, ntok, cluster, groups, stages, int(hilo), stream),
+                                   status.data_ptr(), m, n, k, k, n, ntok, cluster, groups, stages, int(hilo), None, stream),
                 "muse_skinny_tc")
     torch.cuda.synchronize(dev)
     exact = x.double() @ (keep[0].double() + (keep[1].double() if hilo else 0)).T

@@ -1,0 +1,86 @@
+"""One rank of the multi-GPU column-parallel check (launched by tests/test_gpu_tp.py under torchrun).
+
+Each rank shards the target weights by output rows, then for several layers and token counts
+compares (a) the fused exchange (peer stores inside the kernel) and (b) kernel + NCCL all-gather
+against the CPU oracle's full result, and (a) against (b) bit for bit where the plan is
+deterministic. Includes CUDA-graph replays of the fused path. Prints TP_WORKER_OK on success.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def main() -> None:
+    from llm_inference_engine_b200 import muse_bf16_proj as proj
+    from llm_inference_engine_b200 import tp
+    from oracle import muse_proj_oracle as oracle   # the checker
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    layers = {k: oracle.TARGET_LAYERS[k] for k in ("qkv_gate", "o", "router", "unpooler")}
+    w_cpu = oracle.target_weights(layers=layers)
+    w_gpu = {k: v.to(dev) for k, v in w_cpu.items()}
+    nccl = tp.ColumnParallelProjection(proj.prepare, proj.kernel_fn)
+    state = nccl.prepare(w_gpu)
+    fused = tp.FusedColumnParallel(proj.prepare, proj.kernel_fn)
+    fused.rows = dict(nccl.rows)
+    for name, w in w_gpu.items():
+        fused._ensure_layer(name, w.shape[0], w.dtype, dev)
+    bad = []
+    for layer in layers:
+        for m in (1, 2, 8, 32, 100, 256):
+            data = oracle.target_input(m, layer, 7000 + m, layers=layers)
+            gdata = {"x": data["x"].to(dev), "config": data["config"]}
+            a = fused.kernel_fn(gdata, state).clone()
+            b = nccl.kernel_fn(gdata, state)
+            proj.check_status(state)
+            for tag, out in (("fused", a), ("nccl", b)):
+                ok, msg = oracle.target_check(data, out.cpu(), w_cpu)
+                if not ok:
+                    bad.append(f"{tag} {layer} m={m}: {msg}")
+            plan = proj.plan_for(state, layer, m, layers[layer][0] // world, layers[layer][1])
+            if getattr(plan, "groups", 1) == 1 and not torch.equal(a, b):
+                bad.append(f"fused != nccl bitwise: {layer} m={m}")
+    # graph replays of the fused path: every rank replays the same graph the same number of times
+    data = oracle.target_input(32, "qkv_gate", 99, layers=layers)
+    gx = data["x"].to(dev)
+    want = oracle.fp32_reference(data, w_cpu).to(dev)
+    stream = torch.cuda.Stream(dev)
+    hold = {}
+    with torch.cuda.stream(stream):
+        hold["o"] = fused.kernel_fn({"x": gx, "config": data["config"]}, state)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            hold["o"] = fused.kernel_fn({"x": gx, "config": data["config"]}, state)
+        worst = torch.zeros((), device=dev)
+        for _ in range(200):
+            g.replay()
+            worst = torch.maximum(worst, (hold["o"].float() - want).abs().max())
+        stream.synchronize()
+    if float(worst) > 0.05:
+        bad.append(f"fused graph replays: max abs error {float(worst):.3e}")
+    proj.check_status(state)
+    flag = torch.tensor([len(bad)], device=dev)
+    dist.all_reduce(flag)
+    for line in bad:
+        print(f"[rank {rank}] {line}", flush=True)
+    if rank == 0 and int(flag.item()) == 0:
+        print("TP_WORKER_OK", flush=True)
+    dist.destroy_process_group()
+    sys.exit(1 if bad else 0)
+
+
+if __name__ == "__main__":
+    main()
