@@ -127,7 +127,7 @@ __device__ __forceinline__ void store_out8(void* out, int out_f32, bool vec_ok, 
 // More tokens per thread than this go out through a shared-memory transpose as 16-byte vectors.
 constexpr int DIRECT_STORE_TOKENS = 16;
 
-template <int NTOK, bool HILO>
+template <int NTOK, bool HILO, bool PEERS>
 __global__ void __launch_bounds__(128)
 skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wlo,
                  const __grid_constant__ CUtensorMap tm_x, void* __restrict__ out, float* __restrict__ ws,
@@ -191,7 +191,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     for (int i = 0; i < pre; ++i) issue(i, i);
     s_abort = 0;
     s_issued = 0;
-    if (peer_active(ps)) {
+    if constexpr (PEERS) {
       s_epoch = peer_epoch(ps);
       if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) peer_announce_enter(ps, s_epoch);
     }
@@ -304,15 +304,15 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   // Workspace of a tile: [row][NTOK tokens], so that four tokens of a row are one 16-byte vector.
   float* const ws_row = ws + static_cast<size_t>(tile_id) * (TILE_ROWS * NTOK) + static_cast<size_t>(r) * NTOK;
   // Destinations: the caller's `out`, or every rank's gathered output (this rank's columns start at col0).
-  const int ndst = peer_active(ps) ? ps.world : 1;
-  const int col0 = peer_active(ps) ? ps.col0 : 0;
+  const int ndst = PEERS ? ps.world : 1;
+  const int col0 = PEERS ? ps.col0 : 0;
   int pe = 0;
-  if (peer_active(ps)) {
+  if constexpr (PEERS) {
     // No store may reach a peer that has not entered this call: its previous output may still be in use.
     pe = s_epoch;
     peer_wait_all_entered(ps, pe, status);
   }
-  auto dst = [&](int d) -> void* { return peer_active(ps) ? ps.out[d] : out; };
+  auto dst = [&](int d) -> void* { return PEERS ? ps.out[d] : out; };
   auto store_tok = [&](int j, float f) {
     if (row_ok && j < mvalid) {
       const size_t o = static_cast<size_t>(tok0 + j) * ld_out + col0 + n_idx;
@@ -458,7 +458,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   }
 
   // Column-parallel: publish "this rank's slice is everywhere" and wait for the same from every peer.
-  if (peer_active(ps)) peer_finish(ps, pe, static_cast<int>(gridDim.x * gridDim.y * gridDim.z), status, &s_last);
+  if constexpr (PEERS) peer_finish(ps, pe, static_cast<int>(gridDim.x * gridDim.y * gridDim.z), status, &s_last);
 
   // ---- teardown
   if (tid == 0) MUSE_STAMP(9);
@@ -493,10 +493,10 @@ int skinny_smem_bytes(int ntok, int hilo, int stages, int cluster, int m) {
   return (ring > staged ? ring : staged) + rx + 1024;
 }
 
-template <int NTOK, bool HILO>
+template <int NTOK, bool HILO, bool PEERS>
 static cudaError_t configure(int dev, int* room_out) {
   static int dyn_max[64] = {0};  // per device: opt-in ceiling for dynamic shared memory, once raised
-  auto kern = skinny_tc_kernel<NTOK, HILO>;
+  auto kern = skinny_tc_kernel<NTOK, HILO, PEERS>;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   if (!dyn_max[dev]) {
     cudaFuncAttributes fa;
@@ -533,20 +533,36 @@ static void fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int 
   cfg->numAttrs = 1;
 }
 
+template <int NTOK, bool HILO, bool PEERS>
+static cudaError_t launch_with(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
+                               int* cnt, int* status, int m, int n, int chunks, int cluster, int groups, int stages,
+                               int out_f32, int ld_out, const PeerSync& ps, cudaStream_t stream);
+
+// The single-GPU instantiation carries no trace of the peer exchange (PEERS = false).
 template <int NTOK, bool HILO>
 static cudaError_t launch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                           int* cnt, int* status, int m, int n, int chunks, int cluster, int groups, int stages,
                           int out_f32, int ld_out, const PeerSync& ps, cudaStream_t stream) {
+  if (ps.world > 1) return launch_with<NTOK, HILO, true>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups,
+                                                         stages, out_f32, ld_out, ps, stream);
+  return launch_with<NTOK, HILO, false>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups, stages, out_f32,
+                                        ld_out, ps, stream);
+}
+
+template <int NTOK, bool HILO, bool PEERS>
+static cudaError_t launch_with(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
+                               int* cnt, int* status, int m, int n, int chunks, int cluster, int groups, int stages,
+                               int out_f32, int ld_out, const PeerSync& ps, cudaStream_t stream) {
   int dev = 0, room = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if ((e = configure<NTOK, HILO>(dev, &room)) != cudaSuccess) return e;
+  if ((e = configure<NTOK, HILO, PEERS>(dev, &room)) != cudaSuccess) return e;
   const size_t smem = static_cast<size_t>(skinny_smem_bytes(NTOK, HILO, stages, cluster, m));
   if (smem > static_cast<size_t>(room)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
   fill_config<NTOK, HILO>(&cfg, attr, m, n, cluster, groups, smem, stream);
-  return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<NTOK, HILO>, *tw, HILO ? *twlo : *tw, *tx, out, ws, cnt, status, m, n,
+  return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<NTOK, HILO, PEERS>, *tw, HILO ? *twlo : *tw, *tx, out, ws, cnt, status, m, n,
                             chunks, cluster * groups, stages, out_f32, ld_out, g_trace, ps);
 }
 
@@ -555,14 +571,14 @@ template <int NTOK, bool HILO>
 static int max_clusters(int m, int stages, int cluster) {
   int dev = 0, room = 0, num = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
-  if (configure<NTOK, HILO>(dev, &room) != cudaSuccess) return -1;
+  if (configure<NTOK, HILO, false>(dev, &room) != cudaSuccess) return -1;
   const size_t smem = static_cast<size_t>(skinny_smem_bytes(NTOK, HILO, stages, cluster, m));
   if (smem > static_cast<size_t>(room)) return 0;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
   // the grid only has to be a legal multiple of the cluster for the query
   fill_config<NTOK, HILO>(&cfg, attr, m, TILE_ROWS, cluster, 1, smem, nullptr);
-  if (cudaOccupancyMaxActiveClusters(&num, skinny_tc_kernel<NTOK, HILO>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&num, skinny_tc_kernel<NTOK, HILO, false>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
