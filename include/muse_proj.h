@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 6
+#define MUSE_PROJ_ABI_VERSION 7
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -112,6 +112,21 @@ int muse_skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster)
 int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
                    int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
                    int out_is_f32, const muse_peer_sync_t* peers, void* stream);
+
+/* The same product as muse_skinny_tc for tall weights at up to 64 tokens (ntok 16, 32 or 64), as a
+ * persistent "stream-K" launch: `grid` CTAs (one per SM is the intended use) each take an equal,
+ * contiguous share of all (tile, K chunk) units, so every SM streams the same number of weight
+ * bytes and set-up is paid once per SM. Tiles shared by several CTAs are summed through workspace
+ * slots in K order (bit-reproducible); the workspace (muse_streamk_ws_floats floats) needs no
+ * zeroing, the counters (muse_skinny_tiles ints) must be zero before the first call and are left
+ * zero. Same tensor maps, x, out, status and peers arguments as muse_skinny_tc. Replaces the same
+ * reference code (best_submissions/muse_bf16_proj.py:215-287). */
+int muse_streamk_smem_bytes(int ntok, int hilo, int stages);
+int muse_streamk_max_contrib(int m, int n, int k, int ntok, int grid);
+long long muse_streamk_ws_floats(int m, int n, int k, int ntok, int grid);
+int muse_streamk_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt, int* status,
+                    int m, int n, int k, int ld_x, int ld_out, int ntok, int grid, int stages, int out_is_f32,
+                    const muse_peer_sync_t* peers, void* stream);
 
 /* muse_skinny_tc for callers that must not allocate device memory. No counterpart in the reference.
  *

@@ -29,6 +29,12 @@ SIGNATURES = {
     "muse_skinny_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_skinny_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_nop": (C.c_int, [C.c_void_p]),
+    "muse_streamk_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "muse_streamk_max_contrib": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "muse_streamk_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "muse_streamk_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                  C.c_void_p, C.c_void_p]),
     "muse_static_scratch_floats": (C.c_longlong, []),
     "muse_static_scratch_tiles": (C.c_int, []),
     "muse_skinny_tc_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
@@ -37,7 +43,7 @@ SIGNATURES = {
     "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 
 class MuseError(RuntimeError):

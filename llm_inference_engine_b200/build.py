@@ -17,7 +17,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libmuse_proj.so"
-SOURCES = ["gemv1.cu", "skinny_tc.cu", "capi.cu"]
+SOURCES = ["gemv1.cu", "skinny_tc.cu", "streamk_tc.cu", "capi.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -44,15 +44,28 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile the library if it is missing or older than its sources; return its path."""
     if not force and not _stale():
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [str(CSRC / s) for s in SOURCES] + ["-o", str(LIB_PATH)]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or proc.returncode != 0:
-        sys.stderr.write(proc.stdout + proc.stderr)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+    nvcc = _nvcc()
+    compile_flags = [f for f in NVCC_FLAGS if f != "--shared"] + (["-Xptxas", "-v"] if verbose else [])
+    objs = [CSRC / (Path(s).stem + ".o") for s in SOURCES]
+
+    def compile_one(src_obj):
+        src, obj = src_obj
+        return subprocess.run([nvcc, *compile_flags, "-c", str(CSRC / src), "-o", str(obj)], capture_output=True, text=True)
+
+    from concurrent.futures import ThreadPoolExecutor
+
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:   # one nvcc per translation unit, side by side
+        results = list(pool.map(compile_one, zip(SOURCES, objs)))
+    for src, proc in zip(SOURCES, results):
+        if verbose or proc.returncode != 0:
+            sys.stderr.write(proc.stdout + proc.stderr)
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed ({proc.returncode}) on {src}")
+    link = subprocess.run([nvcc, "--shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a",
+                           *[str(o) for o in objs], "-o", str(LIB_PATH)], capture_output=True, text=True)
+    if link.returncode != 0:
+        sys.stderr.write(link.stdout + link.stderr)
+        raise RuntimeError(f"link failed ({link.returncode})")
     return LIB_PATH
 
 

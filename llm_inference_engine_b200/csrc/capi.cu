@@ -18,6 +18,12 @@ int skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster);
 int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out,
                               int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                               int stages, int out_f32, cudaStream_t stream);
+int streamk_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
+                        int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int grid, int stages,
+                        int out_f32, const PeerSync* peers, cudaStream_t stream);
+int streamk_smem_bytes(int ntok, int hilo, int stages);
+int streamk_max_contrib(int m, int n, int k, int ntok, int grid);
+long long streamk_ws_floats(int m, int n, int k, int ntok, int grid);
 long long skinny_static_ws_floats();
 int skinny_static_cnt_ints();
 void skinny_set_trace(unsigned long long* device_buffer);
@@ -139,6 +145,31 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
   return muse::skinny_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
                                   cluster, groups, stages, out_is_f32, reinterpret_cast<const muse::PeerSync*>(peers),
                                   static_cast<cudaStream_t>(stream));
+}
+
+int muse_streamk_smem_bytes(int ntok, int hilo, int stages) { return muse::streamk_smem_bytes(ntok, hilo, stages); }
+int muse_streamk_max_contrib(int m, int n, int k, int ntok, int grid) {
+  return muse::streamk_max_contrib(m, n, k, ntok, grid);
+}
+long long muse_streamk_ws_floats(int m, int n, int k, int ntok, int grid) {
+  return muse::streamk_ws_floats(m, n, k, ntok, grid);
+}
+
+int muse_streamk_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt, int* status,
+                    int m, int n, int k, int ld_x, int ld_out, int ntok, int grid, int stages, int out_is_f32,
+                    const muse_peer_sync_t* peers, void* stream) {
+  if (!tmap_w || !x) return -1;
+  if (ld_x < k || ld_x % 8 != 0) return -2;
+  if (ntok != 16 && ntok != 32 && ntok != 64) return -7;
+  CUtensorMap tx;
+  const int r = muse::encode_2d(&tx, x, m, k, static_cast<long long>(ld_x) * 2, ntok);
+  if (r != 0) return r;
+  CUtensorMap tw, twlo;
+  memcpy(&tw, tmap_w, sizeof(tw));
+  if (tmap_w_lo) memcpy(&twlo, tmap_w_lo, sizeof(twlo));
+  return muse::streamk_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
+                                   grid, stages, out_is_f32, reinterpret_cast<const muse::PeerSync*>(peers),
+                                   static_cast<cudaStream_t>(stream));
 }
 
 long long muse_static_scratch_floats(void) { return muse::skinny_static_ws_floats(); }

@@ -480,6 +480,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
 static unsigned long long* g_trace = nullptr;  // device buffer the next launches stamp into (diagnostics)
 void skinny_set_trace(unsigned long long* device_buffer) { g_trace = device_buffer; }
+unsigned long long* skinny_get_trace() { return g_trace; }
 
 int skinny_stage_bytes(int ntok, int hilo) { return TILE_ROWS * BK * 2 * (hilo ? 2 : 1) + ntok * BK * 2; }
 
