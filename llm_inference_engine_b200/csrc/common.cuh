@@ -242,14 +242,19 @@ __device__ __forceinline__ int ld_volatile_s32(const int* p) {
   asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ bool peer_active(const PeerSync& ps) { return ps.world > 1; }
 // The call number this launch represents (every rank makes the same sequence of calls). The word was
 // written by this GPU's previous kernel, so a plain load sees it. ONE thread per CTA reads it and
 // hands it to the others through shared memory: system-scope operations are kept to a handful per CTA.
 __device__ __forceinline__ int peer_epoch(const PeerSync& ps) { return ld_volatile_s32(ps.flags[ps.rank] + 16) + 1; }
-// One thread of the grid: tell every peer that this rank has entered call `e`.
+// One thread of the grid: tell every peer that this rank has entered call `e`. Nothing is released by
+// this flag (the kernels that consumed the previous output completed before this one started), so the
+// stores are relaxed and leave back to back: a release per peer would cost one NVLink round trip each.
 __device__ __forceinline__ void peer_announce_enter(const PeerSync& ps, int e) {
-  for (int p = 0; p < ps.world; ++p) st_release_sys(ps.flags[p] + ps.rank, e);
+  for (int p = 0; p < ps.world; ++p) st_relaxed_sys(ps.flags[p] + ps.rank, e);
 }
 __device__ __forceinline__ bool peer_wait_flag(const int* flag, int e) {
   if (ld_acquire_sys(flag) >= e) return true;
@@ -291,12 +296,14 @@ __device__ __forceinline__ void peer_publish(const PeerSync& ps, int e, int* sta
   int* mine = ps.flags[ps.rank];
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    mine[17] = 0;
+  if (threadIdx.x == 0) mine[17] = 0;
+  if (threadIdx.x < ps.world) {
+    // One thread per peer, all in parallel: a system-scope fence (it covers the whole CTA's stores, which
+    // the barrier above ordered before it), the flag, then the wait for that peer's flag.
     __threadfence_system();
-    for (int p = 0; p < ps.world; ++p) st_release_sys(ps.flags[p] + 8 + ps.rank, e);
+    st_relaxed_sys(ps.flags[threadIdx.x] + 8 + ps.rank, e);
+    if (!peer_wait_flag(mine + 8 + threadIdx.x, e)) atomicOr(status, ST_PEER_DONE_TIMEOUT);
   }
-  if (threadIdx.x < ps.world && !peer_wait_flag(mine + 8 + threadIdx.x, e)) atomicOr(status, ST_PEER_DONE_TIMEOUT);
   __syncthreads();
   if (threadIdx.x == 0) {
     mine[16] = e;
