@@ -385,24 +385,39 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     cluster_wait();  // pairs with the arrive after set-up: every peer's receive barrier is initialised
     if (tid == 0) MUSE_STAMP(6);
     if (ok) {
-      // Push: tokens [q T, (q + 1) T) go to CTA q, into the slot of our rank.
+      // Push: tokens [q T, (q + 1) T) go to CTA q, into the slot of our rank. The walk over the
+      // tokens is in order, so the owner and the offset inside its block advance by counting (T is
+      // a multiple of four), and a peer's addresses are translated once per owner, not per store.
       const uint32_t my_slot = rx_base + static_cast<uint32_t>((crank * TILE_ROWS + r) * T) * 4u;
       const uint32_t bar_local = smem_u32(&bar_rx);
-#pragma unroll 1
-      for (int c = 0; c < mpad; c += 16) {
-        uint32_t v[16];
-        tmem_ld16(taddr + c, v);
-        tmem_ld_wait();
+      int owner = 0, t = 0;
+      uint32_t slot_remote = dsmem_addr(my_slot, 0), bar_remote = dsmem_addr(bar_local, 0);
+      auto push16 = [&](const uint32_t (&val)[16], int base) {
 #pragma unroll
         for (int j = 0; j < 16; j += 4) {
-          const int tok = c + j;
-          if (tok < mpad) {
-            const int owner = tok / T, t = tok - owner * T;
-            st_async_f32x4(dsmem_addr(my_slot + static_cast<uint32_t>(t) * 4u, owner), __uint_as_float(v[j]),
-                           __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]),
-                           dsmem_addr(bar_local, owner));
+          if (base + j < mpad) {
+            st_async_f32x4(slot_remote + static_cast<uint32_t>(t) * 4u, __uint_as_float(val[j]), __uint_as_float(val[j + 1]),
+                           __uint_as_float(val[j + 2]), __uint_as_float(val[j + 3]), bar_remote);
+            t += 4;
+            if (t == T) {
+              t = 0;
+              if (++owner < csize) {
+                slot_remote = dsmem_addr(my_slot, owner);
+                bar_remote = dsmem_addr(bar_local, owner);
+              }
+            }
           }
         }
+      };
+#pragma unroll 1
+      for (int c = 0; c < mpad; c += 32) {
+        uint32_t v[16], w[16];
+        const bool two = c + 16 < mpad;
+        tmem_ld16(taddr + c, v);
+        if (two) tmem_ld16(taddr + c + 16, w);   // both loads in flight before the one wait
+        tmem_ld_wait();
+        push16(v, c);
+        if (two) push16(w, c + 16);
       }
     }
     if (tid == 0) MUSE_STAMP(7);
