@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 7
+#define MUSE_PROJ_ABI_VERSION 8
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -70,6 +70,17 @@ int muse_query(int what);
  * best_submissions/muse_bf16_proj.py:193-196). */
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,
                int* status, const muse_peer_sync_t* peers, void* stream);
+
+/* out[m, N] = x[m, K] . W[N, K]^T for m = 1..16 tokens against a BF16 weight, as a persistent
+ * streaming walk over W with register-level tensor-core MMAs (no tensor memory, no split-K
+ * workspace): the regime between muse_gemv1 and muse_skinny_tc. K % 32 == 0; x BF16 with ld_x
+ * elements between rows (multiple of 8, 16-byte aligned base), out BF16 with ld_out elements
+ * between rows; warps in {16, 32} per CTA, unroll in {1, 2, 4}. Serves the small-m calls that the
+ * reference gives to skinny_launch (bf16_proj/skinny.cu:1014-1027). -5 = x does not fit in shared
+ * memory (muse_fewtok_smem_bytes > 227 KB). */
+int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
+                    int unroll, int* status, void* stream);
+long long muse_fewtok_smem_bytes(int m, int K, int warps);
 
 /* Fill a 128-byte tensor map for a row-major BF16 matrix [rows, cols] at `base` (device pointer,
  * 16-byte aligned) with `row_stride_bytes` between rows (multiple of 16), delivering boxes of

@@ -29,6 +29,9 @@ SIGNATURES = {
     "muse_skinny_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_skinny_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_nop": (C.c_int, [C.c_void_p]),
+    "muse_fewtok_mma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                  C.c_int, C.c_void_p, C.c_void_p]),
+    "muse_fewtok_smem_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "muse_streamk_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "muse_streamk_max_contrib": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_streamk_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
@@ -43,7 +46,7 @@ SIGNATURES = {
     "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 
 class MuseError(RuntimeError):

@@ -17,7 +17,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libmuse_proj.so"
-SOURCES = ["gemv1.cu", "skinny_tc.cu", "streamk_tc.cu", "capi.cu"]
+SOURCES = ["gemv1.cu", "fewtok_mma.cu", "skinny_tc.cu", "streamk_tc.cu", "capi.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -18,6 +18,9 @@ int skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster);
 int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out,
                               int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                               int stages, int out_f32, cudaStream_t stream);
+int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
+                        int unroll, int* status, cudaStream_t stream);
+size_t fewtok_smem_bytes(int m, int K, int warps);
 int streamk_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                         int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int grid, int stages,
                         int out_f32, const PeerSync* peers, cudaStream_t stream);
@@ -95,6 +98,16 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
                int* status, const muse_peer_sync_t* peers, void* stream) {
   return muse::gemv1_dispatch(W, x, out, N, K, w_is_f32, wpr, unroll, persistent, status,
                               reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
+}
+
+int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
+                    int unroll, int* status, void* stream) {
+  return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, status,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+long long muse_fewtok_smem_bytes(int m, int K, int warps) {
+  return static_cast<long long>(muse::fewtok_smem_bytes(m, K, warps));
 }
 
 int muse_tmap_encode_2d(void* tmap_out128, const void* base, long long rows, long long cols,

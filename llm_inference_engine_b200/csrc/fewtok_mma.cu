@@ -1,0 +1,193 @@
+// out[m, N] = x[m, K] . W[N, K]^T for 2..16 tokens against a BF16 weight, as a persistent streaming
+// walk over the weight with register-level tensor-core MMAs (mma.sync m16n8k16): the latency-bound
+// regime between the one-token GEMV and the TMEM kernel, where allocating tensor memory, building a
+// shared-memory pipeline and reducing split-K partials across a cluster cost more than they save.
+// Extends the reference's m = 1 GEMV (bf16_proj/gemv1.cu:27-125) to the small m that its
+// tensor-core kernel (bf16_proj/skinny.cu) serves.
+//
+// One CTA of NW warps per SM slot. x (m rows, padded by 64 bytes so that the 8 tokens of a fragment
+// fall in different banks) is brought into shared memory once by bulk copies. The CTA then takes
+// groups of 8 weight rows (one contiguous 8 x K block of W) round robin; the NW warps split K, each
+// lane streaming 16-byte pieces of W straight from global memory into the B fragments of two MMAs:
+// lane (g, q) loads W[row0 + g][kb + 8q .. kb + 8q + 7]. The MMA's k slots are a permutation of those
+// eight elements, and the same permutation is applied to x (the A fragment is the 16 bytes of
+// x[token g] at the same offset), so the dot products are unchanged. Tokens are the MMA's M (16),
+// weight rows its N (8). Warps reduce through shared memory in a fixed order (deterministic).
+#include "common.cuh"
+
+namespace muse {
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int FEWTOK_X_PAD = 64;   // bytes added to each x row in shared memory
+
+// HI = tokens 8..15 exist (second half of the A fragment); otherwise those MMA rows are fed zeros.
+template <int NW, int U, bool HI>
+__global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16* __restrict__ W,
+                                                             const __nv_bfloat16* __restrict__ x,
+                                                             __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
+                                                             int ld_out, int* __restrict__ status,
+                                                             unsigned long long* __restrict__ trace) {
+  // Diagnostics: thread 0 of every CTA stamps clock64() into its 16 slots (0 entry, 1 first loads issued,
+  // 2 x arrived, 3/4/5 first group multiplied / reduced in shared memory / stored, 6 last group multiplied,
+  // 7 end, 8 groups walked; 15 and 11 = entry and exit on the global nanosecond timer).
+  unsigned long long* const tr = trace && threadIdx.x == 0 ? trace + 16ull * blockIdx.x : nullptr;
+#define FEWTOK_STAMP(slot) do { if (tr) tr[slot] = static_cast<unsigned long long>(clock64()); } while (0)
+  if (tr) { FEWTOK_STAMP(0); tr[15] = global_ns(); }
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t xbar;
+  constexpr int TOK = HI ? 16 : 8;
+  constexpr int OUTS = TOK * 8;                  // outputs of one row group
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const uint32_t x_stride = static_cast<uint32_t>(K) * 2u + FEWTOK_X_PAD;
+  float* red = reinterpret_cast<float*>(smem + static_cast<size_t>(TOK) * x_stride);   // [2][NW][OUTS]
+  const int kblocks = K >> 5;                    // 32-element (64-byte) pieces of a row
+  const int nb = (kblocks + NW * U - 1) / (NW * U);
+  const int groups = (N + 7) >> 3;
+  const int my_groups = blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int steps = my_groups * nb;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&xbar), 1);
+    fence_mbar_init();
+    mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u * static_cast<uint32_t>(m));
+    for (int t = 0; t < m; ++t)
+      bulk_load_1d(smem_u32(smem) + static_cast<uint32_t>(t) * x_stride, x + static_cast<size_t>(t) * ld_x,
+                   static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
+  }
+  // Lane's piece of batch b of row group i: W[min(8 * group + g, N - 1)][32 * (b * NW * U + warp * U + u) + 8q ..].
+  auto load = [&](uint4 (&w)[U], int i, int b) {
+    int row = (blockIdx.x + i * static_cast<int>(gridDim.x)) * 8 + g;
+    row = row < N ? row : N - 1;
+    const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K) + q;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int kb = b * NW * U + warp * U + u;
+      w[u] = kb < kblocks ? ldg_stream16(p + kb * 4) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  uint4 w[U], wn[U];
+  if (steps > 0) load(w, 0, 0);
+  FEWTOK_STAMP(1);
+  __syncthreads();
+  if (!mbar_wait(smem_u32(&xbar), 0)) {
+    if (threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
+    return;
+  }
+  FEWTOK_STAMP(2);
+  const uint8_t* xg = smem + static_cast<size_t>(g) * x_stride + q * 16;        // token g
+  const uint8_t* xh = xg + 8 * static_cast<size_t>(x_stride);                    // token g + 8
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int i = 0, b = 0;
+  for (int s = 0; s < steps; ++s) {
+    int in = i, bn = b + 1;
+    if (bn == nb) { bn = 0; ++in; }
+    if (s + 1 < steps) load(wn, in, bn);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int kb = b * NW * U + warp * U + u;
+      if (kb < kblocks) {
+        const uint4 xa = *reinterpret_cast<const uint4*>(xg + kb * 64);
+        uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (HI) xb = *reinterpret_cast<const uint4*>(xh + kb * 64);
+        mma_bf16_16816(acc, xa.x, xb.x, xa.y, xb.y, w[u].x, w[u].y);
+        mma_bf16_16816(acc, xa.z, xb.z, xa.w, xb.w, w[u].z, w[u].w);
+      }
+    }
+    if (b == nb - 1) {
+      if (i == 0) FEWTOK_STAMP(3);
+      if (i == my_groups - 1) FEWTOK_STAMP(6);
+      // acc[0..1]: token g, rows 2q, 2q+1 of the group; acc[2..3]: token g + 8.
+      float* mine = red + (static_cast<size_t>(i & 1) * NW + warp) * OUTS;
+      *reinterpret_cast<float2*>(mine + g * 8 + 2 * q) = make_float2(acc[0], acc[1]);
+      if constexpr (HI) *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * q) = make_float2(acc[2], acc[3]);
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      __syncthreads();   // the buffer written two groups ago is free again once every warp passed this
+      if (i == 0) FEWTOK_STAMP(4);
+      if (threadIdx.x < OUTS) {
+        const float* col = red + static_cast<size_t>(i & 1) * NW * OUTS + threadIdx.x;
+        float sum = 0.f;
+#pragma unroll 8
+        for (int wv = 0; wv < NW; ++wv) sum += col[wv * OUTS];
+        const int t = threadIdx.x >> 3;
+        const int row = (blockIdx.x + i * static_cast<int>(gridDim.x)) * 8 + (threadIdx.x & 7);
+        if (t < m && row < N) out[static_cast<size_t>(t) * ld_out + row] = __float2bfloat16_rn(sum);
+      }
+      if (i == 0) FEWTOK_STAMP(5);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) w[u] = wn[u];
+    i = in;
+    b = bn;
+  }
+  if (tr) { FEWTOK_STAMP(7); tr[8] = static_cast<unsigned long long>(my_groups); tr[11] = global_ns(); }
+#undef FEWTOK_STAMP
+}
+
+unsigned long long* skinny_get_trace();
+
+static size_t fewtok_smem(int K, bool hi, int nw) {
+  const int tok = hi ? 16 : 8;
+  return static_cast<size_t>(tok) * (static_cast<size_t>(K) * 2 + FEWTOK_X_PAD) + 2ull * nw * tok * 8 * sizeof(float);
+}
+
+template <int NW, int U, bool HI>
+static cudaError_t launch_fewtok(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
+                                 int* status, cudaStream_t s) {
+  auto kern = fewtok_mma_kernel<NW, U, HI>;
+  static int configured[64] = {0}, sms[64] = {0}, optin[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    if ((e = cudaDeviceGetAttribute(&optin[dev], cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
+    cudaFuncAttributes fa;
+    if ((e = cudaFuncGetAttributes(&fa, kern)) != cudaSuccess) return e;
+    optin[dev] -= static_cast<int>(fa.sharedSizeBytes);
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin[dev])) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    configured[dev] = 1;
+  }
+  const size_t smem = fewtok_smem(K, HI, NW);
+  if (smem > static_cast<size_t>(optin[dev])) return cudaErrorInvalidConfiguration;
+  int resident = 0;
+  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, NW * 32, smem)) != cudaSuccess) return e;
+  if (resident < 1) return cudaErrorInvalidConfiguration;
+  int grid = sms[dev] * resident;
+  const int groups = (N + 7) / 8;
+  if (grid > groups) grid = groups;
+  kern<<<grid, NW * 32, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(W), reinterpret_cast<const __nv_bfloat16*>(x),
+                                   reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, status, skinny_get_trace());
+  return cudaGetLastError();
+}
+
+size_t fewtok_smem_bytes(int m, int K, int warps) { return fewtok_smem(K, m > 8, warps); }
+
+// 1..16 tokens, BF16 weight and output; warps in {16, 32}, unroll in {1, 2, 4}. Negative = argument error.
+int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
+                        int unroll, int* status, cudaStream_t stream) {
+  if (!W || !x || !out || !status || N <= 0 || K <= 0) return -1;
+  if (m < 1 || m > 16) return -9;
+  if (K % 32 != 0 || ld_x % 8 != 0 || ld_x < K || ld_out < N) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
+  if (fewtok_smem(K, m > 8, warps) > 227 * 1024) return -5;
+  cudaError_t e = cudaErrorInvalidValue;
+#define MUSE_FEWTOK(NW_, U_)                                                                                    \
+  if (warps == NW_ && unroll == U_)                                                                             \
+    e = m > 8 ? launch_fewtok<NW_, U_, true>(W, x, out, m, N, K, ld_x, ld_out, status, stream)                  \
+              : launch_fewtok<NW_, U_, false>(W, x, out, m, N, K, ld_x, ld_out, status, stream);
+  MUSE_FEWTOK(32, 1) MUSE_FEWTOK(32, 2) MUSE_FEWTOK(32, 4) MUSE_FEWTOK(16, 1) MUSE_FEWTOK(16, 2) MUSE_FEWTOK(16, 4)
+#undef MUSE_FEWTOK
+  if (e == cudaErrorInvalidConfiguration) return -5;
+  return static_cast<int>(e);
+}
+
+}  // namespace muse

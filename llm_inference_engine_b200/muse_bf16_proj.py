@@ -25,7 +25,7 @@ import ctypes
 import torch
 
 from . import _capi
-from .plan import DeviceFacts, GemvPlan, SkinnyPlan, gemv_plan, gemv_valid, skinny_plan
+from .plan import DeviceFacts, FewTokPlan, GemvPlan, SkinnyPlan, fewtok_plan, gemv_plan, gemv_valid, skinny_plan
 
 FP32_LAYERS = {"router"}
 # Workspace rule: sized once in prepare() so that every layer at up to this many tokens can split K;
@@ -145,17 +145,23 @@ def _weight_maps(state, layer: str, n: int):
     return maps
 
 
-def plan_for(state, layer: str, m: int, n: int, k: int) -> GemvPlan | SkinnyPlan:
-    """The (cached) launch plan of a shape; `state["_override"][(layer, m)]` = dict(cluster=, groups=, stages=) or
-    dict(wpr=, unroll=) forces values for tuning sweeps."""
-    key = (layer, m, n, k)
+def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> GemvPlan | FewTokPlan | SkinnyPlan:
+    """The (cached) launch plan of a shape; `state["_override"][(layer, m)]` = dict(cluster=, groups=, stages=),
+    dict(wpr=, unroll=) or dict(warps=, unroll=) forces values for tuning sweeps. `fused` = the call carries a
+    peer descriptor (the register-MMA kernel has no exchange epilogue)."""
+    key = (layer, m, n, k, fused)
     ov = state["_override"].get((layer, m))
     if ov is None and key in state["_plans"]:
         return state["_plans"][key]
     f32 = layer in FP32_LAYERS
     dev = state["_dev"]
+    few = None
+    if not fused and not f32 and 2 <= m <= 16:
+        few = FewTokPlan(**ov) if ov and "warps" in ov else (None if ov else fewtok_plan(m, n, k, f32, dev))
     if m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):
         plan = GemvPlan(**ov) if ov else gemv_plan(n, k, f32, dev)
+    elif few is not None:
+        plan = few
     else:
         lib = _capi.load()
         fit = lambda ntok, hilo, m_, stages, cluster: lib.muse_skinny_max_clusters(ntok, int(hilo), m_, stages, cluster)
@@ -192,8 +198,13 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None, peers=None) 
         raise ValueError("out must be [m, >= n], unit column stride, BF16 (FP32 for the router)")
     lib = state.get("_lib") or _capi.load()
     stream = torch.cuda.current_stream(x.device).cuda_stream
-    plan = plan_for(state, layer, m, n, k)
+    plan = plan_for(state, layer, m, n, k, fused=peers is not None)
     status = state["_status"].data_ptr()
+    if isinstance(plan, FewTokPlan):
+        _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0),
+                                        plan.warps, plan.unroll, status, stream),
+                    f"muse_fewtok_mma({layer}, m={m}, n={n}, k={k}, {plan})")
+        return out
     if isinstance(plan, GemvPlan):
         _capi.check(lib.muse_gemv1(w.data_ptr(), x.data_ptr(), out.data_ptr(), n, k, int(f32), plan.wpr, plan.unroll,
                                    int(plan.persistent), status, _peer_ptr(peers), stream), f"muse_gemv1({layer}, n={n}, k={k})")

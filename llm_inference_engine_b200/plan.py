@@ -35,6 +35,13 @@ class GemvPlan:
 
 
 @dataclass(frozen=True)
+class FewTokPlan:
+    """Up to 16 tokens streamed through register-level MMAs (muse_fewtok_mma)."""
+    warps: int    # per CTA: 16 (two CTAs per SM) or 32
+    unroll: int   # 16-byte loads in flight per lane per batch
+
+
+@dataclass(frozen=True)
 class SkinnyPlan:
     ntok: int       # tokens per tile (MMA N)
     cluster: int    # K slices reduced on chip (CTAs per thread-block cluster)
@@ -60,6 +67,17 @@ TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int, bool]] = {
     (4096, 1024, False): (1, 4, False),    # unpooler 3.5 us
     (256, 4096, True): (8, 4, False),      # router 2.8 us
 }
+# Same protocol: (n, k, 8 or 16 = token bucket) -> (warps, unroll) where the register-MMA walk beats the
+# TMEM kernel (the figure after it is the TMEM kernel's).
+TUNED_FEWTOK: dict[tuple[int, int, int], tuple[int, int]] = {
+    (12288, 4096, 8): (16, 4),    # qkv_gate 18.6-18.9 us / 20.1-20.4
+    (4096, 4096, 8): (16, 4),     # o 8.5-9.0 / 9.8-10.0
+    (1024, 4096, 8): (32, 4),     # pooler 4.3 / 6.8-7.0
+    (1024, 4096, 16): (32, 4),    # 4.5 / 7.1
+    (4096, 1024, 8): (16, 2),     # unpooler 4.2-4.3 / 6.1-6.2
+    (4096, 1024, 16): (16, 2),    # 4.75 / 6.4
+}
+FEWTOK_X_PAD = 64
 # Same protocol: (n, k, hilo, token bucket) -> (ntok, cluster, groups, stages). The bucket is the
 # smallest of NTOK_CHOICES holding m; ntok may be smaller (several token tiles: small weights gain
 # more from extra tiles than they lose re-reading W through L2).
@@ -118,6 +136,27 @@ def gemv_plan(n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) 
     # Tall weights (several rows per resident warp slot) drain more evenly on the persistent grid.
     persistent = wpr == 1 and n >= 16 * dev.sms and k * 2 <= 64 * 1024
     return GemvPlan(wpr=wpr, unroll=min(4, _pow2_floor(vec_per_lane)), persistent=persistent)
+
+
+def fewtok_smem_bytes(m: int, k: int, warps: int) -> int:
+    """Shared memory of muse_fewtok_mma: 8 or 16 padded x rows + two reduction buffers (mirrors the C side)."""
+    tok = 16 if m > 8 else 8
+    return tok * (k * 2 + FEWTOK_X_PAD) + 2 * warps * tok * 8 * 4
+
+
+def fewtok_plan(m: int, n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) -> FewTokPlan | None:
+    """The register-MMA plan of a shape that gains from it, else None (TMEM kernel). Tuned shapes come
+    from the table; others take it at m <= 8 when the weight has enough 8-row groups to occupy most SMs."""
+    if w_is_f32 or not 2 <= m <= 16 or k % 32:
+        return None
+    tuned = TUNED_FEWTOK.get((n, k, 16 if m > 8 else 8))
+    if tuned is None:
+        if m > 8 or (n + 7) // 8 < dev.sms * 3 // 4:
+            return None
+        tuned = (16, min(4, _pow2_floor(max(1, k // 32 // 16))))
+    if fewtok_smem_bytes(m, k, tuned[0]) > dev.smem_optin:
+        return None
+    return FewTokPlan(*tuned)
 
 
 def pick_ntok(m: int) -> int:

@@ -45,6 +45,8 @@ def test_pure_host_entry_points_without_a_gpu():
     assert lib.muse_skinny_tiles(300, 200, 256) == 4
     assert lib.muse_skinny_ws_floats(32, 12288, 32) == 96 * 128 * 32
     assert lib.muse_skinny_tiles(0, 1, 16) < 0
+    for m, k, warps in ((2, 4096, 16), (8, 1024, 32), (9, 4096, 32), (16, 2048, 16)):
+        assert lib.muse_fewtok_smem_bytes(m, k, warps) == plan.fewtok_smem_bytes(m, k, warps)
     for ntok in plan.NTOK_CHOICES:
         for hilo in (False, True):
             assert lib.muse_skinny_stage_bytes(ntok, int(hilo)) == plan.stage_bytes(ntok, hilo)

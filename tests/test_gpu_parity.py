@@ -151,6 +151,7 @@ def test_linearity_at_full_size(oracle, proj, dev, target_setup):
 # rarely picks on its own: sums meeting in the global workspace (groups > 1), with and without clusters.
 REPLAY_CASES = [
     ("qkv_gate", 32, None), ("pooler", 8, None), ("router", 32, None), ("router", 256, None), ("unpooler", 128, None),
+    ("qkv_gate", 4, None), ("unpooler", 16, None), ("o", 7, dict(warps=32, unroll=2)),
     ("qkv_gate", 32, dict(cluster=1, groups=3, stages=4)),
     ("pooler", 8, dict(cluster=2, groups=9, stages=3)),
     ("pooler", 100, dict(ntok=128, cluster=4, groups=2, stages=3)),
@@ -196,9 +197,10 @@ def test_graph_replays_are_stable_and_leave_workspace_clean(oracle, proj, dev, t
                     changed += (holder["out"] != first).any().int()
             timer.stream.synchronize()
             assert int(bad) == 0, f"{layer} m={m} {plan}: {int(bad)}/300 bad replays"
-            if plan.groups == 1:
+            groups = getattr(plan, "groups", 1)   # the register-MMA plans have no global workspace either
+            if groups == 1:
                 assert int(changed) == 0, f"{layer} m={m} {plan}: output changed between replays"
-            if plan.groups > 1:   # only these plans touch (and therefore create) the stream's workspace
+            if groups > 1:   # only these plans touch (and therefore create) the stream's workspace
                 ws, cnt = state["_ws_by_stream"][timer.stream.cuda_stream]
                 assert float(ws.abs().max()) == 0.0 and int(cnt.abs().max()) == 0
     finally:
@@ -262,3 +264,58 @@ def test_streamk_entry_point_matches_oracle_and_is_bit_stable(dev, case):
     err = float((outs[0].double() - ref).norm() / ref.norm())
     assert err < (1e-5 if hilo else 5e-3), err
     assert all(torch.equal(outs[0], o) for o in outs[1:])
+
+
+FEWTOK_CASES = [  # (m, n, k, warps, unroll)
+    (2, 12288, 4096, 16, 4), (8, 12288, 4096, 32, 4), (16, 4096, 1024, 16, 2), (3, 1001, 4096, 32, 1), (9, 520, 2080, 16, 2),
+    (1, 8, 32, 16, 1), (5, 3, 64, 32, 4), (13, 1024, 4096, 32, 4), (7, 300, 8192, 16, 4),
+]
+
+
+@pytest.mark.parametrize("case", FEWTOK_CASES, ids=lambda c: "m{}_n{}_k{}_w{}u{}".format(*c))
+def test_fewtok_entry_point_matches_oracle_and_is_bit_stable(dev, case):
+    """muse_fewtok_mma (register-level MMAs, 1..16 tokens) through the C ABI: FP64 product within the
+    BF16 tolerance, ragged N (rows not a multiple of 8), strided x and out, columns beyond n untouched,
+    identical bits on repeated calls (the warps' partial sums are added in a fixed order)."""
+    from llm_inference_engine_b200 import _capi
+
+    m, n, k, warps, unroll = case
+    lib = _capi.load()
+    g = torch.Generator(device=dev).manual_seed(m * 11 + n)
+    w = (torch.randn((n, k), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    x = torch.randn((m, k + 24), generator=g, device=dev).to(torch.bfloat16)[:, :k]
+    ref = x.double() @ w.double().T
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    outs = []
+    for _ in range(3):
+        out = torch.full((m, n + 5), 3.0, device=dev, dtype=torch.bfloat16)
+        _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0), warps,
+                                        unroll, status.data_ptr(), torch.cuda.current_stream(dev).cuda_stream), "muse_fewtok_mma")
+        torch.cuda.synchronize(dev)
+        outs.append(out)
+    assert int(status.item()) == 0
+    assert bool((outs[0][:, n:] == 3.0).all())
+    err = float((outs[0][:, :n].double() - ref).norm() / ref.norm())
+    assert err < 5e-3, err
+    row_err = ((outs[0][:, :n].double() - ref).norm(dim=1) / ref.norm(dim=1).clamp(min=1e-6)).max()
+    assert float(row_err) < 1e-2
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+
+
+def test_fewtok_rejections(dev):
+    from llm_inference_engine_b200 import _capi
+
+    lib = _capi.load()
+    w = torch.zeros((64, 4096), device=dev, dtype=torch.bfloat16)
+    x = torch.zeros((17, 4096), device=dev, dtype=torch.bfloat16)
+    out = torch.zeros((17, 64), device=dev, dtype=torch.bfloat16)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    call = lambda m, n, k, ldx, ldo, warps, unroll: lib.muse_fewtok_mma(
+        w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, ldx, ldo, warps, unroll, status.data_ptr(), None)
+    assert call(17, 64, 4096, 4096, 64, 16, 4) == -9        # more than 16 tokens
+    assert call(4, 64, 4080, 4096, 64, 16, 4) == -2         # K not a multiple of 32
+    assert call(4, 64, 4096, 4096, 32, 16, 4) == -2         # out rows shorter than n
+    assert call(4, 64, 4096, 4096, 64, 8, 4) != 0           # unsupported CTA size
+    assert call(16, 64, 16384, 16384, 64, 32, 4) == -5      # 16 rows of x do not fit in shared memory
+    torch.cuda.synchronize(dev)
+    assert int(status.item()) == 0
