@@ -73,11 +73,11 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
 
 /* out[m, N] = x[m, K] . W[N, K]^T for m = 1..16 tokens against a BF16 weight, as a persistent
  * streaming walk over W with register-level tensor-core MMAs (no tensor memory, no split-K
- * workspace): the regime between muse_gemv1 and muse_skinny_tc. K % 32 == 0; x BF16 with ld_x
+ * workspace, bit-reproducible): the regime between muse_gemv1 and muse_skinny_tc. K % 32 == 0; x BF16 with ld_x
  * elements between rows (multiple of 8, 16-byte aligned base), out BF16 with ld_out elements
- * between rows; warps in {16, 32} per CTA, unroll in {1, 2, 4}. Serves the small-m calls that the
- * reference gives to skinny_launch (bf16_proj/skinny.cu:1014-1027). -5 = x does not fit in shared
- * memory (muse_fewtok_smem_bytes > 227 KB). */
+ * between rows; warps in {16, 32} per CTA, unroll in {1, 2, 4}. Serves the smallest of the m <= 32
+ * calls that the reference gives to _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337,
+ * :236-257). -5 = x does not fit in shared memory (muse_fewtok_smem_bytes > 227 KB). */
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
                     int unroll, int* status, void* stream);
 long long muse_fewtok_smem_bytes(int m, int K, int warps);

@@ -2,10 +2,10 @@
 // walk over the weight with register-level tensor-core MMAs (mma.sync m16n8k16): the latency-bound
 // regime between the one-token GEMV and the TMEM kernel, where allocating tensor memory, building a
 // shared-memory pipeline and reducing split-K partials across a cluster cost more than they save.
-// Extends the reference's m = 1 GEMV (bf16_proj/gemv1.cu:27-125) to the small m that its
-// tensor-core kernel (bf16_proj/skinny.cu) serves.
+// Extends the reference's m = 1 GEMV (bf16_proj/gemv1.cu:27-125) to the smallest of the m <= 32 calls
+// that its swap-AB kernel serves (_swab_kernel, best_submissions/muse_bf16_proj.py:236-257).
 //
-// One CTA of NW warps per SM slot. x (m rows, padded by 64 bytes so that the 8 tokens of a fragment
+// A persistent grid of CTAs of NW warps. x (m rows, padded by 64 bytes so that the 8 tokens of a fragment
 // fall in different banks) is brought into shared memory once by bulk copies. The CTA then takes
 // groups of 8 weight rows (one contiguous 8 x K block of W) round robin; the NW warps split K, each
 // lane streaming 16-byte pieces of W straight from global memory into the B fragments of two MMAs:
@@ -13,6 +13,10 @@
 // eight elements, and the same permutation is applied to x (the A fragment is the 16 bytes of
 // x[token g] at the same offset), so the dot products are unchanged. Tokens are the MMA's M (16),
 // weight rows its N (8). Warps reduce through shared memory in a fixed order (deterministic).
+//
+// When one batch of the CTA's loads covers a whole row (K <= 32 * NW * U) and m <= 8, every warp meets
+// the same pieces of K in every group, so its A fragments never change: fewtok_xreg_kernel loads them
+// once from global memory into registers and runs with no shared-memory copy of x at all.
 #include "common.cuh"
 
 namespace muse {
@@ -47,7 +51,7 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const uint32_t x_stride = static_cast<uint32_t>(K) * 2u + FEWTOK_X_PAD;
-  float* red = reinterpret_cast<float*>(smem + static_cast<size_t>(TOK) * x_stride);   // [2][NW][OUTS]
+  float* red = reinterpret_cast<float*>(smem + static_cast<size_t>(m) * x_stride);   // [2][NW][OUTS]
   const int kblocks = K >> 5;                    // 32-element (64-byte) pieces of a row
   const int nb = (kblocks + NW * U - 1) / (NW * U);
   const int groups = (N + 7) >> 3;
@@ -82,8 +86,10 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
     return;
   }
   FEWTOK_STAMP(2);
-  const uint8_t* xg = smem + static_cast<size_t>(g) * x_stride + q * 16;        // token g
-  const uint8_t* xh = xg + 8 * static_cast<size_t>(x_stride);                    // token g + 8
+  // MMA rows of tokens that do not exist read the last real token (fewer distinct shared-memory
+  // addresses per load than zero rows would cost); their results are never stored.
+  const uint8_t* xg = smem + static_cast<size_t>(min(g, m - 1)) * x_stride + q * 16;        // token g
+  const uint8_t* xh = smem + static_cast<size_t>(min(g + 8, m - 1)) * x_stride + q * 16;    // token g + 8
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   int i = 0, b = 0;
   for (int s = 0; s < steps; ++s) {
@@ -131,11 +137,65 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 #undef FEWTOK_STAMP
 }
 
+// m <= 8 and K <= 32 * NW * U: one batch per group, A fragments resident in registers (no shared-memory x).
+template <int NW, int U>
+__global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
+                                                              const __nv_bfloat16* __restrict__ x,
+                                                              __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
+                                                              int ld_out) {
+  constexpr int OUTS = 64;                       // 8 tokens x 8 rows
+  __shared__ __align__(16) float red[2][NW][OUTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int C = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  const int kblocks = K >> 5;
+  const int groups = (N + 7) >> 3;
+  const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
+  const int first = warp * U;                    // this warp's 64-byte pieces of every row: first .. first + U - 1
+  auto load = [&](uint4 (&w)[U], int i) {
+    int row = (c + i * C) * 8 + g;
+    row = row < N ? row : N - 1;
+    const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K) + q;
+#pragma unroll
+    for (int u = 0; u < U; ++u) w[u] = first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+  };
+  // One register buffer: a group's loads are re-issued into it as soon as its MMAs have read it, and stay
+  // in flight across the reduction below. (A second buffer costs 16 registers the 32-warp CTA does not have.)
+  uint4 w[U], xr[U];
+  if (my_groups > 0) load(w, 0);
+  {
+    const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = 0; i < my_groups; ++i) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, w[u].x, w[u].y);
+      mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, w[u].z, w[u].w);
+    }
+    if (i + 1 < my_groups) load(w, i + 1);
+    *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+    __syncthreads();   // the buffer written two groups ago is free again once every warp passed this
+    if (threadIdx.x < OUTS) {
+      float sum = 0.f;
+#pragma unroll 8
+      for (int wv = 0; wv < NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
+      const int t = threadIdx.x >> 3;
+      const int row = (c + i * C) * 8 + (threadIdx.x & 7);
+      if (t < m && row < N) out[static_cast<size_t>(t) * ld_out + row] = __float2bfloat16_rn(sum);
+    }
+  }
+}
+
 unsigned long long* skinny_get_trace();
 
-static size_t fewtok_smem(int K, bool hi, int nw) {
-  const int tok = hi ? 16 : 8;
-  return static_cast<size_t>(tok) * (static_cast<size_t>(K) * 2 + FEWTOK_X_PAD) + 2ull * nw * tok * 8 * sizeof(float);
+static size_t fewtok_smem(int K, int m, int nw) {
+  const int tok = m > 8 ? 16 : 8;
+  return static_cast<size_t>(m) * (static_cast<size_t>(K) * 2 + FEWTOK_X_PAD) + 2ull * nw * tok * 8 * sizeof(float);
 }
 
 template <int NW, int U, bool HI>
@@ -156,7 +216,7 @@ static cudaError_t launch_fewtok(const void* W, const void* x, void* out, int m,
     if ((e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
     configured[dev] = 1;
   }
-  const size_t smem = fewtok_smem(K, HI, NW);
+  const size_t smem = fewtok_smem(K, m, NW);
   if (smem > static_cast<size_t>(optin[dev])) return cudaErrorInvalidConfiguration;
   int resident = 0;
   if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, NW * 32, smem)) != cudaSuccess) return e;
@@ -169,7 +229,31 @@ static cudaError_t launch_fewtok(const void* W, const void* x, void* out, int m,
   return cudaGetLastError();
 }
 
-size_t fewtok_smem_bytes(int m, int K, int warps) { return fewtok_smem(K, m > 8, warps); }
+template <int NW, int U>
+static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
+                               cudaStream_t s) {
+  auto kern = fewtok_xreg_kernel<NW, U>;
+  static int per_sm[64] = {0}, sms[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!per_sm[dev]) {
+    if ((e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    int resident = 0;
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, NW * 32, 0)) != cudaSuccess) return e;
+    if (resident < 1) return cudaErrorInvalidConfiguration;
+    per_sm[dev] = resident;
+  }
+  int grid = sms[dev] * per_sm[dev];
+  const int groups = (N + 7) / 8;
+  if (grid > groups) grid = groups;
+  kern<<<grid, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W), reinterpret_cast<const __nv_bfloat16*>(x),
+                                reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out);
+  return cudaGetLastError();
+}
+
+size_t fewtok_smem_bytes(int m, int K, int warps) { return fewtok_smem(K, m, warps); }
 
 // 1..16 tokens, BF16 weight and output; warps in {16, 32}, unroll in {1, 2, 4}. Negative = argument error.
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
@@ -178,8 +262,15 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
   if (m < 1 || m > 16) return -9;
   if (K % 32 != 0 || ld_x % 8 != 0 || ld_x < K || ld_out < N) return -2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
-  if (fewtok_smem(K, m > 8, warps) > 227 * 1024) return -5;
+  if (fewtok_smem(K, m, warps) > 227 * 1024) return -5;
   cudaError_t e = cudaErrorInvalidValue;
+  if (m <= 8 && K / 32 <= warps * unroll) {   // a whole row per batch: the A fragments stay in registers
+#define MUSE_XREG(NW_, U_) \
+    if (warps == NW_ && unroll == U_) e = launch_xreg<NW_, U_>(W, x, out, m, N, K, ld_x, ld_out, stream);
+    MUSE_XREG(32, 1) MUSE_XREG(32, 2) MUSE_XREG(32, 4) MUSE_XREG(16, 1) MUSE_XREG(16, 2) MUSE_XREG(16, 4)
+#undef MUSE_XREG
+    return static_cast<int>(e);
+  }
 #define MUSE_FEWTOK(NW_, U_)                                                                                    \
   if (warps == NW_ && unroll == U_)                                                                             \
     e = m > 8 ? launch_fewtok<NW_, U_, true>(W, x, out, m, N, K, ld_x, ld_out, status, stream)                  \

@@ -156,12 +156,12 @@ def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> 
     f32 = layer in FP32_LAYERS
     dev = state["_dev"]
     few = None
-    if not fused and not f32 and 2 <= m <= 16:
+    if not fused and not f32 and m <= 16:
         few = FewTokPlan(**ov) if ov and "warps" in ov else (None if ov else fewtok_plan(m, n, k, f32, dev))
-    if m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):
-        plan = GemvPlan(**ov) if ov else gemv_plan(n, k, f32, dev)
-    elif few is not None:
+    if few is not None:
         plan = few
+    elif m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):
+        plan = GemvPlan(**ov) if ov else gemv_plan(n, k, f32, dev)
     else:
         lib = _capi.load()
         fit = lambda ntok, hilo, m_, stages, cluster: lib.muse_skinny_max_clusters(ntok, int(hilo), m_, stages, cluster)

@@ -67,14 +67,16 @@ TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int, bool]] = {
     (4096, 1024, False): (1, 4, False),    # unpooler 3.5 us
     (256, 4096, True): (8, 4, False),      # router 2.8 us
 }
-# Same protocol: (n, k, 8 or 16 = token bucket) -> (warps, unroll) where the register-MMA walk beats the
-# TMEM kernel (the figure after it is the TMEM kernel's).
+# Same protocol: (n, k, token bucket 1, 8 or 16) -> (warps, unroll) where the register-MMA walk beats the
+# alternative (the figure after the slash: the GEMV in bucket 1, else the TMEM kernel). warps * unroll
+# >= K / 32 with m <= 8 selects its variant that keeps x in registers.
 TUNED_FEWTOK: dict[tuple[int, int, int], tuple[int, int]] = {
-    (12288, 4096, 8): (16, 4),    # qkv_gate 18.6-18.9 us / 20.1-20.4
-    (4096, 4096, 8): (16, 4),     # o 8.5-9.0 / 9.8-10.0
-    (1024, 4096, 8): (32, 4),     # pooler 4.3 / 6.8-7.0
+    (12288, 4096, 1): (32, 4),    # qkv_gate 17.6 us / 18.1
+    (12288, 4096, 8): (32, 4),    # 18.1-18.4 / 20.1-20.4
+    (4096, 4096, 8): (32, 4),     # o 8.1-8.2 / 9.8-10.0
+    (1024, 4096, 8): (32, 4),     # pooler 4.2-4.5 / 6.8-7.0
     (1024, 4096, 16): (32, 4),    # 4.5 / 7.1
-    (4096, 1024, 8): (16, 2),     # unpooler 4.2-4.3 / 6.1-6.2
+    (4096, 1024, 8): (16, 2),     # unpooler 3.9 / 6.1-6.2
     (4096, 1024, 16): (16, 2),    # 4.75 / 6.4
 }
 FEWTOK_X_PAD = 64
@@ -139,22 +141,23 @@ def gemv_plan(n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) 
 
 
 def fewtok_smem_bytes(m: int, k: int, warps: int) -> int:
-    """Shared memory of muse_fewtok_mma: 8 or 16 padded x rows + two reduction buffers (mirrors the C side)."""
+    """Shared memory of muse_fewtok_mma: m padded x rows + two reduction buffers (mirrors the C side)."""
     tok = 16 if m > 8 else 8
-    return tok * (k * 2 + FEWTOK_X_PAD) + 2 * warps * tok * 8 * 4
+    return m * (k * 2 + FEWTOK_X_PAD) + 2 * warps * tok * 8 * 4
 
 
 def fewtok_plan(m: int, n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) -> FewTokPlan | None:
     """The register-MMA plan of a shape that gains from it, else None (TMEM kernel). Tuned shapes come
     from the table; others take it at m <= 8 when the weight has enough 8-row groups to occupy most SMs."""
-    if w_is_f32 or not 2 <= m <= 16 or k % 32:
+    if w_is_f32 or not 1 <= m <= 16 or k % 32:
         return None
-    tuned = TUNED_FEWTOK.get((n, k, 16 if m > 8 else 8))
+    tuned = TUNED_FEWTOK.get((n, k, 1 if m == 1 else 16 if m > 8 else 8))
     if tuned is None:
-        if m > 8 or (n + 7) // 8 < dev.sms * 3 // 4:
+        if m == 1 or m > 8 or (n + 7) // 8 < dev.sms * 3 // 4:
             return None
-        tuned = (16, min(4, _pow2_floor(max(1, k // 32 // 16))))
-    if fewtok_smem_bytes(m, k, tuned[0]) > dev.smem_optin:
+        kblocks = k // 32   # a whole row per batch (x stays in registers) whenever 32 warps x 4 loads reach
+        tuned = (16, 1) if kblocks <= 16 else (16, 2) if kblocks <= 32 else (16, 4) if kblocks <= 64 else (32, 4)
+    if tuned[0] * tuned[1] < k // 32 and fewtok_smem_bytes(m, k, tuned[0]) > dev.smem_optin:
         return None
     return FewTokPlan(*tuned)
 

@@ -76,12 +76,12 @@ def test_tuned_entries_are_launchable():
     for (n, k, f32), (wpr, unroll, persistent) in plan.TUNED_GEMV.items():
         assert plan.gemv_valid(k, f32, wpr) and unroll in (1, 2, 4, 8) and (wpr == 1 or not persistent)
     for (n, k, bucket), (warps, unroll) in plan.TUNED_FEWTOK.items():
-        assert bucket in (8, 16) and warps in (16, 32) and unroll in (1, 2, 4) and k % 32 == 0
+        assert bucket in (1, 8, 16) and warps in (16, 32) and unroll in (1, 2, 4) and k % 32 == 0
         assert plan.fewtok_plan(bucket, n, k, False) == plan.FewTokPlan(warps, unroll)
 
 
 def test_fewtok_plan_only_where_it_applies():
-    assert plan.fewtok_plan(1, 12288, 4096, False) is None           # one token: the GEMV
+    assert plan.fewtok_plan(1, 4096, 4096, False) is None            # one token, untuned: the GEMV
     assert plan.fewtok_plan(8, 256, 4096, True) is None              # FP32 router weights
     assert plan.fewtok_plan(17, 1024, 4096, False) is None           # more than one MMA of tokens
     assert plan.fewtok_plan(4, 12288, 4100, False) is None           # K not in whole 32-element pieces
@@ -89,8 +89,10 @@ def test_fewtok_plan_only_where_it_applies():
     assert plan.fewtok_plan(4, 512, 4096, False) is None             # too few row groups to occupy the SMs
     assert plan.fewtok_plan(4, 8192, 2048, False) == plan.FewTokPlan(16, 4)
     assert plan.fewtok_plan(4, 8192, 512, False) == plan.FewTokPlan(16, 1)
-    assert plan.fewtok_plan(8, 8192, 16384, False) is None           # 8 rows of x exceed shared memory
+    assert plan.fewtok_plan(4, 8192, 8192, False) == plan.FewTokPlan(32, 4)    # two batches per row: x in shared memory
+    assert plan.fewtok_plan(8, 8192, 32768, False) is None           # 8 rows of x exceed shared memory
     assert plan.fewtok_smem_bytes(8, 4096, 16) == 8 * (8192 + 64) + 2 * 16 * 64 * 4
+    assert plan.fewtok_smem_bytes(3, 4096, 32) == 3 * (8192 + 64) + 2 * 32 * 64 * 4
 
 
 def test_hi_lo_split_recovers_fp32_weights_to_16_bits():
