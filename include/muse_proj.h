@@ -71,15 +71,19 @@ int muse_query(int what);
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,
                int* status, const muse_peer_sync_t* peers, void* stream);
 
-/* out[m, N] = x[m, K] . W[N, K]^T for m = 1..16 tokens against a BF16 weight, as a persistent
+/* out[m, N] = x[m, K] . W[N, K]^T for m = 1..16 * tok_split tokens against a BF16 weight, as a persistent
  * streaming walk over W with register-level tensor-core MMAs (no tensor memory, no split-K
  * workspace, bit-reproducible): the regime between muse_gemv1 and muse_skinny_tc. K % 32 == 0; x BF16 with ld_x
  * elements between rows (multiple of 8, 16-byte aligned base), out BF16 with ld_out elements
- * between rows; warps in {16, 32} per CTA, unroll in {1, 2, 4}. Serves the smallest of the m <= 32
+ * between rows; warps in {16, 32} per CTA, unroll in {1, 2, 4} (8 with 16 warps when K <= 4096).
+ * When warps * unroll * 32 >= K the kernel keeps its x fragments in registers; only then may
+ * tok_split be 2..4: the grid is that many interleaved copies of the walk, each multiplying its own
+ * block of 8 or 16 tokens, and W is read from HBM once and a second time from L2. Otherwise
+ * tok_split = 1. Serves the smallest of the m <= 32
  * calls that the reference gives to _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337,
  * :236-257). -5 = x does not fit in shared memory (muse_fewtok_smem_bytes > 227 KB). */
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int* status, void* stream);
+                    int unroll, int tok_split, int* status, void* stream);
 long long muse_fewtok_smem_bytes(int m, int K, int warps);
 
 /* Fill a 128-byte tensor map for a row-major BF16 matrix [rows, cols] at `base` (device pointer,

@@ -30,7 +30,7 @@ SIGNATURES = {
     "muse_skinny_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_nop": (C.c_int, [C.c_void_p]),
     "muse_fewtok_mma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                  C.c_int, C.c_void_p, C.c_void_p]),
+                                  C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "muse_fewtok_smem_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "muse_streamk_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "muse_streamk_max_contrib": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),

@@ -19,7 +19,7 @@ int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, co
                               int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                               int stages, int out_f32, cudaStream_t stream);
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                        int unroll, int* status, cudaStream_t stream);
+                        int unroll, int tok_split, int* status, cudaStream_t stream);
 size_t fewtok_smem_bytes(int m, int K, int warps);
 int streamk_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                         int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int grid, int stages,
@@ -101,8 +101,8 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
 }
 
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int* status, void* stream) {
-  return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, status,
+                    int unroll, int tok_split, int* status, void* stream) {
+  return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, status,
                                    static_cast<cudaStream_t>(stream));
 }
 

@@ -14,9 +14,10 @@
 // x[token g] at the same offset), so the dot products are unchanged. Tokens are the MMA's M (16),
 // weight rows its N (8). Warps reduce through shared memory in a fixed order (deterministic).
 //
-// When one batch of the CTA's loads covers a whole row (K <= 32 * NW * U) and m <= 8, every warp meets
-// the same pieces of K in every group, so its A fragments never change: fewtok_xreg_kernel loads them
-// once from global memory into registers and runs with no shared-memory copy of x at all.
+// When one batch of the CTA's loads covers a whole row (K <= 32 * NW * U), every warp meets the same
+// pieces of K in every group, so its A fragments never change: fewtok_xreg_kernel loads them once from
+// global memory into registers and runs with no shared-memory copy of x at all. Tokens 8..15 double
+// those registers, which a 32-warp CTA only has for U <= 2; 16 warps x 8 loads serve K = 4096 there.
 #include "common.cuh"
 
 namespace muse {
@@ -137,17 +138,28 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 #undef FEWTOK_STAMP
 }
 
-// m <= 8 and K <= 32 * NW * U: one batch per group, A fragments resident in registers (no shared-memory x).
-template <int NW, int U>
+// K <= 32 * NW * U: one batch per group, A fragments resident in registers (no shared-memory x).
+// HI = tokens 8..15 exist. With tok_split > 1 the grid is tok_split interleaved copies of the walk, copy j
+// multiplying tokens [j * TOKS, (j + 1) * TOKS): CTAs c and c + 1 stream the same groups at the same time,
+// so W still leaves HBM once (the second reader finds it in L2) while each SM keeps only its own tokens.
+template <int NW, int U, bool HI>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ x,
                                                               __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
-                                                              int ld_out) {
-  constexpr int OUTS = 64;                       // 8 tokens x 8 rows
+                                                              int ld_out, int tok_split) {
+  constexpr int OUTS = HI ? 128 : 64;            // 8 or 16 tokens x 8 rows
+  constexpr int TOKS = HI ? 16 : 8;
   __shared__ __align__(16) float red[2][NW][OUTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int C = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  const int C = static_cast<int>(gridDim.x) / tok_split, c = static_cast<int>(blockIdx.x) / tok_split;
+  {
+    const int t0 = (static_cast<int>(blockIdx.x) % tok_split) * TOKS;
+    x += static_cast<size_t>(t0) * ld_x;
+    out += static_cast<size_t>(t0) * ld_out;
+    m = m - t0 < TOKS ? m - t0 : TOKS;
+    if (m <= 0) return;
+  }
   const int kblocks = K >> 5;
   const int groups = (N + 7) >> 3;
   const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
@@ -161,23 +173,33 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
   };
   // One register buffer: a group's loads are re-issued into it as soon as its MMAs have read it, and stay
   // in flight across the reduction below. (A second buffer costs 16 registers the 32-warp CTA does not have.)
-  uint4 w[U], xr[U];
+  uint4 w[U], xr[U], xh[HI ? U : 1];
   if (my_groups > 0) load(w, 0);
   {
     const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
 #pragma unroll
     for (int u = 0; u < U; ++u)
       xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (HI) {
+      const uint4* ph = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g + 8 < m ? g + 8 : 0) * ld_x) + q;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        xh[u] = (g + 8 < m && first + u < kblocks) ? __ldg(ph + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+      xh[0] = make_uint4(0u, 0u, 0u, 0u);
+    }
   }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int i = 0; i < my_groups; ++i) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, w[u].x, w[u].y);
-      mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, w[u].z, w[u].w);
+      const uint4 hi = xh[HI ? u : 0];
+      mma_bf16_16816(acc, xr[u].x, hi.x, xr[u].y, hi.y, w[u].x, w[u].y);
+      mma_bf16_16816(acc, xr[u].z, hi.z, xr[u].w, hi.w, w[u].z, w[u].w);
     }
     if (i + 1 < my_groups) load(w, i + 1);
     *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
+    if constexpr (HI) *reinterpret_cast<float2*>(&red[i & 1][warp][(g + 8) * 8 + 2 * q]) = make_float2(acc[2], acc[3]);
     acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
     __syncthreads();   // the buffer written two groups ago is free again once every warp passed this
     if (threadIdx.x < OUTS) {
@@ -229,10 +251,10 @@ static cudaError_t launch_fewtok(const void* W, const void* x, void* out, int m,
   return cudaGetLastError();
 }
 
-template <int NW, int U>
+template <int NW, int U, bool HI>
 static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
-                               cudaStream_t s) {
-  auto kern = fewtok_xreg_kernel<NW, U>;
+                               int tok_split, cudaStream_t s) {
+  auto kern = fewtok_xreg_kernel<NW, U, HI>;
   static int per_sm[64] = {0}, sms[64] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -245,32 +267,48 @@ static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, i
     if (resident < 1) return cudaErrorInvalidConfiguration;
     per_sm[dev] = resident;
   }
-  int grid = sms[dev] * per_sm[dev];
+  int walkers = sms[dev] * per_sm[dev] / tok_split;   // CTAs per copy of the walk
   const int groups = (N + 7) / 8;
-  if (grid > groups) grid = groups;
-  kern<<<grid, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W), reinterpret_cast<const __nv_bfloat16*>(x),
-                                reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out);
+  if (walkers > groups) walkers = groups;
+  if (walkers < 1) return cudaErrorInvalidConfiguration;
+  kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
+                                               reinterpret_cast<const __nv_bfloat16*>(x),
+                                               reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split);
   return cudaGetLastError();
 }
 
 size_t fewtok_smem_bytes(int m, int K, int warps) { return fewtok_smem(K, m, warps); }
 
-// 1..16 tokens, BF16 weight and output; warps in {16, 32}, unroll in {1, 2, 4}. Negative = argument error.
+// Whether (warps, unroll) has a register-resident instantiation for CTAs of `toks` (8 or 16) tokens.
+static bool xreg_serves(int toks, int K, int warps, int unroll) {
+  if (K / 32 > warps * unroll) return false;
+  if (warps == 16) return unroll == 1 || unroll == 2 || unroll == 4 || unroll == 8;
+  if (warps == 32) return unroll == 1 || unroll == 2 || (unroll == 4 && toks <= 8);
+  return false;
+}
+
+// 1..16 tokens, BF16 weight and output; warps in {16, 32}, unroll in {1, 2, 4}, and 8 with 16 warps when
+// that covers a whole row (K <= 4096). Negative = argument error.
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                        int unroll, int* status, cudaStream_t stream) {
+                        int unroll, int tok_split, int* status, cudaStream_t stream) {
   if (!W || !x || !out || !status || N <= 0 || K <= 0) return -1;
-  if (m < 1 || m > 16) return -9;
+  if (tok_split < 1 || tok_split > 4 || m < 1 || m > 16 * tok_split) return -9;
+  const int toks = m <= 8 * tok_split ? 8 : 16;   // tokens per CTA
   if (K % 32 != 0 || ld_x % 8 != 0 || ld_x < K || ld_out < N) return -2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
-  if (fewtok_smem(K, m, warps) > 227 * 1024) return -5;
   cudaError_t e = cudaErrorInvalidValue;
-  if (m <= 8 && K / 32 <= warps * unroll) {   // a whole row per batch: the A fragments stay in registers
-#define MUSE_XREG(NW_, U_) \
-    if (warps == NW_ && unroll == U_) e = launch_xreg<NW_, U_>(W, x, out, m, N, K, ld_x, ld_out, stream);
-    MUSE_XREG(32, 1) MUSE_XREG(32, 2) MUSE_XREG(32, 4) MUSE_XREG(16, 1) MUSE_XREG(16, 2) MUSE_XREG(16, 4)
+  if (xreg_serves(toks, K, warps, unroll)) {   // a whole row per batch: the A fragments stay in registers
+#define MUSE_XREG(NW_, U_, HI_)                                 \
+    if (warps == NW_ && unroll == U_ && (toks > 8) == HI_)      \
+      e = launch_xreg<NW_, U_, HI_>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
+    MUSE_XREG(32, 1, false) MUSE_XREG(32, 2, false) MUSE_XREG(32, 4, false) MUSE_XREG(32, 1, true) MUSE_XREG(32, 2, true)
+    MUSE_XREG(16, 1, false) MUSE_XREG(16, 2, false) MUSE_XREG(16, 4, false) MUSE_XREG(16, 8, false)
+    MUSE_XREG(16, 1, true) MUSE_XREG(16, 2, true) MUSE_XREG(16, 4, true) MUSE_XREG(16, 8, true)
 #undef MUSE_XREG
     return static_cast<int>(e);
   }
+  if (tok_split != 1) return -9;   // the shared-memory path holds all of a call's tokens in one CTA
+  if (fewtok_smem(K, m, warps) > 227 * 1024) return -5;
 #define MUSE_FEWTOK(NW_, U_)                                                                                    \
   if (warps == NW_ && unroll == U_)                                                                             \
     e = m > 8 ? launch_fewtok<NW_, U_, true>(W, x, out, m, N, K, ld_x, ld_out, status, stream)                  \

@@ -25,7 +25,7 @@ import ctypes
 import torch
 
 from . import _capi
-from .plan import DeviceFacts, FewTokPlan, GemvPlan, SkinnyPlan, fewtok_plan, gemv_plan, gemv_valid, skinny_plan
+from .plan import FEWTOK_BUCKETS, DeviceFacts, FewTokPlan, GemvPlan, SkinnyPlan, fewtok_plan, gemv_plan, gemv_valid, skinny_plan
 
 FP32_LAYERS = {"router"}
 # Workspace rule: sized once in prepare() so that every layer at up to this many tokens can split K;
@@ -156,7 +156,7 @@ def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> 
     f32 = layer in FP32_LAYERS
     dev = state["_dev"]
     few = None
-    if not fused and not f32 and m <= 16:
+    if not fused and not f32 and m <= FEWTOK_BUCKETS[-1]:
         few = FewTokPlan(**ov) if ov and "warps" in ov else (None if ov else fewtok_plan(m, n, k, f32, dev))
     if few is not None:
         plan = few
@@ -202,7 +202,7 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None, peers=None) 
     status = state["_status"].data_ptr()
     if isinstance(plan, FewTokPlan):
         _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0),
-                                        plan.warps, plan.unroll, status, stream),
+                                        plan.warps, plan.unroll, plan.tok_split, status, stream),
                     f"muse_fewtok_mma({layer}, m={m}, n={n}, k={k}, {plan})")
         return out
     if isinstance(plan, GemvPlan):

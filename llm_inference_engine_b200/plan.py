@@ -37,8 +37,9 @@ class GemvPlan:
 @dataclass(frozen=True)
 class FewTokPlan:
     """Up to 16 tokens streamed through register-level MMAs (muse_fewtok_mma)."""
-    warps: int    # per CTA: 16 (two CTAs per SM) or 32
+    warps: int    # per CTA: 16 or 32
     unroll: int   # 16-byte loads in flight per lane per batch
+    tok_split: int = 1   # interleaved copies of the walk, each with its own block of 8 or 16 tokens
 
 
 @dataclass(frozen=True)
@@ -67,17 +68,25 @@ TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int, bool]] = {
     (4096, 1024, False): (1, 4, False),    # unpooler 3.5 us
     (256, 4096, True): (8, 4, False),      # router 2.8 us
 }
-# Same protocol: (n, k, token bucket 1, 8 or 16) -> (warps, unroll) where the register-MMA walk beats the
+# Same protocol: (n, k, token bucket) -> (warps, unroll[, tok_split]) where the register-MMA walk beats the
 # alternative (the figure after the slash: the GEMV in bucket 1, else the TMEM kernel). warps * unroll
-# >= K / 32 with m <= 8 selects its variant that keeps x in registers.
-TUNED_FEWTOK: dict[tuple[int, int, int], tuple[int, int]] = {
+# >= K / 32 selects its variant that keeps x in registers; tok_split copies of that walk share W through
+# L2, which pays for the small weights only.
+FEWTOK_BUCKETS = (1, 8, 16, 32, 64)
+TUNED_FEWTOK: dict[tuple[int, int, int], tuple[int, ...]] = {
     (12288, 4096, 1): (32, 4),    # qkv_gate 17.6 us / 18.1
     (12288, 4096, 8): (32, 4),    # 18.1-18.4 / 20.1-20.4
+    (12288, 4096, 16): (16, 8),   # 19.8 / 21.4
     (4096, 4096, 8): (32, 4),     # o 8.1-8.2 / 9.8-10.0
+    (4096, 4096, 16): (16, 8),    # 9.7 / 10.1
     (1024, 4096, 8): (32, 4),     # pooler 4.2-4.5 / 6.8-7.0
     (1024, 4096, 16): (32, 4),    # 4.5 / 7.1
+    (1024, 4096, 32): (16, 8, 2),  # 6.1 / 7.5
+    (1024, 4096, 64): (16, 8, 4),  # 7.8 / 8.6
     (4096, 1024, 8): (16, 2),     # unpooler 3.9 / 6.1-6.2
-    (4096, 1024, 16): (16, 2),    # 4.75 / 6.4
+    (4096, 1024, 16): (16, 2),    # 4.2 / 6.4
+    (4096, 1024, 32): (16, 2, 2),  # 5.4 / 7.0
+    (4096, 1024, 64): (16, 2, 4),  # 7.2 / 9.5
 }
 FEWTOK_X_PAD = 64
 # Same protocol: (n, k, hilo, token bucket) -> (ntok, cluster, groups, stages). The bucket is the
@@ -149,9 +158,9 @@ def fewtok_smem_bytes(m: int, k: int, warps: int) -> int:
 def fewtok_plan(m: int, n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) -> FewTokPlan | None:
     """The register-MMA plan of a shape that gains from it, else None (TMEM kernel). Tuned shapes come
     from the table; others take it at m <= 8 when the weight has enough 8-row groups to occupy most SMs."""
-    if w_is_f32 or not 1 <= m <= 16 or k % 32:
+    if w_is_f32 or not 1 <= m <= FEWTOK_BUCKETS[-1] or k % 32:
         return None
-    tuned = TUNED_FEWTOK.get((n, k, 1 if m == 1 else 16 if m > 8 else 8))
+    tuned = TUNED_FEWTOK.get((n, k, next(b for b in FEWTOK_BUCKETS if b >= m)))
     if tuned is None:
         if m == 1 or m > 8 or (n + 7) // 8 < dev.sms * 3 // 4:
             return None

@@ -266,20 +266,24 @@ def test_streamk_entry_point_matches_oracle_and_is_bit_stable(dev, case):
     assert all(torch.equal(outs[0], o) for o in outs[1:])
 
 
-FEWTOK_CASES = [  # (m, n, k, warps, unroll)
+FEWTOK_CASES = [  # (m, n, k, warps, unroll) + optional tok_split
     (2, 12288, 4096, 16, 4), (8, 12288, 4096, 32, 4), (16, 4096, 1024, 16, 2), (3, 1001, 4096, 32, 1), (9, 520, 2080, 16, 2),
     (1, 8, 32, 16, 1), (5, 3, 64, 32, 4), (13, 1024, 4096, 32, 4), (7, 300, 8192, 16, 4),
+    (16, 12288, 4096, 16, 8), (9, 4093, 1024, 16, 2), (12, 1000, 2048, 32, 2), (5, 4096, 4096, 16, 8), (11, 777, 3072, 16, 8),
+    (32, 12288, 4096, 16, 8, 2), (16, 12288, 4096, 32, 4, 2), (27, 1001, 4096, 32, 4, 4), (19, 4096, 1024, 16, 2, 2),
+    (40, 300, 2048, 16, 4, 3), (3, 520, 1024, 32, 1, 2),
 ]
 
 
-@pytest.mark.parametrize("case", FEWTOK_CASES, ids=lambda c: "m{}_n{}_k{}_w{}u{}".format(*c))
+@pytest.mark.parametrize("case", FEWTOK_CASES, ids=lambda c: "m{}_n{}_k{}_w{}u{}".format(*c) + ("_t%d" % c[5] if len(c) > 5 else ""))
 def test_fewtok_entry_point_matches_oracle_and_is_bit_stable(dev, case):
     """muse_fewtok_mma (register-level MMAs, 1..16 tokens) through the C ABI: FP64 product within the
     BF16 tolerance, ragged N (rows not a multiple of 8), strided x and out, columns beyond n untouched,
     identical bits on repeated calls (the warps' partial sums are added in a fixed order)."""
     from llm_inference_engine_b200 import _capi
 
-    m, n, k, warps, unroll = case
+    m, n, k, warps, unroll = case[:5]
+    tok_split = case[5] if len(case) > 5 else 1
     lib = _capi.load()
     g = torch.Generator(device=dev).manual_seed(m * 11 + n)
     w = (torch.randn((n, k), generator=g, device=dev) * 0.02).to(torch.bfloat16)
@@ -290,7 +294,8 @@ def test_fewtok_entry_point_matches_oracle_and_is_bit_stable(dev, case):
     for _ in range(3):
         out = torch.full((m, n + 5), 3.0, device=dev, dtype=torch.bfloat16)
         _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0), warps,
-                                        unroll, status.data_ptr(), torch.cuda.current_stream(dev).cuda_stream), "muse_fewtok_mma")
+                                        unroll, tok_split, status.data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
+                    "muse_fewtok_mma")
         torch.cuda.synchronize(dev)
         outs.append(out)
     assert int(status.item()) == 0
@@ -310,9 +315,11 @@ def test_fewtok_rejections(dev):
     x = torch.zeros((17, 4096), device=dev, dtype=torch.bfloat16)
     out = torch.zeros((17, 64), device=dev, dtype=torch.bfloat16)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
-    call = lambda m, n, k, ldx, ldo, warps, unroll: lib.muse_fewtok_mma(
-        w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, ldx, ldo, warps, unroll, status.data_ptr(), None)
-    assert call(17, 64, 4096, 4096, 64, 16, 4) == -9        # more than 16 tokens
+    call = lambda m, n, k, ldx, ldo, warps, unroll, split=1: lib.muse_fewtok_mma(
+        w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, ldx, ldo, warps, unroll, split, status.data_ptr(), None)
+    assert call(17, 64, 4096, 4096, 64, 16, 4) == -9        # more than 16 tokens per copy of the walk
+    assert call(17, 64, 4096, 4096, 64, 16, 4, split=2) == -9   # x in shared memory: one CTA holds all tokens
+    assert call(4, 64, 4096, 4096, 64, 32, 4, split=5) == -9
     assert call(4, 64, 4080, 4096, 64, 16, 4) == -2         # K not a multiple of 32
     assert call(4, 64, 4096, 4096, 32, 16, 4) == -2         # out rows shorter than n
     assert call(4, 64, 4096, 4096, 64, 8, 4) != 0           # unsupported CTA size

@@ -75,17 +75,23 @@ def test_tuned_entries_are_launchable():
         assert (p.ntok, p.cluster, p.groups, p.stages) == (ntok, cluster, groups, min(stages, longest))
     for (n, k, f32), (wpr, unroll, persistent) in plan.TUNED_GEMV.items():
         assert plan.gemv_valid(k, f32, wpr) and unroll in (1, 2, 4, 8) and (wpr == 1 or not persistent)
-    for (n, k, bucket), (warps, unroll) in plan.TUNED_FEWTOK.items():
-        assert bucket in (1, 8, 16) and warps in (16, 32) and unroll in (1, 2, 4) and k % 32 == 0
-        assert plan.fewtok_plan(bucket, n, k, False) == plan.FewTokPlan(warps, unroll)
+    for (n, k, bucket), tuned in plan.TUNED_FEWTOK.items():
+        warps, unroll, tok_split = (*tuned, 1)[:3]
+        assert bucket in plan.FEWTOK_BUCKETS and warps in (16, 32) and unroll in (1, 2, 4, 8) and k % 32 == 0
+        assert unroll < 8 or (warps == 16 and k // 32 <= 128)   # 8 loads per lane exist only with x in registers
+        assert bucket <= 16 * tok_split
+        if tok_split > 1 or bucket > 8:   # these need x in registers: a whole row per batch
+            assert warps * unroll >= k // 32 or bucket <= 16
+        assert plan.fewtok_plan(bucket, n, k, False) == plan.FewTokPlan(warps, unroll, tok_split)
 
 
 def test_fewtok_plan_only_where_it_applies():
     assert plan.fewtok_plan(1, 4096, 4096, False) is None            # one token, untuned: the GEMV
     assert plan.fewtok_plan(8, 256, 4096, True) is None              # FP32 router weights
-    assert plan.fewtok_plan(17, 1024, 4096, False) is None           # more than one MMA of tokens
+    assert plan.fewtok_plan(17, 4096, 4096, False) is None           # more than one MMA of tokens, untuned
+    assert plan.fewtok_plan(65, 1024, 4096, False) is None
     assert plan.fewtok_plan(4, 12288, 4100, False) is None           # K not in whole 32-element pieces
-    assert plan.fewtok_plan(16, 12288, 4096, False) is None          # untuned above 8 tokens: TMEM kernel
+    assert plan.fewtok_plan(16, 8192, 4096, False) is None           # untuned above 8 tokens: TMEM kernel
     assert plan.fewtok_plan(4, 512, 4096, False) is None             # too few row groups to occupy the SMs
     assert plan.fewtok_plan(4, 8192, 2048, False) == plan.FewTokPlan(16, 4)
     assert plan.fewtok_plan(4, 8192, 512, False) == plan.FewTokPlan(16, 1)
