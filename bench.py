@@ -288,6 +288,8 @@ def kernel_family(h: Harness, state, layer: str, m: int, n_local: int, k: int) -
     plan = h.proj.plan_for(state, layer, m, n_local, k, fused=h.world > 1 and h.fused is not None)
     if isinstance(plan, GemvPlan):
         return "gemv1_rows" if plan.persistent else "gemv1"
+    if isinstance(plan, FewTokPlan) and layer in FP32_LAYERS:
+        return f"fewtok_xreg_f32<{plan.warps},{plan.unroll}>"
     if isinstance(plan, FewTokPlan):
         name = "fewtok_xreg" if plan.warps * plan.unroll * 32 >= k else "fewtok_mma"
         return f"{name}<{plan.warps},{plan.unroll},{'true' if m > 8 * plan.tok_split else 'false'}>"
@@ -333,7 +335,9 @@ def case_table(h: Harness, layers, steps: int, warmup: int, peak: float, only=No
 
 def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
     """The same six calls through the public API from HOST buffers: per call, x is copied from pinned
-    host memory, kernel_fn() runs, and the result is copied back to pinned host memory and waited for."""
+    host memory, the projection runs, and the result is copied back to pinned host memory and waited
+    for. On one GPU that is kernel_fn_host() (staging copies and launch through the C ABI); column-parallel
+    it is torch copies around the group's kernel_fn()."""
     n, k = LAYERS[WORKLOAD_LAYER]
     xs_host = [make_x(WORKLOAD_LAYER, m, "cpu", 1000 + m).pin_memory() for m in WORKLOAD_TOKENS]
     outs_host = [torch.empty((m, n), dtype=torch.bfloat16).pin_memory() for m in WORKLOAD_TOKENS]
@@ -341,8 +345,13 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
     h2d = sum(x.numel() * 2 for x in xs_host)
     d2h = sum(o.numel() * 2 for o in outs_host)
 
+    cfgs = [{"m": m, "n": n, "k": k, "layer": WORKLOAD_LAYER} for m in WORKLOAD_TOKENS]
+
     def one_step():
         for j, (xh, oh) in enumerate(zip(xs_host, outs_host)):
+            if h.world == 1:
+                h.proj.kernel_fn_host({"x": xh, "config": cfgs[j]}, states[j], out=oh)
+                continue
             xd = xh.to(h.device, non_blocking=True)
             out = h.call(WORKLOAD_LAYER, xd, states[j])
             oh.copy_(out, non_blocking=True)
@@ -359,7 +368,8 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
         dt = time.perf_counter() - t0
     us = h.max_over_ranks(dt * 1e6 / (steps * len(WORKLOAD_TOKENS)))
     return {"value": us, "unit": "us/call", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "how": "wall clock around pinned-host x -> device, kernel_fn(), result -> pinned host, stream sync, per call"}
+            "how": "wall clock around pinned-host x -> device, the projection, result -> pinned host, stream sync, per call; "
+                   + ("kernel_fn_host()" if h.world == 1 else "torch copies around the column-parallel kernel_fn()")}
 
 
 def load_traffic() -> dict:

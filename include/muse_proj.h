@@ -86,6 +86,23 @@ int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K
                     int unroll, int tok_split, int* status, void* stream);
 long long muse_fewtok_smem_bytes(int m, int K, int warps);
 
+/* The same walk over an FP32 weight with FP32 output (the MoE router) for m = 1..8 * tok_split tokens:
+ * the kernel reads W as FP32 once and splits every element in registers into BF16 hi = bf16(w) and
+ * lo = bf16(w - hi), both multiplied into one FP32 accumulator -- the arithmetic of the reference's
+ * prepare() split and _router_kernel (best_submissions/muse_bf16_proj.py:346-349, :260-287) without
+ * the pre-split copies. 16 warps per CTA, unroll in {2, 4, 8} with K <= 512 * unroll (x stays in
+ * registers), K % 32 == 0; x BF16, ld_x % 8 == 0. */
+int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
+                    int tok_split, void* stream);
+
+/* Staging for callers whose activations live in HOST memory (page-locked for the copies to be
+ * asynchronous): x goes host -> device on `stream` before the projection is launched there, and
+ * muse_copy_d2h_sync brings the result back and returns once it has landed (it synchronises the
+ * stream). Positive = CUDA error. No counterpart in the reference, whose harness hands kernel_fn
+ * device tensors (best_submissions/muse_bf16_proj.py:369-372). */
+int muse_copy_h2d_async(void* dst_device, const void* src_host, long long bytes, void* stream);
+int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, void* stream);
+
 /* Fill a 128-byte tensor map for a row-major BF16 matrix [rows, cols] at `base` (device pointer,
  * 16-byte aligned) with `row_stride_bytes` between rows (multiple of 16), delivering boxes of
  * [box_rows, 64 columns] with the 128-byte shared-memory swizzle and zero fill outside the matrix.

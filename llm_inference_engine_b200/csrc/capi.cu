@@ -21,6 +21,8 @@ int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, co
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
                         int unroll, int tok_split, int* status, cudaStream_t stream);
 size_t fewtok_smem_bytes(int m, int K, int warps);
+int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
+                        int tok_split, cudaStream_t stream);
 int streamk_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                         int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int grid, int stages,
                         int out_f32, const PeerSync* peers, cudaStream_t stream);
@@ -100,10 +102,29 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
                               reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 
+int muse_copy_h2d_async(void* dst_device, const void* src_host, long long bytes, void* stream) {
+  if (!dst_device || !src_host || bytes < 0) return -1;
+  return static_cast<int>(cudaMemcpyAsync(dst_device, src_host, static_cast<size_t>(bytes), cudaMemcpyHostToDevice,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
+int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, void* stream) {
+  if (!dst_host || !src_device || bytes < 0) return -1;
+  cudaError_t e = cudaMemcpyAsync(dst_host, src_device, static_cast<size_t>(bytes), cudaMemcpyDeviceToHost,
+                                  static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+}
+
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
                     int unroll, int tok_split, int* status, void* stream) {
   return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, status,
                                    static_cast<cudaStream_t>(stream));
+}
+
+int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
+                    int tok_split, void* stream) {
+  return muse::fewtok_f32_dispatch(W, x, out, m, N, K, ld_x, ld_out, unroll, tok_split, static_cast<cudaStream_t>(stream));
 }
 
 long long muse_fewtok_smem_bytes(int m, int K, int warps) {

@@ -213,6 +213,89 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
   }
 }
 
+// The same walk over FP32 weights (the MoE router): each lane loads 32 bytes (8 FP32) per piece, splits
+// them in registers into BF16 hi = bf16(w) and lo = bf16(w - hi) -- the split the reference's prepare()
+// stores (best_submissions/muse_bf16_proj.py:346-349) -- and feeds both to MMAs on one FP32
+// accumulator (its _router_kernel, :260-287), so W is read once, as FP32, with no pre-split copy.
+// Up to 8 tokens per CTA (tok_split copies for more); output FP32.
+template <int NW, int U>
+__global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* __restrict__ W,
+                                                                  const __nv_bfloat16* __restrict__ x,
+                                                                  float* __restrict__ out, int m, int N, int K, int ld_x,
+                                                                  int ld_out, int tok_split) {
+  constexpr int OUTS = 64, TOKS = 8;
+  __shared__ __align__(16) float red[2][NW][OUTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int C = static_cast<int>(gridDim.x) / tok_split, c = static_cast<int>(blockIdx.x) / tok_split;
+  {
+    const int t0 = (static_cast<int>(blockIdx.x) % tok_split) * TOKS;
+    x += static_cast<size_t>(t0) * ld_x;
+    out += static_cast<size_t>(t0) * ld_out;
+    m = m - t0 < TOKS ? m - t0 : TOKS;
+    if (m <= 0) return;
+  }
+  const int kblocks = K >> 5;
+  const int groups = (N + 7) >> 3;
+  const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
+  const int first = warp * U;
+  uint4 w[2 * U], xr[U];
+  auto load = [&](int i) {
+    int row = (c + i * C) * 8 + g;
+    row = row < N ? row : N - 1;
+    const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K) + 2 * q;   // 8 FP32 = two vectors
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool ok = first + u < kblocks;
+      w[2 * u] = ok ? ldg_stream16(p + (first + u) * 8) : make_uint4(0u, 0u, 0u, 0u);
+      w[2 * u + 1] = ok ? ldg_stream16(p + (first + u) * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  if (my_groups > 0) load(0);
+  {
+    const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  // (a, b) -> BF16 pair of the hi halves (a in the low 16 bits) and of the lo halves.
+  auto split = [](uint32_t a_bits, uint32_t b_bits, uint32_t& hi, uint32_t& lo) {
+    const float a = __uint_as_float(a_bits), b = __uint_as_float(b_bits);
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    const float ra = a - __uint_as_float(hi << 16), rb = b - __uint_as_float(hi & 0xffff0000u);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(ra, rb);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+  };
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = 0; i < my_groups; ++i) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+      split(w[2 * u].x, w[2 * u].y, h0, l0);
+      split(w[2 * u].z, w[2 * u].w, h1, l1);
+      split(w[2 * u + 1].x, w[2 * u + 1].y, h2, l2);
+      split(w[2 * u + 1].z, w[2 * u + 1].w, h3, l3);
+      mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, h0, h1);
+      mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, h2, h3);
+      mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, l0, l1);
+      mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, l2, l3);
+    }
+    if (i + 1 < my_groups) load(i + 1);
+    *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+    __syncthreads();
+    if (threadIdx.x < OUTS) {
+      float sum = 0.f;
+#pragma unroll 8
+      for (int wv = 0; wv < NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
+      const int t = threadIdx.x >> 3;
+      const int row = (c + i * C) * 8 + (threadIdx.x & 7);
+      if (t < m && row < N) out[static_cast<size_t>(t) * ld_out + row] = sum;
+    }
+  }
+}
+
 unsigned long long* skinny_get_trace();
 
 static size_t fewtok_smem(int K, int m, int nw) {
@@ -275,6 +358,45 @@ static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, i
                                                reinterpret_cast<const __nv_bfloat16*>(x),
                                                reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split);
   return cudaGetLastError();
+}
+
+template <int NW, int U>
+static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
+                                   int tok_split, cudaStream_t s) {
+  auto kern = fewtok_xreg_f32_kernel<NW, U>;
+  static int per_sm[64] = {0}, sms[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!per_sm[dev]) {
+    if ((e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    int resident = 0;
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, NW * 32, 0)) != cudaSuccess) return e;
+    if (resident < 1) return cudaErrorInvalidConfiguration;
+    per_sm[dev] = resident;
+  }
+  int walkers = sms[dev] * per_sm[dev] / tok_split;
+  const int groups = (N + 7) / 8;
+  if (walkers > groups) walkers = groups;
+  if (walkers < 1) return cudaErrorInvalidConfiguration;
+  kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), reinterpret_cast<const __nv_bfloat16*>(x),
+                                               reinterpret_cast<float*>(out), m, N, K, ld_x, ld_out, tok_split);
+  return cudaGetLastError();
+}
+
+// FP32 weight and output, 1..8 * tok_split tokens, 16 warps, unroll in {2, 4, 8} with K <= 512 * unroll.
+int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
+                        int tok_split, cudaStream_t stream) {
+  if (!W || !x || !out || N <= 0 || K <= 0) return -1;
+  if (tok_split < 1 || tok_split > 4 || m < 1 || m > 8 * tok_split) return -9;
+  if (K % 32 != 0 || ld_x % 8 != 0 || ld_x < K || ld_out < N || K / 32 > 16 * unroll) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
+  cudaError_t e = cudaErrorInvalidValue;
+  if (unroll == 8) e = launch_xreg_f32<16, 8>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
+  else if (unroll == 4) e = launch_xreg_f32<16, 4>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
+  else if (unroll == 2) e = launch_xreg_f32<16, 2>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
+  return static_cast<int>(e);
 }
 
 size_t fewtok_smem_bytes(int m, int K, int warps) { return fewtok_smem(K, m, warps); }

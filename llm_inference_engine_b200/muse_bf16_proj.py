@@ -156,7 +156,7 @@ def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> 
     f32 = layer in FP32_LAYERS
     dev = state["_dev"]
     few = None
-    if not fused and not f32 and m <= FEWTOK_BUCKETS[-1]:
+    if not fused and m <= FEWTOK_BUCKETS[-1]:
         few = FewTokPlan(**ov) if ov and "warps" in ov else (None if ov else fewtok_plan(m, n, k, f32, dev))
     if few is not None:
         plan = few
@@ -196,26 +196,78 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None, peers=None) 
         out = torch.empty((m, n), device=x.device, dtype=torch.float32 if f32 else torch.bfloat16)
     elif out.shape[0] != m or out.shape[1] < n + (peers.col0 if peers is not None else 0) or out.stride(1) != 1 or out.dtype != (torch.float32 if f32 else torch.bfloat16):
         raise ValueError("out must be [m, >= n], unit column stride, BF16 (FP32 for the router)")
-    lib = state.get("_lib") or _capi.load()
     stream = torch.cuda.current_stream(x.device).cuda_stream
     plan = plan_for(state, layer, m, n, k, fused=peers is not None)
+    _launch(state, layer, plan, m, n, k, x.data_ptr(), x.stride(0) if m > 1 else k, out.data_ptr(), out.stride(0), peers,
+            stream, x.device)
+    return out
+
+
+def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: int, out_ptr: int, ld_out: int, peers,
+            stream: int, device) -> None:
+    """One C-ABI call: the kernel `plan` names, on validated arguments."""
+    lib = _capi.load()
+    f32 = layer in FP32_LAYERS
+    w = state[layer]
     status = state["_status"].data_ptr()
+    if isinstance(plan, FewTokPlan) and f32:
+        _capi.check(lib.muse_fewtok_f32(w.data_ptr(), x_ptr, out_ptr, m, n, k, ld_x, ld_out, plan.unroll, plan.tok_split, stream),
+                    f"muse_fewtok_f32({layer}, m={m}, n={n}, k={k}, {plan})")
+        return
     if isinstance(plan, FewTokPlan):
-        _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0),
-                                        plan.warps, plan.unroll, plan.tok_split, status, stream),
+        _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x_ptr, out_ptr, m, n, k, ld_x, ld_out, plan.warps, plan.unroll,
+                                        plan.tok_split, status, stream),
                     f"muse_fewtok_mma({layer}, m={m}, n={n}, k={k}, {plan})")
-        return out
+        return
     if isinstance(plan, GemvPlan):
-        _capi.check(lib.muse_gemv1(w.data_ptr(), x.data_ptr(), out.data_ptr(), n, k, int(f32), plan.wpr, plan.unroll,
+        _capi.check(lib.muse_gemv1(w.data_ptr(), x_ptr, out_ptr, n, k, int(f32), plan.wpr, plan.unroll,
                                    int(plan.persistent), status, _peer_ptr(peers), stream), f"muse_gemv1({layer}, n={n}, k={k})")
-        return out
+        return
     maps = _weight_maps(state, layer, n)
     ws_ptr = cnt_ptr = None
     if plan.groups > 1:
-        ws, cnt = _stream_workspace(state, x.device)
+        ws, cnt = _stream_workspace(state, device)
         ws_ptr, cnt_ptr = ws.data_ptr(), cnt.data_ptr()
-    _capi.check(lib.muse_skinny_tc(maps[0].ptr, maps[1].ptr if f32 else None, x.data_ptr(), out.data_ptr(), ws_ptr,
-                                   cnt_ptr, status, m, n, k, x.stride(0) if m > 1 else k, out.stride(0), plan.ntok,
-                                   plan.cluster, plan.groups, plan.stages, int(f32), _peer_ptr(peers), stream),
+    _capi.check(lib.muse_skinny_tc(maps[0].ptr, maps[1].ptr if f32 else None, x_ptr, out_ptr, ws_ptr, cnt_ptr, status, m, n, k,
+                                   ld_x, ld_out, plan.ntok, plan.cluster, plan.groups, plan.stages, int(f32),
+                                   _peer_ptr(peers), stream),
                 f"muse_skinny_tc({layer}, m={m}, n={n}, k={k}, {plan})")
+
+
+def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Tensor:
+    """kernel_fn for a caller whose activations live in HOST memory: `data["x"]` is a contiguous BF16
+    [m, K] CPU tensor (page-locked for an asynchronous copy), the result is a CPU tensor (`out` if
+    given: contiguous [m, n], page-locked), complete when the call returns. x is staged into a device
+    buffer kept per (layer, m, n), the projection runs on the current stream, and the result is copied
+    back and waited for: three C-ABI calls, no allocation after the first call of a shape. Beyond the
+    reference, whose harness owns the transfers (best_submissions/muse_bf16_proj.py:369-372)."""
+    x, cfg = data["x"], data["config"]
+    layer, n = cfg["layer"], int(cfg["n"])
+    if layer not in state or layer.startswith("_"):
+        raise KeyError(f"unknown layer {layer!r}")
+    w = state[layer]
+    if x.is_cuda or x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+        raise TypeError("x must be a contiguous BF16 [m, K] CPU tensor")
+    m, k = x.shape
+    if k != w.shape[1] or not 0 < n <= w.shape[0] or m < 1:
+        raise ValueError(f"{layer}: x {tuple(x.shape)} / n={n} do not fit W {tuple(w.shape)}")
+    f32 = layer in FP32_LAYERS
+    odt = torch.float32 if f32 else torch.bfloat16
+    key = (layer, m, n)
+    slot = state.setdefault("_host_slots", {}).get(key)
+    if slot is None:
+        slot = (torch.empty((m, k), device=w.device, dtype=torch.bfloat16), torch.empty((m, n), device=w.device, dtype=odt),
+                plan_for(state, layer, m, n, k))
+        state["_host_slots"][key] = slot
+    x_dev, out_dev, plan = slot
+    if out is None:
+        out = torch.empty((m, n), dtype=odt, pin_memory=True)
+    elif out.is_cuda or out.dtype != odt or tuple(out.shape) != (m, n) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous CPU [m, n] tensor, BF16 (FP32 for the router)")
+    lib = _capi.load()
+    stream = torch.cuda.current_stream(w.device).cuda_stream
+    _capi.check(lib.muse_copy_h2d_async(x_dev.data_ptr(), x.data_ptr(), m * k * 2, stream), "muse_copy_h2d_async")
+    _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out_dev.data_ptr(), n, None, stream, w.device)
+    _capi.check(lib.muse_copy_d2h_sync(out.data_ptr(), out_dev.data_ptr(), out.numel() * out.element_size(), stream),
+                "muse_copy_d2h_sync")
     return out

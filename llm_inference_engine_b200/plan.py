@@ -88,6 +88,13 @@ TUNED_FEWTOK: dict[tuple[int, int, int], tuple[int, ...]] = {
     (4096, 1024, 32): (16, 2, 2),  # 5.4 / 7.0
     (4096, 1024, 64): (16, 2, 4),  # 7.2 / 9.5
 }
+# FP32 weights (the router), split to BF16 hi + lo in registers: (n, k, token bucket) -> (unroll, tok_split);
+# 16 warps, up to 8 tokens per copy of the walk.
+TUNED_FEWTOK_F32: dict[tuple[int, int, int], tuple[int, int]] = {
+    (256, 4096, 8): (8, 1),     # router 5.4-5.9 us / 6.4-6.5
+    (256, 4096, 16): (8, 2),    # 6.1 / 6.8
+    (256, 4096, 32): (8, 4),    # 6.2 / 7.0
+}
 FEWTOK_X_PAD = 64
 # Same protocol: (n, k, hilo, token bucket) -> (ntok, cluster, groups, stages). The bucket is the
 # smallest of NTOK_CHOICES holding m; ntok may be smaller (several token tiles: small weights gain
@@ -158,8 +165,11 @@ def fewtok_smem_bytes(m: int, k: int, warps: int) -> int:
 def fewtok_plan(m: int, n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) -> FewTokPlan | None:
     """The register-MMA plan of a shape that gains from it, else None (TMEM kernel). Tuned shapes come
     from the table; others take it at m <= 8 when the weight has enough 8-row groups to occupy most SMs."""
-    if w_is_f32 or not 1 <= m <= FEWTOK_BUCKETS[-1] or k % 32:
+    if not 1 <= m <= FEWTOK_BUCKETS[-1] or k % 32:
         return None
+    if w_is_f32:
+        tuned = TUNED_FEWTOK_F32.get((n, k, next(b for b in FEWTOK_BUCKETS if b >= m))) if m > 1 else None
+        return FewTokPlan(16, tuned[0], tuned[1]) if tuned else None
     tuned = TUNED_FEWTOK.get((n, k, next(b for b in FEWTOK_BUCKETS if b >= m)))
     if tuned is None:
         if m == 1 or m > 8 or (n + 7) // 8 < dev.sms * 3 // 4:

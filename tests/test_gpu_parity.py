@@ -326,3 +326,60 @@ def test_fewtok_rejections(dev):
     assert call(16, 64, 16384, 16384, 64, 32, 4) == -5      # 16 rows of x do not fit in shared memory
     torch.cuda.synchronize(dev)
     assert int(status.item()) == 0
+
+
+def test_host_buffer_entry_point_matches_device_path(proj, dev, target_setup):
+    """kernel_fn_host (x and the result in page-locked host memory) returns the bits of kernel_fn for the
+    GEMV, register-MMA and TMEM plans, reuses its staging buffers, and rejects device tensors."""
+    _, state = target_setup
+    g = torch.Generator().manual_seed(99)
+    for layer, m, n, k in (("qkv_gate", 1, 12288, 4096), ("qkv_gate", 8, 12288, 4096), ("qkv_gate", 32, 12288, 4096),
+                           ("router", 8, 256, 4096), ("unpooler", 5, 2048, 1024)):
+        cfg = {"m": m, "n": n, "k": k, "layer": layer}
+        x = torch.randn((m, k), generator=g).to(torch.bfloat16).pin_memory()
+        want = proj.kernel_fn({"x": x.to(dev), "config": cfg}, state).cpu()
+        got = proj.kernel_fn_host({"x": x, "config": cfg}, state)
+        assert not got.is_cuda and got.dtype == want.dtype and torch.equal(got, want)
+        out = torch.empty_like(want).pin_memory()
+        again = proj.kernel_fn_host({"x": x, "config": cfg}, state, out=out)
+        assert again is out and torch.equal(out, want)
+    assert len(state["_host_slots"]) == 5
+    with pytest.raises(TypeError):
+        proj.kernel_fn_host({"x": x.to(dev), "config": cfg}, state)
+    proj.check_status(state)
+
+
+FEWTOK_F32_CASES = [  # (m, n, k, unroll, tok_split)
+    (8, 256, 4096, 8, 1), (32, 256, 4096, 8, 4), (1, 256, 4096, 8, 1), (5, 100, 1024, 2, 1), (20, 77, 2048, 4, 3), (13, 1003, 512, 2, 2),
+]
+
+
+@pytest.mark.parametrize("case", FEWTOK_F32_CASES, ids=lambda c: "m{}_n{}_k{}_u{}t{}".format(*c))
+def test_fewtok_f32_entry_point_meets_the_router_tolerance(dev, case):
+    """muse_fewtok_f32 (FP32 weights split to BF16 hi + lo in registers) through the C ABI: within the
+    router's 1e-5 relative L2 of the FP64 product, identical bits on repeated calls, ragged N, strided
+    x and out, columns beyond n untouched."""
+    from llm_inference_engine_b200 import _capi
+
+    m, n, k, unroll, tok_split = case
+    lib = _capi.load()
+    g = torch.Generator(device=dev).manual_seed(m * 13 + n)
+    w = torch.randn((n, k), generator=g, device=dev) * 0.02
+    x = torch.randn((m, k + 8), generator=g, device=dev).to(torch.bfloat16)[:, :k]
+    ref = x.double() @ w.double().T
+    outs = []
+    for _ in range(3):
+        out = torch.full((m, n + 3), 3.0, device=dev, dtype=torch.float32)
+        _capi.check(lib.muse_fewtok_f32(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0), unroll,
+                                        tok_split, torch.cuda.current_stream(dev).cuda_stream), "muse_fewtok_f32")
+        torch.cuda.synchronize(dev)
+        outs.append(out)
+    assert bool((outs[0][:, n:] == 3.0).all())
+    err = float((outs[0][:, :n].double() - ref).norm() / ref.norm())
+    assert err < 1e-5, err
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    call = lambda m_, k_, unroll_, split_: lib.muse_fewtok_f32(w.data_ptr(), x.data_ptr(), outs[0].data_ptr(), m_, n, k_,
+                                                               x.stride(0), outs[0].stride(0), unroll_, split_, None)
+    assert call(8 * tok_split + 1, k, unroll, tok_split) == -9     # more than 8 tokens per copy of the walk
+    assert call(m, k, 1, tok_split) != 0                           # a row does not fit one batch of loads
+    assert call(m, k, unroll, 5) == -9

@@ -85,9 +85,18 @@ def test_tuned_entries_are_launchable():
         assert plan.fewtok_plan(bucket, n, k, False) == plan.FewTokPlan(warps, unroll, tok_split)
 
 
+def test_fewtok_f32_table_is_consistent():
+    for (n, k, bucket), (unroll, tok_split) in plan.TUNED_FEWTOK_F32.items():
+        assert bucket in plan.FEWTOK_BUCKETS and unroll in (2, 4, 8) and k % 32 == 0 and k // 32 <= 16 * unroll
+        assert bucket <= 8 * tok_split <= 32
+        assert plan.fewtok_plan(bucket, n, k, True) == plan.FewTokPlan(16, unroll, tok_split)
+    assert plan.fewtok_plan(1, 256, 4096, True) is None    # one token: the GEMV
+    assert plan.fewtok_plan(64, 256, 4096, True) is None
+
+
 def test_fewtok_plan_only_where_it_applies():
     assert plan.fewtok_plan(1, 4096, 4096, False) is None            # one token, untuned: the GEMV
-    assert plan.fewtok_plan(8, 256, 4096, True) is None              # FP32 router weights
+    assert plan.fewtok_plan(8, 512, 4096, True) is None              # FP32 weights, untuned shape
     assert plan.fewtok_plan(17, 4096, 4096, False) is None           # more than one MMA of tokens, untuned
     assert plan.fewtok_plan(65, 1024, 4096, False) is None
     assert plan.fewtok_plan(4, 12288, 4100, False) is None           # K not in whole 32-element pieces
