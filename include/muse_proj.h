@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 8
+#define MUSE_PROJ_ABI_VERSION 9
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -79,11 +79,12 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
  * When warps * unroll * 32 >= K the kernel keeps its x fragments in registers; only then may
  * tok_split be 2..4: the grid is that many interleaved copies of the walk, each multiplying its own
  * block of 8 or 16 tokens, and W is read from HBM once and a second time from L2. Otherwise
- * tok_split = 1. Serves the smallest of the m <= 32
+ * tok_split = 1. `peers` (NULL on one GPU) makes the call column-parallel as in muse_gemv1; only the
+ * register-resident form supports it (-8 otherwise). Serves the smallest of the m <= 32
  * calls that the reference gives to _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337,
  * :236-257). -5 = x does not fit in shared memory (muse_fewtok_smem_bytes > 227 KB). */
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int tok_split, int* status, void* stream);
+                    int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream);
 long long muse_fewtok_smem_bytes(int m, int K, int warps);
 
 /* The same walk over an FP32 weight with FP32 output (the MoE router) for m = 1..8 * tok_split tokens:

@@ -32,7 +32,7 @@ SIGNATURES = {
     "muse_copy_h2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]),
     "muse_copy_d2h_sync": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]),
     "muse_fewtok_mma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                  C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+                                  C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "muse_fewtok_smem_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "muse_fewtok_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_void_p]),
@@ -50,7 +50,7 @@ SIGNATURES = {
     "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 
 class MuseError(RuntimeError):

@@ -19,7 +19,7 @@ int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, co
                               int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                               int stages, int out_f32, cudaStream_t stream);
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                        int unroll, int tok_split, int* status, cudaStream_t stream);
+                        int unroll, int tok_split, int* status, const PeerSync* peers, cudaStream_t stream);
 size_t fewtok_smem_bytes(int m, int K, int warps);
 int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                         int tok_split, cudaStream_t stream);
@@ -117,9 +117,9 @@ int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, 
 }
 
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int tok_split, int* status, void* stream) {
+                    int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream) {
   return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, status,
-                                   static_cast<cudaStream_t>(stream));
+                                   reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 
 int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,

@@ -31,6 +31,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 
 constexpr int FEWTOK_X_PAD = 64;   // bytes added to each x row in shared memory
+static inline bool peer_active_host(const PeerSync& ps) { return ps.world > 1; }
 
 // HI = tokens 8..15 exist (second half of the A fragment); otherwise those MMA rows are fed zeros.
 template <int NW, int U, bool HI>
@@ -142,27 +143,39 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 // HI = tokens 8..15 exist. With tok_split > 1 the grid is tok_split interleaved copies of the walk, copy j
 // multiplying tokens [j * TOKS, (j + 1) * TOKS): CTAs c and c + 1 stream the same groups at the same time,
 // so W still leaves HBM once (the second reader finds it in L2) while each SM keeps only its own tokens.
-template <int NW, int U, bool HI>
+// PEERS = column-parallel: rows go to columns [col0, col0 + N) of this rank's own gathered output, and
+// the grid's last CTA ships that slice to every peer and exchanges the done flags (as the GEMV does).
+template <int NW, int U, bool HI, bool PEERS>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ x,
                                                               __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
-                                                              int ld_out, int tok_split) {
+                                                              int ld_out, int tok_split, int* __restrict__ status,
+                                                              const __grid_constant__ PeerSync ps) {
   constexpr int OUTS = HI ? 128 : 64;            // 8 or 16 tokens x 8 rows
   constexpr int TOKS = HI ? 16 : 8;
   __shared__ __align__(16) float red[2][NW][OUTS];
+  __shared__ int s_epoch, s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int C = static_cast<int>(gridDim.x) / tok_split, c = static_cast<int>(blockIdx.x) / tok_split;
+  const int m_all = m;
+  if constexpr (PEERS) {
+    if (threadIdx.x == 0) {
+      s_epoch = peer_epoch(ps);
+      if (blockIdx.x == 0) peer_announce_enter(ps, s_epoch);
+    }
+    out = reinterpret_cast<__nv_bfloat16*>(ps.out[ps.rank]) + ps.col0;
+  }
   {
     const int t0 = (static_cast<int>(blockIdx.x) % tok_split) * TOKS;
     x += static_cast<size_t>(t0) * ld_x;
     out += static_cast<size_t>(t0) * ld_out;
     m = m - t0 < TOKS ? m - t0 : TOKS;
-    if (m <= 0) return;
+    if (!PEERS && m <= 0) return;
   }
   const int kblocks = K >> 5;
   const int groups = (N + 7) >> 3;
-  const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
+  const int my_groups = (c < groups && m > 0) ? (groups - c + C - 1) / C : 0;
   const int first = warp * U;                    // this warp's 64-byte pieces of every row: first .. first + U - 1
   auto load = [&](uint4 (&w)[U], int i) {
     int row = (c + i * C) * 8 + g;
@@ -210,6 +223,34 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
       const int row = (c + i * C) * 8 + (threadIdx.x & 7);
       if (t < m && row < N) out[static_cast<size_t>(t) * ld_out + row] = __float2bfloat16_rn(sum);
     }
+  }
+  if constexpr (PEERS) {
+    if (!peer_last_cta(ps, static_cast<int>(gridDim.x), &s_last)) return;
+    // Last CTA: every row of this rank's slice is in the local gathered output. Copy it to the peers
+    // (16-byte vectors when the slice allows) once they have entered the call, then publish and wait.
+    const int e = s_epoch;
+    peer_wait_all_entered(ps, e, status);
+    const size_t pitch = static_cast<size_t>(ld_out) * 2;
+    const char* src = reinterpret_cast<const char*>(ps.out[ps.rank]) + static_cast<size_t>(ps.col0) * 2;
+    const int row_bytes = N * 2;
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) | pitch | static_cast<unsigned>(row_bytes)) & 15) == 0;
+    for (int p = 0; p < ps.world; ++p) {
+      if (p == ps.rank) continue;
+      char* dst = reinterpret_cast<char*>(ps.out[p]) + static_cast<size_t>(ps.col0) * 2;
+      if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        const int per_row = row_bytes / 16;
+        for (int i = threadIdx.x; i < m_all * per_row; i += NW * 32) {
+          const size_t off = static_cast<size_t>(i / per_row) * pitch + static_cast<size_t>(i % per_row) * 16;
+          *reinterpret_cast<uint4*>(dst + off) = __ldcg(reinterpret_cast<const uint4*>(src + off));
+        }
+      } else {
+        for (int i = threadIdx.x; i < m_all * N; i += NW * 32) {
+          const size_t off = static_cast<size_t>(i / N) * pitch + static_cast<size_t>(i % N) * 2;
+          *reinterpret_cast<unsigned short*>(dst + off) = __ldcg(reinterpret_cast<const unsigned short*>(src + off));
+        }
+      }
+    }
+    peer_publish(ps, e, status);
   }
 }
 
@@ -334,10 +375,10 @@ static cudaError_t launch_fewtok(const void* W, const void* x, void* out, int m,
   return cudaGetLastError();
 }
 
-template <int NW, int U, bool HI>
-static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
-                               int tok_split, cudaStream_t s) {
-  auto kern = fewtok_xreg_kernel<NW, U, HI>;
+template <int NW, int U, bool HI, bool PEERS>
+static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
+                                    int tok_split, int* status, const PeerSync& ps, cudaStream_t s) {
+  auto kern = fewtok_xreg_kernel<NW, U, HI, PEERS>;
   static int per_sm[64] = {0}, sms[64] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -356,8 +397,17 @@ static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, i
   if (walkers < 1) return cudaErrorInvalidConfiguration;
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
                                                reinterpret_cast<const __nv_bfloat16*>(x),
-                                               reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split);
+                                               reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
+                                               status, ps);
   return cudaGetLastError();
+}
+
+// The single-GPU instantiation carries no exchange code.
+template <int NW, int U, bool HI>
+static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
+                               int tok_split, int* status, const PeerSync& ps, cudaStream_t s) {
+  return peer_active_host(ps) ? launch_xreg_with<NW, U, HI, true>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s)
+                              : launch_xreg_with<NW, U, HI, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s);
 }
 
 template <int NW, int U>
@@ -412,7 +462,16 @@ static bool xreg_serves(int toks, int K, int warps, int unroll) {
 // 1..16 tokens, BF16 weight and output; warps in {16, 32}, unroll in {1, 2, 4}, and 8 with 16 warps when
 // that covers a whole row (K <= 4096). Negative = argument error.
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                        int unroll, int tok_split, int* status, cudaStream_t stream) {
+                        int unroll, int tok_split, int* status, const PeerSync* peers, cudaStream_t stream) {
+  PeerSync ps = {};
+  if (peers && peers->world > 1) {
+    ps = *peers;
+    if (ps.world > MAX_WORLD || ps.rank < 0 || ps.rank >= ps.world || ps.col0 < 0) return -8;
+    for (int p = 0; p < ps.world; ++p)
+      if (!ps.out[p] || !ps.flags[p]) return -8;
+    out = ps.out[ps.rank];
+    if (ld_out < ps.col0 + N) return -2;
+  }
   if (!W || !x || !out || !status || N <= 0 || K <= 0) return -1;
   if (tok_split < 1 || tok_split > 4 || m < 1 || m > 16 * tok_split) return -9;
   const int toks = m <= 8 * tok_split ? 8 : 16;   // tokens per CTA
@@ -422,7 +481,7 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
   if (xreg_serves(toks, K, warps, unroll)) {   // a whole row per batch: the A fragments stay in registers
 #define MUSE_XREG(NW_, U_, HI_)                                 \
     if (warps == NW_ && unroll == U_ && (toks > 8) == HI_)      \
-      e = launch_xreg<NW_, U_, HI_>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
+      e = launch_xreg<NW_, U_, HI_>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, stream);
     MUSE_XREG(32, 1, false) MUSE_XREG(32, 2, false) MUSE_XREG(32, 4, false) MUSE_XREG(32, 1, true) MUSE_XREG(32, 2, true)
     MUSE_XREG(16, 1, false) MUSE_XREG(16, 2, false) MUSE_XREG(16, 4, false) MUSE_XREG(16, 8, false)
     MUSE_XREG(16, 1, true) MUSE_XREG(16, 2, true) MUSE_XREG(16, 4, true) MUSE_XREG(16, 8, true)
@@ -430,6 +489,7 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
     return static_cast<int>(e);
   }
   if (tok_split != 1) return -9;   // the shared-memory path holds all of a call's tokens in one CTA
+  if (peer_active_host(ps)) return -8;   // and has no exchange epilogue
   if (fewtok_smem(K, m, warps) > 227 * 1024) return -5;
 #define MUSE_FEWTOK(NW_, U_)                                                                                    \
   if (warps == NW_ && unroll == U_)                                                                             \

@@ -148,7 +148,7 @@ def _weight_maps(state, layer: str, n: int):
 def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> GemvPlan | FewTokPlan | SkinnyPlan:
     """The (cached) launch plan of a shape; `state["_override"][(layer, m)]` = dict(cluster=, groups=, stages=),
     dict(wpr=, unroll=) or dict(warps=, unroll=) forces values for tuning sweeps. `fused` = the call carries a
-    peer descriptor (the register-MMA kernel has no exchange epilogue)."""
+    peer descriptor."""
     key = (layer, m, n, k, fused)
     ov = state["_override"].get((layer, m))
     if ov is None and key in state["_plans"]:
@@ -156,8 +156,10 @@ def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> 
     f32 = layer in FP32_LAYERS
     dev = state["_dev"]
     few = None
-    if not fused and m <= FEWTOK_BUCKETS[-1]:
+    if m <= FEWTOK_BUCKETS[-1]:
         few = FewTokPlan(**ov) if ov and "warps" in ov else (None if ov else fewtok_plan(m, n, k, f32, dev))
+        if fused and few is not None and (f32 or few.warps * few.unroll * 32 < k):
+            few = None   # only the BF16 register-resident kernel has the exchange epilogue
     if few is not None:
         plan = few
     elif m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):
@@ -216,7 +218,7 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
         return
     if isinstance(plan, FewTokPlan):
         _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x_ptr, out_ptr, m, n, k, ld_x, ld_out, plan.warps, plan.unroll,
-                                        plan.tok_split, status, stream),
+                                        plan.tok_split, status, _peer_ptr(peers), stream),
                     f"muse_fewtok_mma({layer}, m={m}, n={n}, k={k}, {plan})")
         return
     if isinstance(plan, GemvPlan):

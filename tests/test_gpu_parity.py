@@ -294,7 +294,7 @@ def test_fewtok_entry_point_matches_oracle_and_is_bit_stable(dev, case):
     for _ in range(3):
         out = torch.full((m, n + 5), 3.0, device=dev, dtype=torch.bfloat16)
         _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0), warps,
-                                        unroll, tok_split, status.data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
+                                        unroll, tok_split, status.data_ptr(), None, torch.cuda.current_stream(dev).cuda_stream),
                     "muse_fewtok_mma")
         torch.cuda.synchronize(dev)
         outs.append(out)
@@ -316,7 +316,7 @@ def test_fewtok_rejections(dev):
     out = torch.zeros((17, 64), device=dev, dtype=torch.bfloat16)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
     call = lambda m, n, k, ldx, ldo, warps, unroll, split=1: lib.muse_fewtok_mma(
-        w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, ldx, ldo, warps, unroll, split, status.data_ptr(), None)
+        w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, ldx, ldo, warps, unroll, split, status.data_ptr(), None, None)
     assert call(17, 64, 4096, 4096, 64, 16, 4) == -9        # more than 16 tokens per copy of the walk
     assert call(17, 64, 4096, 4096, 64, 16, 4, split=2) == -9   # x in shared memory: one CTA holds all tokens
     assert call(4, 64, 4096, 4096, 64, 32, 4, split=5) == -9

@@ -53,24 +53,26 @@ def main() -> None:
             if getattr(plan, "groups", 1) == 1 and not torch.equal(a, b):
                 bad.append(f"fused != nccl bitwise: {layer} m={m}")
     # graph replays of the fused path: every rank replays the same graph the same number of times
-    data = oracle.target_input(32, "qkv_gate", 99, layers=layers)
-    gx = data["x"].to(dev)
-    want = oracle.fp32_reference(data, w_cpu).to(dev)
+    # (m = 32: the TMEM kernel's epilogue exchange; m = 8: the register-MMA kernel's; m = 1: the GEMV's)
     stream = torch.cuda.Stream(dev)
-    hold = {}
-    with torch.cuda.stream(stream):
-        hold["o"] = fused.kernel_fn({"x": gx, "config": data["config"]}, state)
-        stream.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
+    for m in (32, 8, 1):
+        data = oracle.target_input(m, "qkv_gate", 99, layers=layers)
+        gx = data["x"].to(dev)
+        want = oracle.fp32_reference(data, w_cpu).to(dev)
+        hold = {}
+        with torch.cuda.stream(stream):
             hold["o"] = fused.kernel_fn({"x": gx, "config": data["config"]}, state)
-        worst = torch.zeros((), device=dev)
-        for _ in range(200):
-            g.replay()
-            worst = torch.maximum(worst, (hold["o"].float() - want).abs().max())
-        stream.synchronize()
-    if float(worst) > 0.05:
-        bad.append(f"fused graph replays: max abs error {float(worst):.3e}")
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                hold["o"] = fused.kernel_fn({"x": gx, "config": data["config"]}, state)
+            worst = torch.zeros((), device=dev)
+            for _ in range(200):
+                g.replay()
+                worst = torch.maximum(worst, (hold["o"].float() - want).abs().max())
+            stream.synchronize()
+        if float(worst) > 0.05:
+            bad.append(f"fused graph replays at m={m}: max abs error {float(worst):.3e}")
     proj.check_status(state)
     flag = torch.tensor([len(bad)], device=dev)
     dist.all_reduce(flag)
