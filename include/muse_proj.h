@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 9
+#define MUSE_PROJ_ABI_VERSION 10
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -44,12 +44,23 @@ extern "C" {
  * before the first call and owned by these kernels afterwards. All ranks must make the same sequence
  * of calls. Waits on peers are bounded (status bits above). Plain peer stores only: no multimem,
  * no TMA to or from peer memory. No counterpart in the reference, which runs on one GPU and leaves
- * the all-gather out (bf16_proj/baseline.py:11). */
+ * the all-gather out (bf16_proj/baseline.py:11).
+ *
+ * muse_fewtok_mma exchanges differently (m <= MUSE_LL_TOKENS): it never writes into a peer's gathered
+ * output. Every CTA sends its rows to each peer's staging area ll[p] as 16-byte lines
+ * {data, call number, data, call number} -- 8 bytes of payload that validate themselves, so no fence
+ * and no flag follow them -- and finishes by unpacking the lines the peers sent it into its own
+ * out[rank], polling each line until it carries this call's number. ll[p] is rank p's zeroed staging
+ * of 2 x world x MUSE_LL_TOKENS x n x 4 bytes (n = the slice width; two halves used by odd and even
+ * calls, then one block per sending rank), peer-mapped like out[p]; it may be NULL when
+ * muse_fewtok_mma is not used column-parallel. */
 #define MUSE_MAX_WORLD 8
+#define MUSE_LL_TOKENS 16
 typedef struct muse_peer_sync {
   int world, rank, col0, reserved;
   void* out[MUSE_MAX_WORLD];
   int* flags[MUSE_MAX_WORLD];
+  void* ll[MUSE_MAX_WORLD];
 } muse_peer_sync_t;
 
 /* ABI version of the loaded library (MUSE_PROJ_ABI_VERSION at build time). */
@@ -79,8 +90,9 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
  * When warps * unroll * 32 >= K the kernel keeps its x fragments in registers; only then may
  * tok_split be 2..4: the grid is that many interleaved copies of the walk, each multiplying its own
  * block of 8 or 16 tokens, and W is read from HBM once and a second time from L2. Otherwise
- * tok_split = 1. `peers` (NULL on one GPU) makes the call column-parallel as in muse_gemv1; only the
- * register-resident form supports it (-8 otherwise). Serves the smallest of the m <= 32
+ * tok_split = 1. `peers` (NULL on one GPU) makes the call column-parallel (the self-validating
+ * lines described at muse_peer_sync_t): only the register-resident form, m <= MUSE_LL_TOKENS,
+ * N % 8 == 0 and col0 % 8 == 0 (-8 otherwise). Serves the smallest of the m <= 32
  * calls that the reference gives to _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337,
  * :236-257). -5 = x does not fit in shared memory (muse_fewtok_smem_bytes > 227 KB). */
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,

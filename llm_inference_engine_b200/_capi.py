@@ -50,7 +50,7 @@ SIGNATURES = {
     "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 
 class MuseError(RuntimeError):
@@ -89,13 +89,14 @@ def check(rc: int, what: str) -> None:
 
 
 MAX_WORLD = 8
+LL_TOKENS = 16   # MUSE_LL_TOKENS: most tokens of a column-parallel muse_fewtok_mma call
 
 
 class PeerSync(C.Structure):
     """muse_peer_sync_t: where a column-parallel kernel writes its slice on every rank (muse_proj.h)."""
 
     _fields_ = [("world", C.c_int), ("rank", C.c_int), ("col0", C.c_int), ("reserved", C.c_int),
-                ("out", C.c_void_p * MAX_WORLD), ("flags", C.c_void_p * MAX_WORLD)]
+                ("out", C.c_void_p * MAX_WORLD), ("flags", C.c_void_p * MAX_WORLD), ("ll", C.c_void_p * MAX_WORLD)]
 
 
 class TensorMap:

@@ -215,6 +215,13 @@ __device__ __forceinline__ float bf16hi_f32(uint32_t v) { return __uint_as_float
 //   done[r]    written to every peer by rank r's last CTA after all its stores (system-scope fence).
 //              The same CTA then waits for every peer's done[.] >= e, so when the kernel completes
 //              the local [m, N] holds every rank's slice.
+// The register-MMA kernel exchanges without fences or flags: its CTAs send 16-byte lines {data, call
+// number, data, call number} into a staging area on each peer (ll[.], two halves used by odd and even
+// calls, one block per sending rank) and finish by unpacking what the peers sent them into their own
+// gathered output, polling each line until both of its 8-byte halves carry this call's number. Nothing
+// is written into a peer's gathered output, so that path needs no enter round either. A half is reused
+// two calls later; between the two uses lies a whole call in which both ranks had to receive each
+// other's lines, i.e. the receiver had finished unpacking the earlier use.
 // Layout of a rank's flag array (int32): [0, 8) enter, [8, 16) done, [16] epoch of the last finished
 // call, [17] CTA arrival counter. All waits are bounded and report through the status word.
 constexpr int MAX_WORLD = 8;
@@ -227,7 +234,9 @@ struct PeerSync {
   int pad_;
   void* out[MAX_WORLD];    // every rank's gathered output (same shape and row stride everywhere)
   int* flags[MAX_WORLD];   // every rank's flag array
+  void* ll[MAX_WORLD];     // every rank's staging for self-validating lines (register-MMA kernel; may be null)
 };
+constexpr int LL_TOKENS = 16;   // most tokens of a call exchanged through the staging
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
@@ -312,6 +321,41 @@ __device__ __forceinline__ void peer_publish(const PeerSync& ps, int e, int* sta
 }
 __device__ __forceinline__ void peer_finish(const PeerSync& ps, int e, int total_ctas, int* status, int* s_flag) {
   if (peer_last_cta(ps, total_ctas, s_flag)) peer_publish(ps, e, status);
+}
+
+// ---- self-validating lines (see above)
+__device__ __forceinline__ void st_volatile_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// Byte offset, inside a rank's staging, of the lines that `src` sends for token t of call e (n = slice width).
+__device__ __forceinline__ size_t ll_row_offset(int e, int world, int src, int t, int n) {
+  return ((static_cast<size_t>(e & 1) * world + src) * LL_TOKENS + t) * static_cast<size_t>(n) * 4;
+}
+// 16 bytes of payload (8 BF16 outputs) as two lines tagged with the call number.
+__device__ __forceinline__ void ll_send16(void* dst, uint4 v, int e) {
+  st_volatile_v4(dst, v.x, static_cast<uint32_t>(e), v.y, static_cast<uint32_t>(e));
+  st_volatile_v4(static_cast<char*>(dst) + 16, v.z, static_cast<uint32_t>(e), v.w, static_cast<uint32_t>(e));
+}
+// Poll two lines until all four halves carry call number e (bounded); false on time-out.
+__device__ __forceinline__ bool ll_recv16(const void* src, int e, uint4& v) {
+  const uint32_t want = static_cast<uint32_t>(e);
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      const uint4 a = ld_volatile_v4(src), b = ld_volatile_v4(static_cast<const char*>(src) + 16);
+      if (a.y == want && a.w == want && b.y == want && b.w == want) {
+        v = make_uint4(a.x, a.z, b.x, b.z);
+        return true;
+      }
+    }
+    if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
 }
 
 }  // namespace muse

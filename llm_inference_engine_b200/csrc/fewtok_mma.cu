@@ -30,6 +30,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+unsigned long long* skinny_get_trace();   // device buffer the next launches stamp into (diagnostics)
+
 constexpr int FEWTOK_X_PAD = 64;   // bytes added to each x row in shared memory
 static inline bool peer_active_host(const PeerSync& ps) { return ps.world > 1; }
 
@@ -143,31 +145,34 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 // HI = tokens 8..15 exist. With tok_split > 1 the grid is tok_split interleaved copies of the walk, copy j
 // multiplying tokens [j * TOKS, (j + 1) * TOKS): CTAs c and c + 1 stream the same groups at the same time,
 // so W still leaves HBM once (the second reader finds it in L2) while each SM keeps only its own tokens.
-// PEERS = column-parallel: rows go to columns [col0, col0 + N) of this rank's own gathered output, and
-// the grid's last CTA ships that slice to every peer and exchanges the done flags (as the GEMV does).
+// PEERS = column-parallel: every CTA stores its rows at columns [col0, col0 + N) of this rank's gathered
+// output and sends them to every peer's staging as self-validating lines; when its groups are done it
+// unpacks its share of the lines the peers sent here. No fence, no flag, no wait on another CTA.
 template <int NW, int U, bool HI, bool PEERS>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ x,
                                                               __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
                                                               int ld_out, int tok_split, int* __restrict__ status,
-                                                              const __grid_constant__ PeerSync ps) {
+                                                              const __grid_constant__ PeerSync ps,
+                                                              unsigned long long* __restrict__ trace) {
+  // Diagnostics of the exchange (PEERS only): per CTA 16 slots of the global nanosecond timer, 0 entry,
+  // 1 first group stored, 2 groups done, 3 peers' lines unpacked; first group: 5 multiplied, 6 synchronised, 7 stored locally.
+  unsigned long long* const tr = PEERS && trace ? trace + 16ull * blockIdx.x : nullptr;
+  if (tr && threadIdx.x == 0) tr[0] = global_ns();
   constexpr int OUTS = HI ? 128 : 64;            // 8 or 16 tokens x 8 rows
   constexpr int TOKS = HI ? 16 : 8;
   __shared__ __align__(16) float red[2][NW][OUTS];
-  __shared__ int s_epoch, s_last;
+  __shared__ int s_epoch;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int C = static_cast<int>(gridDim.x) / tok_split, c = static_cast<int>(blockIdx.x) / tok_split;
-  const int m_all = m;
   if constexpr (PEERS) {
-    if (threadIdx.x == 0) {
-      s_epoch = peer_epoch(ps);
-      if (blockIdx.x == 0) peer_announce_enter(ps, s_epoch);
-    }
     out = reinterpret_cast<__nv_bfloat16*>(ps.out[ps.rank]) + ps.col0;
   }
+  const int m_all = m;
+  int t0 = 0;
   {
-    const int t0 = (static_cast<int>(blockIdx.x) % tok_split) * TOKS;
+    t0 = (static_cast<int>(blockIdx.x) % tok_split) * TOKS;
     x += static_cast<size_t>(t0) * ld_x;
     out += static_cast<size_t>(t0) * ld_out;
     m = m - t0 < TOKS ? m - t0 : TOKS;
@@ -202,6 +207,24 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
       xh[0] = make_uint4(0u, 0u, 0u, 0u);
     }
   }
+  if constexpr (PEERS) {   // after the first loads are in flight: none of this delays them
+    if (threadIdx.x == 0) {
+      // The call number, and the book-keeping that advances it: the last CTA to get HERE closes the number,
+      // because by then every CTA of the grid has read it. Done first so that nothing waits on it at the end.
+      int* mine = ps.flags[ps.rank];
+      const int e = peer_epoch(ps);
+      s_epoch = e;
+      if (atomicAdd(mine + 17, 1) == static_cast<int>(gridDim.x) - 1) {
+        mine[17] = 0;
+        mine[16] = e;
+      }
+    } else if (threadIdx.x >= NW * 32 - ps.world && static_cast<int>(threadIdx.x) - (NW * 32 - ps.world) != ps.rank) {
+      // One lane per peer touches that peer's staging now, so that the address translation of the first
+      // real store (several microseconds later) is already cached. The value is never used.
+      uint32_t unused;
+      asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(unused) : "l"(ps.ll[threadIdx.x - (NW * 32 - ps.world)]) : "memory");
+    }
+  }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int i = 0; i < my_groups; ++i) {
 #pragma unroll
@@ -210,47 +233,60 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
       mma_bf16_16816(acc, xr[u].x, hi.x, xr[u].y, hi.y, w[u].x, w[u].y);
       mma_bf16_16816(acc, xr[u].z, hi.z, xr[u].w, hi.w, w[u].z, w[u].w);
     }
+    if (tr && i == 0 && threadIdx.x == 0) tr[5] = global_ns();
     if (i + 1 < my_groups) load(w, i + 1);
     *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
     if constexpr (HI) *reinterpret_cast<float2*>(&red[i & 1][warp][(g + 8) * 8 + 2 * q]) = make_float2(acc[2], acc[3]);
     acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
     __syncthreads();   // the buffer written two groups ago is free again once every warp passed this
+    if (tr && i == 0 && threadIdx.x == 0) tr[6] = global_ns();
     if (threadIdx.x < OUTS) {
       float sum = 0.f;
 #pragma unroll 8
       for (int wv = 0; wv < NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
-      const int t = threadIdx.x >> 3;
-      const int row = (c + i * C) * 8 + (threadIdx.x & 7);
-      if (t < m && row < N) out[static_cast<size_t>(t) * ld_out + row] = __float2bfloat16_rn(sum);
-    }
-  }
-  if constexpr (PEERS) {
-    if (!peer_last_cta(ps, static_cast<int>(gridDim.x), &s_last)) return;
-    // Last CTA: every row of this rank's slice is in the local gathered output. Copy it to the peers
-    // (16-byte vectors when the slice allows) once they have entered the call, then publish and wait.
-    const int e = s_epoch;
-    peer_wait_all_entered(ps, e, status);
-    const size_t pitch = static_cast<size_t>(ld_out) * 2;
-    const char* src = reinterpret_cast<const char*>(ps.out[ps.rank]) + static_cast<size_t>(ps.col0) * 2;
-    const int row_bytes = N * 2;
-    const bool vec = ((reinterpret_cast<uintptr_t>(src) | pitch | static_cast<unsigned>(row_bytes)) & 15) == 0;
-    for (int p = 0; p < ps.world; ++p) {
-      if (p == ps.rank) continue;
-      char* dst = reinterpret_cast<char*>(ps.out[p]) + static_cast<size_t>(ps.col0) * 2;
-      if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-        const int per_row = row_bytes / 16;
-        for (int i = threadIdx.x; i < m_all * per_row; i += NW * 32) {
-          const size_t off = static_cast<size_t>(i / per_row) * pitch + static_cast<size_t>(i % per_row) * 16;
-          *reinterpret_cast<uint4*>(dst + off) = __ldcg(reinterpret_cast<const uint4*>(src + off));
-        }
+      const int t = threadIdx.x >> 3, r = threadIdx.x & 7;
+      const int grp = c + i * C, row0 = grp * 8;
+      if constexpr (!PEERS) {
+        if (t < m && row0 + r < N) out[static_cast<size_t>(t) * ld_out + row0 + r] = __float2bfloat16_rn(sum);
       } else {
-        for (int i = threadIdx.x; i < m_all * N; i += NW * 32) {
-          const size_t off = static_cast<size_t>(i / N) * pitch + static_cast<size_t>(i % N) * 2;
-          *reinterpret_cast<unsigned short*>(dst + off) = __ldcg(reinterpret_cast<const unsigned short*>(src + off));
+        // The 8 rows of a token sit in 8 neighbouring lanes: gather them into one 16-byte vector (N % 8 == 0 here).
+        const uint32_t v = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sum)));
+        const uint32_t p01 = v | (__shfl_down_sync(0xffffffffu, v, 1) << 16);
+        const uint32_t p23 = __shfl_down_sync(0xffffffffu, p01, 2);
+        const uint32_t p45 = __shfl_down_sync(0xffffffffu, p01, 4), p67 = __shfl_down_sync(0xffffffffu, p23, 4);
+        if (r == 0 && t < m) {
+          const uint4 val = make_uint4(p01, p23, p45, p67);
+          *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ld_out + row0) = val;
+          if (tr && i == 0 && threadIdx.x == 0) tr[7] = global_ns();
+          const int e = s_epoch;
+          const size_t off = ll_row_offset(e, ps.world, ps.rank, t0 + t, N) + static_cast<size_t>(grp) * 32;
+          for (int p = 0; p < ps.world; ++p)
+            if (p != ps.rank) ll_send16(static_cast<char*>(ps.ll[p]) + off, val, e);
         }
       }
     }
-    peer_publish(ps, e, status);
+    if (tr && i == 0 && threadIdx.x == 0) tr[1] = global_ns();
+  }
+  if constexpr (PEERS) {
+    // Unpack this CTA's share of what the peers sent: (sending rank, token, group) units, 16 bytes of output each.
+    __syncthreads();
+    if (tr && threadIdx.x == 0) tr[2] = global_ns();
+    const int e = s_epoch, gpr = N >> 3;
+    const int units = (ps.world - 1) * m_all * gpr;
+    bool ok = true;
+    for (int u = static_cast<int>(blockIdx.x) * NW * 32 + threadIdx.x; u < units; u += static_cast<int>(gridDim.x) * NW * 32) {
+      const int si = u / (m_all * gpr), rem = u - si * (m_all * gpr);
+      const int t = rem / gpr, grp = rem - t * gpr;
+      const int src = si < ps.rank ? si : si + 1;
+      uint4 val;
+      if (ll_recv16(static_cast<const char*>(ps.ll[ps.rank]) + ll_row_offset(e, ps.world, src, t, N) + static_cast<size_t>(grp) * 32, e, val))
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(ps.out[ps.rank]) + static_cast<size_t>(t) * ld_out +
+                                  static_cast<size_t>(src) * N + grp * 8) = val;
+      else
+        ok = false;
+    }
+    if (!ok) atomicOr(status, ST_PEER_DONE_TIMEOUT);
+    if (tr && threadIdx.x == 0) tr[3] = global_ns();
   }
 }
 
@@ -337,7 +373,6 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
   }
 }
 
-unsigned long long* skinny_get_trace();
 
 static size_t fewtok_smem(int K, int m, int nw) {
   const int tok = m > 8 ? 16 : 8;
@@ -398,7 +433,7 @@ static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
                                                reinterpret_cast<const __nv_bfloat16*>(x),
                                                reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
-                                               status, ps);
+                                               status, ps, skinny_get_trace());
   return cudaGetLastError();
 }
 
@@ -470,7 +505,10 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
     for (int p = 0; p < ps.world; ++p)
       if (!ps.out[p] || !ps.flags[p]) return -8;
     out = ps.out[ps.rank];
-    if (ld_out < ps.col0 + N) return -2;
+    // the exchange: equal slices side by side, whole 16-byte vectors, staging for LL_TOKENS tokens
+    if (ld_out < ps.world * N || ps.col0 != ps.rank * N || N % 8 != 0 || ld_out % 8 != 0 || m > LL_TOKENS) return -8;
+    for (int p = 0; p < ps.world; ++p)
+      if (!ps.ll[p] || (reinterpret_cast<uintptr_t>(ps.ll[p]) & 15) || (reinterpret_cast<uintptr_t>(ps.out[p]) & 15)) return -8;
   }
   if (!W || !x || !out || !status || N <= 0 || K <= 0) return -1;
   if (tok_split < 1 || tok_split > 4 || m < 1 || m > 16 * tok_split) return -9;

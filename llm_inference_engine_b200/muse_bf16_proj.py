@@ -25,7 +25,7 @@ import ctypes
 import torch
 
 from . import _capi
-from .plan import FEWTOK_BUCKETS, DeviceFacts, FewTokPlan, GemvPlan, SkinnyPlan, fewtok_plan, gemv_plan, gemv_valid, skinny_plan
+from .plan import FEWTOK_BUCKETS, DeviceFacts, FewTokPlan, fewtok_fused_plan, GemvPlan, SkinnyPlan, fewtok_plan, gemv_plan, gemv_valid, skinny_plan
 
 FP32_LAYERS = {"router"}
 # Workspace rule: sized once in prepare() so that every layer at up to this many tokens can split K;
@@ -156,10 +156,12 @@ def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> 
     f32 = layer in FP32_LAYERS
     dev = state["_dev"]
     few = None
-    if m <= FEWTOK_BUCKETS[-1]:
-        few = FewTokPlan(**ov) if ov and "warps" in ov else (None if ov else fewtok_plan(m, n, k, f32, dev))
-        if fused and few is not None and (f32 or few.warps * few.unroll * 32 < k):
-            few = None   # only the BF16 register-resident kernel has the exchange epilogue
+    if ov and "warps" in ov:
+        few = FewTokPlan(**ov)
+    elif ov is None and fused:
+        few = fewtok_fused_plan(m, n, k, f32)
+    elif ov is None and m <= FEWTOK_BUCKETS[-1]:
+        few = fewtok_plan(m, n, k, f32, dev)
     if few is not None:
         plan = few
     elif m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):

@@ -162,6 +162,21 @@ def fewtok_smem_bytes(m: int, k: int, warps: int) -> int:
     return m * (k * 2 + FEWTOK_X_PAD) + 2 * warps * tok * 8 * 4
 
 
+LL_TOKENS = 16   # most tokens of a column-parallel register-MMA call (MUSE_LL_TOKENS)
+
+
+def fewtok_fused_plan(m: int, n: int, k: int, w_is_f32: bool) -> FewTokPlan | None:
+    """Column-parallel calls (n = this rank's slice): the register-MMA kernel's exchange costs one NVLink
+    flight where the other kernels' costs a fence and two, so it is taken whenever it applies: BF16,
+    m <= LL_TOKENS, whole 8-row groups, x in registers (K <= 4096)."""
+    kblocks = k // 32
+    if w_is_f32 or not 1 <= m <= LL_TOKENS or k % 32 or n % 8 or n < 128 or kblocks > 128:
+        return None
+    if m > 8:
+        return FewTokPlan(16, 1 if kblocks <= 16 else 2 if kblocks <= 32 else 4 if kblocks <= 64 else 8)
+    return FewTokPlan(*((16, 1) if kblocks <= 16 else (16, 2) if kblocks <= 32 else (16, 4) if kblocks <= 64 else (32, 4)))
+
+
 def fewtok_plan(m: int, n: int, k: int, w_is_f32: bool, dev: DeviceFacts = DeviceFacts()) -> FewTokPlan | None:
     """The register-MMA plan of a shape that gains from it, else None (TMEM kernel). Tuned shapes come
     from the table; others take it at m <= 8 when the weight has enough 8-row groups to occupy most SMs."""

@@ -105,6 +105,7 @@ class FusedColumnParallel(ColumnParallelProjection):
         self.max_tokens = max_tokens
         self._capi = _capi
         self._bufs: dict[str, torch.Tensor] = {}
+        self._ll: dict[str, torch.Tensor] = {}
         self._peers: dict[str, object] = {}
         self._handles: list = []
         self._flags = None
@@ -132,12 +133,18 @@ class FusedColumnParallel(ColumnParallelProjection):
             self._flag_ptrs = self._rendezvous(self._flags)
         buf = self._symm_empty((self.max_tokens, rows), dtype, device)
         ptrs = self._rendezvous(buf)
+        # staging of the register-MMA kernel's exchange: 2 halves x sending rank x token x slice column, 4 bytes each
+        ll = self._symm_empty((2, self.world, self._capi.LL_TOKENS, rows // self.world), torch.int32, device)
+        ll.zero_()
+        ll_ptrs = self._rendezvous(ll)
         ps = self._capi.PeerSync()
         ps.world, ps.rank, ps.col0 = self.world, self.rank, self.rank * (rows // self.world)
         for p in range(self.world):
             ps.out[p] = ptrs[p]
             ps.flags[p] = self._flag_ptrs[p]
+            ps.ll[p] = ll_ptrs[p]
         self._bufs[name], self._peers[name] = buf, ps
+        self._ll[name] = ll
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)   # every rank's flags are zero and mapped before anyone launches
 

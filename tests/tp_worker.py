@@ -39,7 +39,7 @@ def main() -> None:
         fused._ensure_layer(name, w.shape[0], w.dtype, dev)
     bad = []
     for layer in layers:
-        for m in (1, 2, 8, 32, 100, 256):
+        for m in (1, 2, 8, 13, 16, 32, 100, 256):
             data = oracle.target_input(m, layer, 7000 + m, layers=layers)
             gdata = {"x": data["x"].to(dev), "config": data["config"]}
             a = fused.kernel_fn(gdata, state).clone()
@@ -49,8 +49,10 @@ def main() -> None:
                 ok, msg = oracle.target_check(data, out.cpu(), w_cpu)
                 if not ok:
                     bad.append(f"{tag} {layer} m={m}: {msg}")
-            plan = proj.plan_for(state, layer, m, layers[layer][0] // world, layers[layer][1])
-            if getattr(plan, "groups", 1) == 1 and not torch.equal(a, b):
+            shape = (layers[layer][0] // world, layers[layer][1])
+            plan = proj.plan_for(state, layer, m, *shape)
+            same_kernel = plan == proj.plan_for(state, layer, m, *shape, fused=True)
+            if same_kernel and getattr(plan, "groups", 1) == 1 and not torch.equal(a, b):
                 bad.append(f"fused != nccl bitwise: {layer} m={m}")
     # graph replays of the fused path: every rank replays the same graph the same number of times
     # (m = 32: the TMEM kernel's epilogue exchange; m = 8: the register-MMA kernel's; m = 1: the GEMV's)
