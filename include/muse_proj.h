@@ -55,7 +55,7 @@ extern "C" {
  * calls, then one block per sending rank), peer-mapped like out[p]; it may be NULL when
  * muse_fewtok_mma is not used column-parallel. */
 #define MUSE_MAX_WORLD 8
-#define MUSE_LL_TOKENS 16
+#define MUSE_LL_TOKENS 32
 typedef struct muse_peer_sync {
   int world, rank, col0, reserved;
   void* out[MUSE_MAX_WORLD];

@@ -89,7 +89,7 @@ def check(rc: int, what: str) -> None:
 
 
 MAX_WORLD = 8
-LL_TOKENS = 16   # MUSE_LL_TOKENS: most tokens of a column-parallel muse_fewtok_mma call
+LL_TOKENS = 32   # MUSE_LL_TOKENS: most tokens of a column-parallel muse_fewtok_mma call
 
 
 class PeerSync(C.Structure):

@@ -236,7 +236,7 @@ struct PeerSync {
   int* flags[MAX_WORLD];   // every rank's flag array
   void* ll[MAX_WORLD];     // every rank's staging for self-validating lines (register-MMA kernel; may be null)
 };
-constexpr int LL_TOKENS = 16;   // most tokens of a call exchanged through the staging
+constexpr int LL_TOKENS = 32;   // most tokens of a call exchanged through the staging
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;

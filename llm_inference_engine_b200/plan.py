@@ -162,7 +162,7 @@ def fewtok_smem_bytes(m: int, k: int, warps: int) -> int:
     return m * (k * 2 + FEWTOK_X_PAD) + 2 * warps * tok * 8 * 4
 
 
-LL_TOKENS = 16   # most tokens of a column-parallel register-MMA call (MUSE_LL_TOKENS)
+LL_TOKENS = 32   # most tokens of a column-parallel register-MMA call (MUSE_LL_TOKENS)
 
 
 def fewtok_fused_plan(m: int, n: int, k: int, w_is_f32: bool) -> FewTokPlan | None:
@@ -172,8 +172,8 @@ def fewtok_fused_plan(m: int, n: int, k: int, w_is_f32: bool) -> FewTokPlan | No
     kblocks = k // 32
     if w_is_f32 or not 1 <= m <= LL_TOKENS or k % 32 or n % 8 or n < 128 or kblocks > 128:
         return None
-    if m > 8:
-        return FewTokPlan(16, 1 if kblocks <= 16 else 2 if kblocks <= 32 else 4 if kblocks <= 64 else 8)
+    if m > 8:   # 16 tokens per CTA; beyond that two interleaved walks that share W through L2
+        return FewTokPlan(16, 1 if kblocks <= 16 else 2 if kblocks <= 32 else 4 if kblocks <= 64 else 8, 2 if m > 16 else 1)
     return FewTokPlan(*((16, 1) if kblocks <= 16 else (16, 2) if kblocks <= 32 else (16, 4) if kblocks <= 64 else (32, 4)))
 
 

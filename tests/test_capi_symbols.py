@@ -35,6 +35,12 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     lib = _capi.load()
     assert set(_capi.SIGNATURES) == set(declared_symbols()), "ctypes table and header disagree"
     assert lib.muse_abi_version() == int(re.search(r"MUSE_PROJ_ABI_VERSION\s+(\d+)", HEADER).group(1))
+    # constants mirrored by hand in the binding and the planner
+    from llm_inference_engine_b200 import plan
+
+    assert _capi.MAX_WORLD == int(re.search(r"MUSE_MAX_WORLD\s+(\d+)", HEADER).group(1))
+    assert _capi.LL_TOKENS == plan.LL_TOKENS == int(re.search(r"MUSE_LL_TOKENS\s+(\d+)", HEADER).group(1))
+    assert ctypes.sizeof(_capi.PeerSync) == 16 + 3 * 8 * _capi.MAX_WORLD
 
 
 def test_pure_host_entry_points_without_a_gpu():

@@ -99,11 +99,12 @@ def test_fewtok_fused_plan_covers_what_the_exchange_supports():
     assert plan.fewtok_fused_plan(8, 6144, 4096, False) == plan.FewTokPlan(32, 4)
     assert plan.fewtok_fused_plan(16, 1536, 4096, False) == plan.FewTokPlan(16, 8)
     assert plan.fewtok_fused_plan(12, 512, 1024, False) == plan.FewTokPlan(16, 2)
-    assert plan.fewtok_fused_plan(17, 1536, 4096, False) is None      # staging holds 16 tokens
+    assert plan.fewtok_fused_plan(32, 1536, 4096, False) == plan.FewTokPlan(16, 8, 2)
+    assert plan.fewtok_fused_plan(33, 1536, 4096, False) is None      # staging holds 32 tokens
     assert plan.fewtok_fused_plan(4, 1532, 4096, False) is None       # ragged last group
     assert plan.fewtok_fused_plan(4, 32, 4096, True) is None          # FP32 router
     assert plan.fewtok_fused_plan(4, 1536, 8192, False) is None       # x would not stay in registers
-    assert plan.LL_TOKENS == 16
+    assert plan.LL_TOKENS == 32
 
 
 def test_fewtok_plan_only_where_it_applies():

@@ -39,7 +39,7 @@ def main() -> None:
         fused._ensure_layer(name, w.shape[0], w.dtype, dev)
     bad = []
     for layer in layers:
-        for m in (1, 2, 8, 13, 16, 32, 100, 256):
+        for m in (1, 2, 8, 13, 16, 27, 32, 100, 256):
             data = oracle.target_input(m, layer, 7000 + m, layers=layers)
             gdata = {"x": data["x"].to(dev), "config": data["config"]}
             a = fused.kernel_fn(gdata, state).clone()
@@ -55,9 +55,9 @@ def main() -> None:
             if same_kernel and getattr(plan, "groups", 1) == 1 and not torch.equal(a, b):
                 bad.append(f"fused != nccl bitwise: {layer} m={m}")
     # graph replays of the fused path: every rank replays the same graph the same number of times
-    # (m = 32: the TMEM kernel's epilogue exchange; m = 8: the register-MMA kernel's; m = 1: the GEMV's)
+    # (m = 64: the TMEM kernel's epilogue exchange; m = 32, 8, 1: the register-MMA kernel's lines, with and without token split)
     stream = torch.cuda.Stream(dev)
-    for m in (32, 8, 1):
+    for m in (64, 32, 8, 1):
         data = oracle.target_input(m, "qkv_gate", 99, layers=layers)
         gx = data["x"].to(dev)
         want = oracle.fp32_reference(data, w_cpu).to(dev)
