@@ -41,10 +41,12 @@ sys.path.insert(0, str(ROOT))
 LAYERS = {"qkv_gate": (12288, 4096), "o": (4096, 4096), "pooler": (1024, 4096), "unpooler": (4096, 1024),
           "router": (256, 4096)}
 FP32_LAYERS = {"router"}
-CASES = {"qkv_gate": (1, 2, 4, 8, 16, 32), "o": (1,), "router": (1, 8, 32, 128, 256),
-         "pooler": (1, 32, 64, 128, 256), "unpooler": (1, 32, 64, 128, 256)}
 WORKLOAD_LAYER = "qkv_gate"
-WORKLOAD_TOKENS = CASES[WORKLOAD_LAYER]
+WORKLOAD_TOKENS = (1, 2, 4, 8, 16, 32)
+# the table: the workload's calls, then the other configurations the benchmark names (qkv_gate and o at
+# m = 128, 256 belong to its column-parallel sweep)
+CASES = {"qkv_gate": WORKLOAD_TOKENS + (128, 256), "o": (1, 8, 32, 128, 256), "router": (1, 8, 32, 128, 256),
+         "pooler": (1, 32, 64, 128, 256), "unpooler": (1, 32, 64, 128, 256)}
 WEIGHT_STD = 0.02
 SEED = 5151
 ROTATE_BYTES = 640 << 20      # distinct weight bytes a per-case graph cycles through (5x the L2)
