@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 10
+#define MUSE_PROJ_ABI_VERSION 11
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -115,6 +115,10 @@ int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K
  * device tensors (best_submissions/muse_bf16_proj.py:369-372). */
 int muse_copy_h2d_async(void* dst_device, const void* src_host, long long bytes, void* stream);
 int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, void* stream);
+/* The whole round trip of one muse_fewtok_mma call in one entry: x_host [m, K] -> x_device, the
+ * kernel (contiguous x and out), out_device [m, N] -> out_host, stream synchronised. */
+int muse_fewtok_mma_host(const void* W, const void* x_host, void* x_device, void* out_device, void* out_host, int m, int N,
+                         int K, int warps, int unroll, int tok_split, int* status, void* stream);
 
 /* Fill a 128-byte tensor map for a row-major BF16 matrix [rows, cols] at `base` (device pointer,
  * 16-byte aligned) with `row_stride_bytes` between rows (multiple of 16), delivering boxes of

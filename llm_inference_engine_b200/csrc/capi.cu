@@ -122,6 +122,19 @@ int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K
                                    reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 
+int muse_fewtok_mma_host(const void* W, const void* x_host, void* x_device, void* out_device, void* out_host, int m, int N,
+                         int K, int warps, int unroll, int tok_split, int* status, void* stream) {
+  if (!x_host || !x_device || !out_device || !out_host || m < 1 || N < 1 || K < 1) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(x_device, x_host, static_cast<size_t>(m) * K * 2, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int rc = muse::fewtok_mma_dispatch(W, x_device, out_device, m, N, K, K, N, warps, unroll, tok_split, status, nullptr, s);
+  if (rc != 0) return rc;
+  e = cudaMemcpyAsync(out_host, out_device, static_cast<size_t>(m) * N * 2, cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaStreamSynchronize(s));
+}
+
 int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                     int tok_split, void* stream) {
   return muse::fewtok_f32_dispatch(W, x, out, m, N, K, ld_x, ld_out, unroll, tok_split, static_cast<cudaStream_t>(stream));

@@ -243,7 +243,8 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None) -> torc
     [m, K] CPU tensor (page-locked for an asynchronous copy), the result is a CPU tensor (`out` if
     given: contiguous [m, n], page-locked), complete when the call returns. x is staged into a device
     buffer kept per (layer, m, n), the projection runs on the current stream, and the result is copied
-    back and waited for: three C-ABI calls, no allocation after the first call of a shape. Beyond the
+    back and waited for: one C-ABI call for the register-MMA plans, three otherwise; no allocation after
+    the first call of a shape. Beyond the
     reference, whose harness owns the transfers (best_submissions/muse_bf16_proj.py:369-372)."""
     x, cfg = data["x"], data["config"]
     layer, n = cfg["layer"], int(cfg["n"])
@@ -270,6 +271,11 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None) -> torc
         raise ValueError("out must be a contiguous CPU [m, n] tensor, BF16 (FP32 for the router)")
     lib = _capi.load()
     stream = torch.cuda.current_stream(w.device).cuda_stream
+    if isinstance(plan, FewTokPlan) and not f32:   # the whole round trip in one C call
+        _capi.check(lib.muse_fewtok_mma_host(w.data_ptr(), x.data_ptr(), x_dev.data_ptr(), out_dev.data_ptr(), out.data_ptr(), m, n,
+                                             k, plan.warps, plan.unroll, plan.tok_split, state["_status"].data_ptr(), stream),
+                    f"muse_fewtok_mma_host({layer}, m={m}, n={n}, k={k}, {plan})")
+        return out
     _capi.check(lib.muse_copy_h2d_async(x_dev.data_ptr(), x.data_ptr(), m * k * 2, stream), "muse_copy_h2d_async")
     _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out_dev.data_ptr(), n, None, stream, w.device)
     _capi.check(lib.muse_copy_d2h_sync(out.data_ptr(), out_dev.data_ptr(), out.numel() * out.element_size(), stream),
