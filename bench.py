@@ -371,7 +371,8 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
     us = h.max_over_ranks(dt * 1e6 / (steps * len(WORKLOAD_TOKENS)))
     return {"value": us, "unit": "us/call", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "how": "wall clock around pinned-host x -> device, the projection, result -> pinned host, stream sync, per call; "
-                   + ("kernel_fn_host()" if h.world == 1 else "torch copies around the column-parallel kernel_fn()")}
+                   + ("kernel_fn_host(): copy-in, launch and copy-out recorded once per buffer pair as a CUDA graph, replayed and "
+                      "synchronised every call" if h.world == 1 else "torch copies around the column-parallel kernel_fn()")}
 
 
 def load_traffic() -> dict:

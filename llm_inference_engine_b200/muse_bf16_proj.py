@@ -238,16 +238,27 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
                 f"muse_skinny_tc({layer}, m={m}, n={n}, k={k}, {plan})")
 
 
-def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None) -> torch.Tensor:
+HOST_GRAPH_SLOTS = 64   # recorded round trips kept per state (oldest dropped first)
+_EMPTY: dict = {}
+
+
+def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record: bool = True) -> torch.Tensor:
     """kernel_fn for a caller whose activations live in HOST memory: `data["x"]` is a contiguous BF16
     [m, K] CPU tensor (page-locked for an asynchronous copy), the result is a CPU tensor (`out` if
     given: contiguous [m, n], page-locked), complete when the call returns. x is staged into a device
     buffer kept per (layer, m, n), the projection runs on the current stream, and the result is copied
-    back and waited for: one C-ABI call for the register-MMA plans, three otherwise; no allocation after
-    the first call of a shape. Beyond the
-    reference, whose harness owns the transfers (best_submissions/muse_bf16_proj.py:369-372)."""
+    back and waited for. When the caller passes the same x and out tensors again (the normal case: its
+    own pinned buffers), the copy-in, launch and copy-out are recorded once as a CUDA graph and replayed
+    (`record=False` keeps the plain form: one C-ABI call for the register-MMA plans, three otherwise).
+    Beyond the reference, whose harness owns the transfers (best_submissions/muse_bf16_proj.py:369-372)."""
     x, cfg = data["x"], data["config"]
     layer, n = cfg["layer"], int(cfg["n"])
+    if record and out is not None:   # a recorded round trip of exactly these buffers: nothing left to check
+        entry = state.get("_host_graphs", _EMPTY).get((layer, x.shape[0], n, x.data_ptr(), out.data_ptr()))
+        if entry is not None:
+            entry[0].replay()
+            torch.cuda.current_stream(entry[3]).synchronize()
+            return out
     if layer not in state or layer.startswith("_"):
         raise KeyError(f"unknown layer {layer!r}")
     w = state[layer]
@@ -265,12 +276,31 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None) -> torc
                 plan_for(state, layer, m, n, k))
         state["_host_slots"][key] = slot
     x_dev, out_dev, plan = slot
-    if out is None:
+    fresh_out = out is None
+    if fresh_out:
         out = torch.empty((m, n), dtype=odt, pin_memory=True)
     elif out.is_cuda or out.dtype != odt or tuple(out.shape) != (m, n) or not out.is_contiguous():
         raise ValueError("out must be a contiguous CPU [m, n] tensor, BF16 (FP32 for the router)")
     lib = _capi.load()
-    stream = torch.cuda.current_stream(w.device).cuda_stream
+    cur = torch.cuda.current_stream(w.device)
+    stream = cur.cuda_stream
+    if record and not fresh_out and x.is_pinned() and out.is_pinned():
+        graphs = state.setdefault("_host_graphs", {})
+        # The plain form once (it also warms every lazily created resource), then the recording.
+        kernel_fn_host(data, state, out=out, record=False)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            rec = torch.cuda.current_stream(w.device).cuda_stream
+            x_dev.copy_(x, non_blocking=True)
+            _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out_dev.data_ptr(), n, None, rec, w.device)
+            out.copy_(out_dev, non_blocking=True)
+        if len(graphs) >= HOST_GRAPH_SLOTS:
+            graphs.pop(next(iter(graphs)))
+        # the tensors stay alive as long as their addresses are baked in
+        graphs[(layer, m, n, x.data_ptr(), out.data_ptr())] = (graph, x, out, w.device)
+        graph.replay()
+        cur.synchronize()
+        return out
     if isinstance(plan, FewTokPlan) and not f32:   # the whole round trip in one C call
         _capi.check(lib.muse_fewtok_mma_host(w.data_ptr(), x.data_ptr(), x_dev.data_ptr(), out_dev.data_ptr(), out.data_ptr(), m, n,
                                              k, plan.warps, plan.unroll, plan.tok_split, state["_status"].data_ptr(), stream),

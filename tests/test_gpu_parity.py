@@ -341,9 +341,14 @@ def test_host_buffer_entry_point_matches_device_path(proj, dev, target_setup):
         got = proj.kernel_fn_host({"x": x, "config": cfg}, state)
         assert not got.is_cuda and got.dtype == want.dtype and torch.equal(got, want)
         out = torch.empty_like(want).pin_memory()
-        again = proj.kernel_fn_host({"x": x, "config": cfg}, state, out=out)
+        again = proj.kernel_fn_host({"x": x, "config": cfg}, state, out=out)      # records the round trip
         assert again is out and torch.equal(out, want)
-    assert len(state["_host_slots"]) == 5
+        x.copy_(torch.randn((m, k), generator=g).to(torch.bfloat16))               # same buffers, new contents
+        want2 = proj.kernel_fn({"x": x.to(dev), "config": cfg}, state).cpu()
+        out.zero_()
+        assert torch.equal(proj.kernel_fn_host({"x": x, "config": cfg}, state, out=out), want2)   # replays it
+        assert torch.equal(proj.kernel_fn_host({"x": x, "config": cfg}, state, out=out, record=False), want2)
+    assert len(state["_host_slots"]) == 5 and len(state["_host_graphs"]) == 5
     with pytest.raises(TypeError):
         proj.kernel_fn_host({"x": x.to(dev), "config": cfg}, state)
     proj.check_status(state)
