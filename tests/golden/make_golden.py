@@ -1,8 +1,8 @@
 """Writes tests/golden/reference_vectors.json from the reference itself.
 
-Run where the reference checkout is available (default /root/reference, or REFERENCE_ROOT):
+Run where a checkout of the reference is available, naming it in REFERENCE_ROOT:
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<checkout of Sagor0078/llm-inference-engine> python tests/golden/make_golden.py
 
 It imports bf16_proj/reference.py + checks.py UNMODIFIED (CPU generators, FP64 product) and
 records, for a fixed list of cases: digests and leading values of the generated weights and inputs,
@@ -23,7 +23,9 @@ from pathlib import Path
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF_ROOT = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+if "REFERENCE_ROOT" not in os.environ:
+    sys.exit("set REFERENCE_ROOT to a checkout of the reference (see the module docstring)")
+REF_ROOT = Path(os.environ["REFERENCE_ROOT"])
 
 INPUT_CASES = [  # (layer, m, seed, dist)
     ("qkv_gate", 1, 11, "normal"), ("qkv_gate", 8, 12, "normal"), ("qkv_gate", 32, 13, "outliers"),
