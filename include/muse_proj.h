@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 11
+#define MUSE_PROJ_ABI_VERSION 12
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -104,9 +104,11 @@ long long muse_fewtok_smem_bytes(int m, int K, int warps);
  * lo = bf16(w - hi), both multiplied into one FP32 accumulator -- the arithmetic of the reference's
  * prepare() split and _router_kernel (best_submissions/muse_bf16_proj.py:346-349, :260-287) without
  * the pre-split copies. 16 warps per CTA, unroll in {2, 4, 8} with K <= 512 * unroll (x stays in
- * registers), K % 32 == 0; x BF16, ld_x % 8 == 0. */
+ * registers), K % 32 == 0; x BF16, or FP32 when x_is_f32: the FP32-input mode of the reference's decode
+ * layer (X_F32, best_submissions/muse_decode_layer.py:165-200), x split like the weight and
+ * out = x_hi (hi + lo) + x_lo hi. ld_x counts elements of x's type, ld_x % 8 == 0. */
 int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
-                    int tok_split, void* stream);
+                    int tok_split, int x_is_f32, void* stream);
 
 /* Staging for callers whose activations live in HOST memory (page-locked for the copies to be
  * asynchronous): x goes host -> device on `stream` before the projection is launched there, and

@@ -37,7 +37,7 @@ SIGNATURES = {
                                   C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "muse_fewtok_smem_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "muse_fewtok_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                  C.c_int, C.c_void_p]),
+                                  C.c_int, C.c_int, C.c_void_p]),
     "muse_streamk_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "muse_streamk_max_contrib": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_streamk_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
@@ -52,7 +52,7 @@ SIGNATURES = {
     "muse_skinny_set_trace": (None, [C.c_void_p]),
 }
 
-ABI_VERSION = 11
+ABI_VERSION = 12
 
 
 class MuseError(RuntimeError):

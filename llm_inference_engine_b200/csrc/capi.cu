@@ -22,7 +22,7 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
                         int unroll, int tok_split, int* status, const PeerSync* peers, cudaStream_t stream);
 size_t fewtok_smem_bytes(int m, int K, int warps);
 int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
-                        int tok_split, cudaStream_t stream);
+                        int tok_split, int x_is_f32, cudaStream_t stream);
 int streamk_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                         int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int grid, int stages,
                         int out_f32, const PeerSync* peers, cudaStream_t stream);
@@ -136,8 +136,9 @@ int muse_fewtok_mma_host(const void* W, const void* x_host, void* x_device, void
 }
 
 int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
-                    int tok_split, void* stream) {
-  return muse::fewtok_f32_dispatch(W, x, out, m, N, K, ld_x, ld_out, unroll, tok_split, static_cast<cudaStream_t>(stream));
+                    int tok_split, int x_is_f32, void* stream) {
+  return muse::fewtok_f32_dispatch(W, x, out, m, N, K, ld_x, ld_out, unroll, tok_split, x_is_f32,
+                                   static_cast<cudaStream_t>(stream));
 }
 
 long long muse_fewtok_smem_bytes(int m, int K, int warps) {

@@ -295,46 +295,42 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
 // stores (best_submissions/muse_bf16_proj.py:346-349) -- and feeds both to MMAs on one FP32
 // accumulator (its _router_kernel, :260-287), so W is read once, as FP32, with no pre-split copy.
 // Up to 8 tokens per CTA (tok_split copies for more); output FP32.
-template <int NW, int U>
-__global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* __restrict__ W,
-                                                                  const __nv_bfloat16* __restrict__ x,
+// XF32 = the router's FP32-input mode of the reference's decode layer (X_F32,
+// best_submissions/muse_decode_layer.py:165-200): x is FP32, split the same way once into registers, and
+// out = x_hi (hi + lo) + x_lo hi, three MMAs per step. Its x fragments take twice the registers, so a
+// group's weights then pass through in two halves (one half in flight at a time).
+template <int NW, int U, bool XF32>
+__global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* __restrict__ W, const void* __restrict__ xv,
                                                                   float* __restrict__ out, int m, int N, int K, int ld_x,
                                                                   int ld_out, int tok_split) {
   constexpr int OUTS = 64, TOKS = 8;
+  constexpr int SUBS = XF32 && U > 1 ? 2 : 1, PS = U / SUBS;   // weight sub-batches of a group, pieces in each
   __shared__ __align__(16) float red[2][NW][OUTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const int C = static_cast<int>(gridDim.x) / tok_split, c = static_cast<int>(blockIdx.x) / tok_split;
-  {
-    const int t0 = (static_cast<int>(blockIdx.x) % tok_split) * TOKS;
-    x += static_cast<size_t>(t0) * ld_x;
-    out += static_cast<size_t>(t0) * ld_out;
-    m = m - t0 < TOKS ? m - t0 : TOKS;
-    if (m <= 0) return;
-  }
+  const int t0 = (static_cast<int>(blockIdx.x) % tok_split) * TOKS;
+  out += static_cast<size_t>(t0) * ld_out;
+  m = m - t0 < TOKS ? m - t0 : TOKS;
+  if (m <= 0) return;
   const int kblocks = K >> 5;
   const int groups = (N + 7) >> 3;
   const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
   const int first = warp * U;
-  uint4 w[2 * U], xr[U];
-  auto load = [&](int i) {
+  uint4 w[2 * PS], xr[U], xl[XF32 ? U : 1];
+  auto load = [&](int i, int h) {
     int row = (c + i * C) * 8 + g;
     row = row < N ? row : N - 1;
     const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K) + 2 * q;   // 8 FP32 = two vectors
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const bool ok = first + u < kblocks;
-      w[2 * u] = ok ? ldg_stream16(p + (first + u) * 8) : make_uint4(0u, 0u, 0u, 0u);
-      w[2 * u + 1] = ok ? ldg_stream16(p + (first + u) * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
+    for (int u = 0; u < PS; ++u) {
+      const int piece = first + h * PS + u;
+      const bool ok = piece < kblocks;
+      w[2 * u] = ok ? ldg_stream16(p + piece * 8) : make_uint4(0u, 0u, 0u, 0u);
+      w[2 * u + 1] = ok ? ldg_stream16(p + piece * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
-  if (my_groups > 0) load(0);
-  {
-    const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-      xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
-  }
+  if (my_groups > 0) load(0, 0);
   // (a, b) -> BF16 pair of the hi halves (a in the low 16 bits) and of the lo halves.
   auto split = [](uint32_t a_bits, uint32_t b_bits, uint32_t& hi, uint32_t& lo) {
     const float a = __uint_as_float(a_bits), b = __uint_as_float(b_bits);
@@ -344,21 +340,52 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
     const __nv_bfloat162 l = __floats2bfloat162_rn(ra, rb);
     lo = *reinterpret_cast<const uint32_t*>(&l);
   };
+  if constexpr (XF32) {
+    const float* xf = reinterpret_cast<const float*>(xv) + static_cast<size_t>(t0 + (g < m ? g : 0)) * ld_x;
+    const uint4* px = reinterpret_cast<const uint4*>(xf) + 2 * q;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool ok = g < m && first + u < kblocks;
+      const uint4 a = ok ? __ldg(px + (first + u) * 8) : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 b = ok ? __ldg(px + (first + u) * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
+      split(a.x, a.y, xr[u].x, xl[u].x);
+      split(a.z, a.w, xr[u].y, xl[u].y);
+      split(b.x, b.y, xr[u].z, xl[u].z);
+      split(b.z, b.w, xr[u].w, xl[u].w);
+    }
+  } else {
+    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(xv) + static_cast<size_t>(t0 + (g < m ? g : 0)) * ld_x;
+    const uint4* px = reinterpret_cast<const uint4*>(xb) + q;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    xl[0] = make_uint4(0u, 0u, 0u, 0u);
+  }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int i = 0; i < my_groups; ++i) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-      split(w[2 * u].x, w[2 * u].y, h0, l0);
-      split(w[2 * u].z, w[2 * u].w, h1, l1);
-      split(w[2 * u + 1].x, w[2 * u + 1].y, h2, l2);
-      split(w[2 * u + 1].z, w[2 * u + 1].w, h3, l3);
-      mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, h0, h1);
-      mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, h2, h3);
-      mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, l0, l1);
-      mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, l2, l3);
+    for (int h = 0; h < SUBS; ++h) {
+#pragma unroll
+      for (int u = 0; u < PS; ++u) {
+        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+        split(w[2 * u].x, w[2 * u].y, h0, l0);
+        split(w[2 * u].z, w[2 * u].w, h1, l1);
+        split(w[2 * u + 1].x, w[2 * u + 1].y, h2, l2);
+        split(w[2 * u + 1].z, w[2 * u + 1].w, h3, l3);
+        const uint4 xa = xr[h * PS + u];
+        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, h0, h1);
+        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, h2, h3);
+        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, l0, l1);
+        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, l2, l3);
+        if constexpr (XF32) {
+          const uint4 xb = xl[h * PS + u];
+          mma_bf16_16816(acc, xb.x, 0u, xb.y, 0u, h0, h1);
+          mma_bf16_16816(acc, xb.z, 0u, xb.w, 0u, h2, h3);
+        }
+      }
+      if (h + 1 < SUBS) load(i, h + 1);
+      else if (i + 1 < my_groups) load(i + 1, 0);
     }
-    if (i + 1 < my_groups) load(i + 1);
     *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
     acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
     __syncthreads();
@@ -445,10 +472,10 @@ static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, i
                               : launch_xreg_with<NW, U, HI, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s);
 }
 
-template <int NW, int U>
+template <int NW, int U, bool XF32>
 static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
                                    int tok_split, cudaStream_t s) {
-  auto kern = fewtok_xreg_f32_kernel<NW, U>;
+  auto kern = fewtok_xreg_f32_kernel<NW, U, XF32>;
   static int per_sm[64] = {0}, sms[64] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -465,22 +492,26 @@ static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int 
   const int groups = (N + 7) / 8;
   if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
-  kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), reinterpret_cast<const __nv_bfloat16*>(x),
-                                               reinterpret_cast<float*>(out), m, N, K, ld_x, ld_out, tok_split);
+  kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), x, reinterpret_cast<float*>(out), m, N, K,
+                                               ld_x, ld_out, tok_split);
   return cudaGetLastError();
 }
 
-// FP32 weight and output, 1..8 * tok_split tokens, 16 warps, unroll in {2, 4, 8} with K <= 512 * unroll.
+// FP32 weight and output, 1..8 * tok_split tokens, 16 warps, unroll in {2, 4, 8} with K <= 512 * unroll;
+// x BF16, or FP32 when x_is_f32 (ld_x counts elements of x's type).
 int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
-                        int tok_split, cudaStream_t stream) {
+                        int tok_split, int x_is_f32, cudaStream_t stream) {
   if (!W || !x || !out || N <= 0 || K <= 0) return -1;
   if (tok_split < 1 || tok_split > 4 || m < 1 || m > 8 * tok_split) return -9;
   if (K % 32 != 0 || ld_x % 8 != 0 || ld_x < K || ld_out < N || K / 32 > 16 * unroll) return -2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
   cudaError_t e = cudaErrorInvalidValue;
-  if (unroll == 8) e = launch_xreg_f32<16, 8>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
-  else if (unroll == 4) e = launch_xreg_f32<16, 4>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
-  else if (unroll == 2) e = launch_xreg_f32<16, 2>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
+#define MUSE_F32(U_)                                                                                         \
+  if (unroll == U_)                                                                                          \
+    e = x_is_f32 ? launch_xreg_f32<16, U_, true>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream)        \
+                 : launch_xreg_f32<16, U_, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, stream);
+  MUSE_F32(8) MUSE_F32(4) MUSE_F32(2)
+#undef MUSE_F32
   return static_cast<int>(e);
 }
 

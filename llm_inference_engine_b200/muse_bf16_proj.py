@@ -181,13 +181,19 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None, peers=None) 
     reference's signature) is a preallocated [m, >= n] destination whose row stride is honoured.
     `peers` (optional, column-parallel use: see tp.FusedColumnParallel) is a ctypes muse_peer_sync_t:
     the kernel then writes its slice into every rank's gathered output and `out` must be this
-    rank's gathered [m, N] tensor, which is returned."""
+    rank's gathered [m, N] tensor, which is returned.
+
+    The FP32 layers (the router) also take an FP32 x of up to 32 tokens: the FP32-input mode of the
+    reference's decode layer (X_F32, best_submissions/muse_decode_layer.py:165-200, x split into
+    BF16 hi + lo like the weight: out = x_hi (hi + lo) + x_lo hi)."""
     x, cfg = data["x"], data["config"]
     layer, n = cfg["layer"], int(cfg["n"])
     if layer not in state or layer.startswith("_"):
         raise KeyError(f"unknown layer {layer!r}")
     _require_cuda(x, "x")
     w = state[layer]
+    if x.dim() == 2 and x.dtype == torch.float32 and layer in FP32_LAYERS:
+        return _kernel_fn_f32_input(x, n, layer, state, out, peers)
     if x.dtype != torch.bfloat16 or x.dim() != 2:
         raise TypeError(f"x must be BF16 [m, K], got {x.dtype} {tuple(x.shape)}")
     m, k = x.shape
@@ -207,6 +213,33 @@ def kernel_fn(data: Inputs, state, out: torch.Tensor | None = None, peers=None) 
     return out
 
 
+F32_INPUT_MAX_TOKENS = 32
+
+
+def _kernel_fn_f32_input(x: torch.Tensor, n: int, layer: str, state, out, peers) -> torch.Tensor:
+    """The router with FP32 activations: only the register-MMA kernel has this mode (up to 32 tokens,
+    K <= 4096 in whole 32-element pieces, one GPU)."""
+    w = state[layer]
+    m, k = x.shape
+    if k != w.shape[1] or not 0 < n <= w.shape[0] or m < 1:
+        raise ValueError(f"{layer}: x {tuple(x.shape)} / n={n} do not fit W {tuple(w.shape)}")
+    if peers is not None or m > F32_INPUT_MAX_TOKENS or k % 32 or k // 32 > 128:
+        raise TypeError(f"{layer}: FP32 x is supported on one GPU for m <= {F32_INPUT_MAX_TOKENS}, K % 32 == 0, K <= 4096; "
+                        f"got m={m}, K={k}")
+    if x.stride(1) != 1 or x.data_ptr() % 16 or (m > 1 and (x.stride(0) % 8 or x.stride(0) < k)):
+        x = x.contiguous().clone()
+    if out is None:
+        out = torch.empty((m, n), device=x.device, dtype=torch.float32)
+    elif out.shape[0] != m or out.shape[1] < n or out.stride(1) != 1 or out.dtype != torch.float32:
+        raise ValueError("out must be [m, >= n], unit column stride, FP32")
+    kblocks = k // 32
+    unroll = 2 if kblocks <= 32 else 4 if kblocks <= 64 else 8
+    _capi.check(_capi.load().muse_fewtok_f32(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0) if m > 1 else k,
+                                             out.stride(0), unroll, -(-m // 8), 1, torch.cuda.current_stream(x.device).cuda_stream),
+                f"muse_fewtok_f32({layer}, m={m}, n={n}, k={k}, FP32 x)")
+    return out
+
+
 def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: int, out_ptr: int, ld_out: int, peers,
             stream: int, device) -> None:
     """One C-ABI call: the kernel `plan` names, on validated arguments."""
@@ -215,7 +248,7 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
     w = state[layer]
     status = state["_status"].data_ptr()
     if isinstance(plan, FewTokPlan) and f32:
-        _capi.check(lib.muse_fewtok_f32(w.data_ptr(), x_ptr, out_ptr, m, n, k, ld_x, ld_out, plan.unroll, plan.tok_split, stream),
+        _capi.check(lib.muse_fewtok_f32(w.data_ptr(), x_ptr, out_ptr, m, n, k, ld_x, ld_out, plan.unroll, plan.tok_split, 0, stream),
                     f"muse_fewtok_f32({layer}, m={m}, n={n}, k={k}, {plan})")
         return
     if isinstance(plan, FewTokPlan):

@@ -217,6 +217,28 @@ def cpu_kernel_fn(data, state) -> torch.Tensor:
     return xf @ state["router_hi"][:n].float().T + xf @ state["router_lo"][:n].float().T
 
 
+# ---- the decode layer's FP32-input router mode (the path's first "next" caller) --------------------
+
+def router_f32_input_model(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """The arithmetic of `_router_kernel(..., X_F32=True)` (best_submissions/muse_decode_layer.py:165-200;
+    math in README.md:192-194): x and W are FP32, each split into BF16 hi = bf16(v) and lo = bf16(v - hi),
+    and out = x_hi (W_hi + W_lo)^T + x_lo W_hi^T with FP32 accumulation (the x_lo W_lo term, ~2^-32
+    relative, is dropped). Taken in FP64 here, so this is the value the kernel should reach up to FP32
+    summation error. Parity unpinned by a golden vector: the reference checkout holds no stored outputs
+    of this mode and its Triton kernel does not run on CPU; the FP64 product of the unsplit inputs
+    (`router_f32_input_reference`) bounds it, "FP32-accurate to ~2^-16" in the reference's words."""
+    xh = x.to(torch.bfloat16)
+    xl = (x - xh.float()).to(torch.bfloat16)
+    wh = w.to(torch.bfloat16)
+    wl = (w - wh.float()).to(torch.bfloat16)
+    return (xh.double() @ (wh.double() + wl.double()).T + xl.double() @ wh.double().T).float()
+
+
+def router_f32_input_reference(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """FP64 product of the FP32 inputs as given: the yardstick of the mode above."""
+    return (x.double() @ w.double().T)
+
+
 # ---- the benchmark's own synthetic data and acceptance rule ---------------------------------------
 
 def target_weights(seed: int = WEIGHTS_SEED, device: str = "cpu", layers=TARGET_LAYERS, only=None):

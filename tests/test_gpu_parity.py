@@ -376,7 +376,7 @@ def test_fewtok_f32_entry_point_meets_the_router_tolerance(dev, case):
     for _ in range(3):
         out = torch.full((m, n + 3), 3.0, device=dev, dtype=torch.float32)
         _capi.check(lib.muse_fewtok_f32(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0), unroll,
-                                        tok_split, torch.cuda.current_stream(dev).cuda_stream), "muse_fewtok_f32")
+                                        tok_split, 0, torch.cuda.current_stream(dev).cuda_stream), "muse_fewtok_f32")
         torch.cuda.synchronize(dev)
         outs.append(out)
     assert bool((outs[0][:, n:] == 3.0).all())
@@ -384,7 +384,41 @@ def test_fewtok_f32_entry_point_meets_the_router_tolerance(dev, case):
     assert err < 1e-5, err
     assert all(torch.equal(outs[0], o) for o in outs[1:])
     call = lambda m_, k_, unroll_, split_: lib.muse_fewtok_f32(w.data_ptr(), x.data_ptr(), outs[0].data_ptr(), m_, n, k_,
-                                                               x.stride(0), outs[0].stride(0), unroll_, split_, None)
+                                                               x.stride(0), outs[0].stride(0), unroll_, split_, 0, None)
     assert call(8 * tok_split + 1, k, unroll, tok_split) == -9     # more than 8 tokens per copy of the walk
     assert call(m, k, 1, tok_split) != 0                           # a row does not fit one batch of loads
     assert call(m, k, unroll, 5) == -9
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 13, 32])
+def test_router_takes_fp32_activations(oracle, proj, dev, target_setup, m):
+    """The decode layer's FP32-input router mode through kernel_fn: x FP32, split to BF16 hi + lo in the
+    kernel like the weight. Against the FP64 product of the unsplit inputs the error is at the 2^-16
+    level the reference states (here: relative L2 <= 1e-5, the router's tolerance); against the FP64
+    evaluation of the same three-term split it is FP32 summation error only; and it is far closer
+    than the BF16-x call on the same numbers."""
+    w_cpu, state = target_setup
+    g = torch.Generator().manual_seed(300 + m)
+    x = torch.randn((m, 4096), generator=g)
+    cfg = {"m": m, "n": 256, "k": 4096, "layer": "router"}
+    out = proj.kernel_fn({"x": x.to(dev), "config": cfg}, state)
+    proj.check_status(state)
+    assert out.dtype == torch.float32 and tuple(out.shape) == (m, 256)
+    out = out.cpu().double()
+    ref = oracle.router_f32_input_reference(x, w_cpu["router"])
+    model = oracle.router_f32_input_model(x, w_cpu["router"]).double()
+    rel = lambda a, b: float((a - b).norm() / b.norm())
+    assert rel(out, ref) < 1e-5, rel(out, ref)
+    assert rel(out, model) < 2e-6, rel(out, model)
+    coarse = proj.kernel_fn({"x": x.to(torch.bfloat16).to(dev), "config": cfg}, state).cpu().double()
+    assert rel(coarse, ref) > 20 * rel(out, ref)
+    # strided FP32 x and a preallocated output
+    xs = torch.zeros((m, 4096 + 8))
+    xs[:, :4096] = x
+    dst = torch.full((m, 300), 7.0, device=dev)
+    proj.kernel_fn({"x": xs.to(dev)[:, :4096], "config": cfg}, state, out=dst)
+    assert torch.equal(dst[:, :256].cpu().double(), out) and bool((dst[:, 256:] == 7.0).all())
+    with pytest.raises(TypeError):
+        proj.kernel_fn({"x": torch.zeros((33, 4096), device=dev), "config": dict(cfg, m=33)}, state)   # beyond 32 tokens
+    with pytest.raises(TypeError):
+        proj.kernel_fn({"x": torch.zeros((2, 4096), device=dev), "config": {"m": 2, "n": 1024, "k": 4096, "layer": "pooler"}}, state)

@@ -182,3 +182,17 @@ def test_shard_bounds_partition_the_rows():
         tp.shard_bounds(1000, 3, 0)
     with pytest.raises(ValueError):
         tp.shard_bounds(1024, 4, 4)
+
+
+def test_oracle_model_of_the_fp32_input_router_mode():
+    """The three-term split (x_hi W_hi + x_hi W_lo + x_lo W_hi) sits within the router's 1e-5 of the
+    FP64 product of the unsplit FP32 inputs, three orders of magnitude closer than rounding x to BF16."""
+    from oracle import muse_proj_oracle as oracle
+
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn((8, 4096), generator=g)
+    w = torch.randn((256, 4096), generator=g) * 0.02
+    ref = oracle.router_f32_input_reference(x, w)
+    rel = lambda a: float((a.double() - ref).norm() / ref.norm())
+    assert rel(oracle.router_f32_input_model(x, w)) < 1e-5
+    assert rel(x.to(torch.bfloat16).double() @ w.double().T) > 1e-3
