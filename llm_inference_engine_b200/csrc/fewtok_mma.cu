@@ -1,5 +1,6 @@
-// out[m, N] = x[m, K] . W[N, K]^T for 2..16 tokens against a BF16 weight, as a persistent streaming
-// walk over the weight with register-level tensor-core MMAs (mma.sync m16n8k16): the latency-bound
+// out[m, N] = x[m, K] . W[N, K]^T for 1..16 tokens per CTA against a BF16 (or, for the router, FP32)
+// weight, as a persistent streaming walk over the weight with register-level tensor-core MMAs
+// (mma.sync m16n8k16): the latency-bound
 // regime between the one-token GEMV and the TMEM kernel, where allocating tensor memory, building a
 // shared-memory pipeline and reducing split-K partials across a cluster cost more than they save.
 // Extends the reference's m = 1 GEMV (bf16_proj/gemv1.cu:27-125) to the smallest of the m <= 32 calls
@@ -18,6 +19,8 @@
 // pieces of K in every group, so its A fragments never change: fewtok_xreg_kernel loads them once from
 // global memory into registers and runs with no shared-memory copy of x at all. Tokens 8..15 double
 // those registers, which a 32-warp CTA only has for U <= 2; 16 warps x 8 loads serve K = 4096 there.
+// That kernel also runs column-parallel (self-validating lines into the peers' staging) and as several
+// interleaved walks over disjoint token blocks; fewtok_xreg_f32_kernel is its FP32-weight form.
 #include "common.cuh"
 
 namespace muse {
