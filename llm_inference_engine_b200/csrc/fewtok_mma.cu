@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
       // The call number, and the book-keeping that advances it: the last CTA to get HERE closes the number,
       // because by then every CTA of the grid has read it. Done first so that nothing waits on it at the end.
       int* mine = ps.flags[ps.rank];
-      const int e = peer_epoch(ps);
+      const int e = ld_acquire_sys(mine + 16) + 1;   // acquire: the count below may not overtake this read
       s_epoch = e;
       if (atomicAdd(mine + 17, 1) == static_cast<int>(gridDim.x) - 1) {
         mine[17] = 0;
