@@ -151,7 +151,8 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 // PEERS = column-parallel: every CTA stores its rows at columns [col0, col0 + N) of this rank's gathered
 // output and sends them to every peer's staging as self-validating lines; when its groups are done it
 // unpacks its share of the lines the peers sent here. No fence, no flag, no wait on another CTA.
-template <int NW, int U, bool HI, bool PEERS>
+// VEC (one GPU) = 16-byte output stores: the caller guarantees N % 8 == 0 and 16-byte aligned rows of out.
+template <int NW, int U, bool HI, bool PEERS, bool VEC>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ x,
                                                               __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
@@ -249,7 +250,15 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
       for (int wv = 0; wv < NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
       const int t = threadIdx.x >> 3, r = threadIdx.x & 7;
       const int grp = c + i * C, row0 = grp * 8;
-      if constexpr (!PEERS) {
+      if constexpr (!PEERS && VEC) {
+        // 8 rows of a token = 8 neighbouring lanes: one 16-byte store per token and group instead of eight
+        // 2-byte ones (what makes an output in page-locked host memory affordable: one PCIe write each).
+        const uint32_t v = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sum)));
+        const uint32_t p01 = v | (__shfl_down_sync(0xffffffffu, v, 1) << 16);
+        const uint32_t p23 = __shfl_down_sync(0xffffffffu, p01, 2);
+        const uint32_t p45 = __shfl_down_sync(0xffffffffu, p01, 4), p67 = __shfl_down_sync(0xffffffffu, p23, 4);
+        if (r == 0 && t < m) *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ld_out + row0) = make_uint4(p01, p23, p45, p67);
+      } else if constexpr (!PEERS) {
         if (t < m && row0 + r < N) out[static_cast<size_t>(t) * ld_out + row0 + r] = __float2bfloat16_rn(sum);
       } else {
         // The 8 rows of a token sit in 8 neighbouring lanes: gather them into one 16-byte vector (N % 8 == 0 here).
@@ -440,10 +449,10 @@ static cudaError_t launch_fewtok(const void* W, const void* x, void* out, int m,
   return cudaGetLastError();
 }
 
-template <int NW, int U, bool HI, bool PEERS>
+template <int NW, int U, bool HI, bool PEERS, bool VEC>
 static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
                                     int tok_split, int* status, const PeerSync& ps, cudaStream_t s) {
-  auto kern = fewtok_xreg_kernel<NW, U, HI, PEERS>;
+  auto kern = fewtok_xreg_kernel<NW, U, HI, PEERS, VEC>;
   static int per_sm[64] = {0}, sms[64] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -471,8 +480,10 @@ static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int
 template <int NW, int U, bool HI>
 static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
                                int tok_split, int* status, const PeerSync& ps, cudaStream_t s) {
-  return peer_active_host(ps) ? launch_xreg_with<NW, U, HI, true>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s)
-                              : launch_xreg_with<NW, U, HI, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s);
+  if (peer_active_host(ps)) return launch_xreg_with<NW, U, HI, true, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s);
+  const bool vec = N % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | (static_cast<uintptr_t>(ld_out) * 2)) & 15) == 0;
+  return vec ? launch_xreg_with<NW, U, HI, false, true>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s)
+             : launch_xreg_with<NW, U, HI, false, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s);
 }
 
 template <int NW, int U, bool XF32>

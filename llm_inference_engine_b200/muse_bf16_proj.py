@@ -321,12 +321,18 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record:
         graphs = state.setdefault("_host_graphs", {})
         # The plain form once (it also warms every lazily created resource), then the recording.
         kernel_fn_host(data, state, out=out, record=False)
+        # The register-MMA kernel stores its output as 16-byte vectors, one PCIe write each when the
+        # destination is page-locked host memory (device-addressable under unified addressing): it then
+        # writes the caller's buffer itself while it streams the weights, and the copy-out disappears.
+        direct = isinstance(plan, FewTokPlan) and not f32 and n % 8 == 0 and out.data_ptr() % 16 == 0
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             rec = torch.cuda.current_stream(w.device).cuda_stream
             x_dev.copy_(x, non_blocking=True)
-            _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out_dev.data_ptr(), n, None, rec, w.device)
-            out.copy_(out_dev, non_blocking=True)
+            _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out.data_ptr() if direct else out_dev.data_ptr(), n, None,
+                    rec, w.device)
+            if not direct:
+                out.copy_(out_dev, non_blocking=True)
         if len(graphs) >= HOST_GRAPH_SLOTS:
             graphs.pop(next(iter(graphs)))
         # the tensors stay alive as long as their addresses are baked in
