@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 12
+#define MUSE_PROJ_ABI_VERSION 13
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -116,6 +116,11 @@ int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K
  * stream). Positive = CUDA error. No counterpart in the reference, whose harness hands kernel_fn
  * device tensors (best_submissions/muse_bf16_proj.py:369-372). */
 int muse_copy_h2d_async(void* dst_device, const void* src_host, long long bytes, void* stream);
+/* The same copy-in done by a small kernel that reads the page-locked host buffer directly (it must be
+ * device-addressable: cudaHostAlloc / cudaHostRegister memory under unified addressing); bytes a
+ * multiple of 16, both pointers 16-byte aligned. For a few KB the consumer then waits on a
+ * kernel-to-kernel dependency instead of a copy-engine hand-off. */
+int muse_fetch_host(void* dst_device, const void* src_host, long long bytes, void* stream);
 int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, void* stream);
 /* The whole round trip of one muse_fewtok_mma call in one entry: x_host [m, K] -> x_device, the
  * kernel (contiguous x and out), out_device [m, N] -> out_host, stream synchronised. */

@@ -63,6 +63,15 @@ static int encode_2d(CUtensorMap* tm, const void* base, long long rows, long lon
   return static_cast<int>(r);
 }
 __global__ void nop_kernel() {}
+
+// Copies `vecs` 16-byte vectors from page-locked host memory (device-addressable) into device memory with
+// plain loads: for a few KB this is a kernel-to-kernel dependency for the consumer instead of a copy-engine
+// hand-off.
+__global__ void fetch_host_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long vecs) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
 }  // namespace muse
 
 extern "C" {
@@ -106,6 +115,18 @@ int muse_copy_h2d_async(void* dst_device, const void* src_host, long long bytes,
   if (!dst_device || !src_host || bytes < 0) return -1;
   return static_cast<int>(cudaMemcpyAsync(dst_device, src_host, static_cast<size_t>(bytes), cudaMemcpyHostToDevice,
                                           static_cast<cudaStream_t>(stream)));
+}
+
+int muse_fetch_host(void* dst_device, const void* src_host, long long bytes, void* stream) {
+  if (!dst_device || !src_host || bytes < 0 || bytes % 16 ||
+      ((reinterpret_cast<uintptr_t>(dst_device) | reinterpret_cast<uintptr_t>(src_host)) & 15))
+    return -1;
+  if (bytes == 0) return 0;
+  const long long vecs = bytes / 16;
+  const int grid = static_cast<int>(vecs / 256 + 1 < 148 ? vecs / 256 + 1 : 148);
+  muse::fetch_host_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(dst_device), static_cast<const uint4*>(src_host), vecs);
+  return static_cast<int>(cudaGetLastError());
 }
 
 int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, void* stream) {

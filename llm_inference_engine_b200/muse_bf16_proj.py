@@ -271,6 +271,9 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
                 f"muse_skinny_tc({layer}, m={m}, n={n}, k={k}, {plan})")
 
 
+FETCH_X_BY_KERNEL = True
+FETCH_MAX_TOKENS = 8        # beyond: the copy engine
+DIRECT_OUT_MAX_TOKENS = 8   # beyond: 16-byte PCIe writes cost more than the copy-out they replace
 HOST_GRAPH_SLOTS = 64   # recorded round trips kept per state (oldest dropped first)
 _EMPTY: dict = {}
 
@@ -281,8 +284,10 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record:
     given: contiguous [m, n], page-locked), complete when the call returns. x is staged into a device
     buffer kept per (layer, m, n), the projection runs on the current stream, and the result is copied
     back and waited for. When the caller passes the same x and out tensors again (the normal case: its
-    own pinned buffers), the copy-in, launch and copy-out are recorded once as a CUDA graph and replayed
-    (`record=False` keeps the plain form: one C-ABI call for the register-MMA plans, three otherwise).
+    own pinned buffers), the copy-in, launch and copy-out are recorded once as a CUDA graph and replayed;
+    up to 8 tokens the recording has no copy nodes at all (x comes in through muse_fetch_host, and the
+    projection kernel writes the pinned output itself). `record=False` keeps the plain form: one C-ABI
+    call for the register-MMA plans, three otherwise.
     Beyond the reference, whose harness owns the transfers (best_submissions/muse_bf16_proj.py:369-372)."""
     x, cfg = data["x"], data["config"]
     layer, n = cfg["layer"], int(cfg["n"])
@@ -324,11 +329,15 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record:
         # The register-MMA kernel stores its output as 16-byte vectors, one PCIe write each when the
         # destination is page-locked host memory (device-addressable under unified addressing): it then
         # writes the caller's buffer itself while it streams the weights, and the copy-out disappears.
-        direct = isinstance(plan, FewTokPlan) and not f32 and n % 8 == 0 and out.data_ptr() % 16 == 0
+        direct = (isinstance(plan, FewTokPlan) and not f32 and n % 8 == 0 and out.data_ptr() % 16 == 0
+                  and m <= DIRECT_OUT_MAX_TOKENS)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             rec = torch.cuda.current_stream(w.device).cuda_stream
-            x_dev.copy_(x, non_blocking=True)
+            if FETCH_X_BY_KERNEL and m <= FETCH_MAX_TOKENS and x.data_ptr() % 16 == 0:   # x comes in by a small kernel
+                _capi.check(lib.muse_fetch_host(x_dev.data_ptr(), x.data_ptr(), m * k * 2, rec), "muse_fetch_host")
+            else:
+                x_dev.copy_(x, non_blocking=True)
             _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out.data_ptr() if direct else out_dev.data_ptr(), n, None,
                     rec, w.device)
             if not direct:
