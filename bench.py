@@ -372,7 +372,7 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
     return {"value": us, "unit": "us/call", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "how": "wall clock around pinned-host x -> device, the projection, result -> pinned host, stream sync, per call; "
                    + ("kernel_fn_host(): copy-in, launch and copy-out recorded once per buffer pair as a CUDA graph, replayed and "
-                      "synchronised every call; up to 8 tokens x comes in through a fetch kernel and the projection kernel writes "
+                      "synchronised every call; x comes in through a fetch kernel, and up to 8 tokens the projection kernel writes "
                       "the pinned output itself" if h.world == 1 else "torch copies around the column-parallel kernel_fn()")}
 
 
