@@ -119,7 +119,8 @@ int muse_copy_h2d_async(void* dst_device, const void* src_host, long long bytes,
 /* The same copy-in done by a small kernel that reads the page-locked host buffer directly (it must be
  * device-addressable: cudaHostAlloc / cudaHostRegister memory under unified addressing); bytes a
  * multiple of 16, both pointers 16-byte aligned. For a few KB the consumer then waits on a
- * kernel-to-kernel dependency instead of a copy-engine hand-off. */
+ * kernel-to-kernel dependency instead of a copy-engine hand-off. The kernel is a plain 16-byte copy,
+ * so with the pointers swapped (destination in page-locked host memory) it is the copy-out as well. */
 int muse_fetch_host(void* dst_device, const void* src_host, long long bytes, void* stream);
 int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, void* stream);
 /* The whole round trip of one muse_fewtok_mma call in one entry: x_host [m, K] -> x_device, the

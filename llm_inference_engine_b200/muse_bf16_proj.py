@@ -272,6 +272,7 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
 
 
 FETCH_X_BY_KERNEL = True
+STORE_OUT_BY_KERNEL = True   # the copy-out of the larger calls by the same small kernel (786 KB: 5 us less than the copy engine)
 FETCH_MAX_TOKENS = 32       # x up to 256 KB: the fetch kernel beats the copy engine at every size measured
 DIRECT_OUT_MAX_TOKENS = 8   # beyond: 16-byte PCIe writes cost more than the copy-out they replace
 HOST_GRAPH_SLOTS = 64   # recorded round trips kept per state (oldest dropped first)
@@ -340,7 +341,10 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record:
                 x_dev.copy_(x, non_blocking=True)
             _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out.data_ptr() if direct else out_dev.data_ptr(), n, None,
                     rec, w.device)
-            if not direct:
+            if not direct and STORE_OUT_BY_KERNEL and out.data_ptr() % 16 == 0 and (out.numel() * out.element_size()) % 16 == 0:
+                _capi.check(lib.muse_fetch_host(out.data_ptr(), out_dev.data_ptr(), out.numel() * out.element_size(), rec),
+                            "muse_fetch_host (copy-out)")
+            elif not direct:
                 out.copy_(out_dev, non_blocking=True)
         if len(graphs) >= HOST_GRAPH_SLOTS:
             graphs.pop(next(iter(graphs)))
