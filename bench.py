@@ -354,6 +354,9 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
             if h.world == 1:
                 h.proj.kernel_fn_host({"x": xh, "config": cfgs[j]}, states[j], out=oh)
                 continue
+            if h.fused is not None:
+                h.fused.kernel_fn_host({"x": xh, "config": cfgs[j]}, states[j], oh)
+                continue
             xd = xh.to(h.device, non_blocking=True)
             out = h.call(WORKLOAD_LAYER, xd, states[j])
             oh.copy_(out, non_blocking=True)
@@ -373,7 +376,10 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
             "how": "wall clock around pinned-host x -> device, the projection, result -> pinned host, stream sync, per call; "
                    + ("kernel_fn_host(): copy-in, launch and copy-out recorded once per buffer pair as a CUDA graph, replayed and "
                       "synchronised every call; x comes in through a fetch kernel, and up to 8 tokens the projection kernel writes "
-                      "the pinned output itself" if h.world == 1 else "torch copies around the column-parallel kernel_fn()")}
+                      "the pinned output itself" if h.world == 1 else
+                      "FusedColumnParallel.kernel_fn_host(): fetch kernel, column-parallel kernel with its exchange, copy kernel, "
+                      "recorded as a CUDA graph per buffer pair" if h.fused is not None else
+                      "torch copies around the column-parallel kernel_fn()")}
 
 
 def load_traffic() -> dict:

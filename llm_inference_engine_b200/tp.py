@@ -106,6 +106,7 @@ class FusedColumnParallel(ColumnParallelProjection):
         self._capi = _capi
         self._bufs: dict[str, torch.Tensor] = {}
         self._ll: dict[str, torch.Tensor] = {}
+        self._host_graphs: dict = {}
         self._peers: dict[str, object] = {}
         self._handles: list = []
         self._flags = None
@@ -163,3 +164,42 @@ class FusedColumnParallel(ColumnParallelProjection):
         out = self._bufs[layer][:m]
         local = {"x": data["x"], "config": self.local_config(data["config"])}
         return self._kernel_fn(local, state, out=out, peers=self._peers[layer])
+
+    def kernel_fn_host(self, data: dict, state, out: torch.Tensor) -> torch.Tensor:
+        """kernel_fn for activations in page-locked HOST memory: x [m, K] BF16 comes in through a small
+        fetch kernel, the column-parallel kernel runs (exchange included), and the gathered [m, N] is
+        copied into `out` (page-locked, contiguous) by the same small kernel; the three launches are
+        recorded once per (layer, m, x, out) as a CUDA graph, replayed and synchronised on every call.
+        Every rank must make the same calls in the same order, as for kernel_fn."""
+        x = data["x"]
+        layer = data["config"]["layer"]
+        m, k = x.shape
+        key = (layer, m, x.data_ptr(), out.data_ptr())
+        entry = self._host_graphs.get(key)
+        if entry is None:
+            n = self.rows[layer]
+            if (x.is_cuda or out.is_cuda or not x.is_pinned() or not out.is_pinned() or not x.is_contiguous()
+                    or not out.is_contiguous() or tuple(out.shape) != (m, n) or x.dtype != torch.bfloat16
+                    or out.dtype != self._bufs[layer].dtype or m > self.max_tokens):
+                raise ValueError("x and out must be contiguous page-locked CPU tensors, x BF16 [m, K], out [m, N] in the layer's output type")
+            device = self._bufs[layer].device
+            x_dev = torch.empty((m, k), device=device, dtype=torch.bfloat16)
+            lib = self._capi.load()
+            cfg = dict(data["config"])
+
+            def body(stream: int) -> None:
+                self._capi.check(lib.muse_fetch_host(x_dev.data_ptr(), x.data_ptr(), m * k * 2, stream), "muse_fetch_host")
+                gathered = self.kernel_fn({"x": x_dev, "config": cfg}, state)
+                self._capi.check(lib.muse_fetch_host(out.data_ptr(), gathered.data_ptr(), out.numel() * out.element_size(), stream),
+                                 "muse_fetch_host (copy-out)")
+
+            cur = torch.cuda.current_stream(device)
+            body(cur.cuda_stream)          # once in the open: every lazily created resource exists before the recording
+            cur.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                body(torch.cuda.current_stream(device).cuda_stream)
+            entry = self._host_graphs[key] = (graph, x, out, x_dev, device)
+        entry[0].replay()
+        torch.cuda.current_stream(entry[4]).synchronize()
+        return out

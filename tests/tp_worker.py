@@ -54,6 +54,18 @@ def main() -> None:
             same_kernel = plan == proj.plan_for(state, layer, m, *shape, fused=True)
             if same_kernel and getattr(plan, "groups", 1) == 1 and not torch.equal(a, b):
                 bad.append(f"fused != nccl bitwise: {layer} m={m}")
+    # activations in page-locked host memory: recorded round trip, twice per shape (record, then replay with new x)
+    for layer, m in (("qkv_gate", 1), ("qkv_gate", 8), ("o", 32), ("qkv_gate", 64)):
+        data = oracle.target_input(m, layer, 8100 + m, layers=layers)
+        xh = data["x"].clone().pin_memory()
+        oh = torch.empty((m, layers[layer][0]), dtype=torch.bfloat16).pin_memory()
+        for rep in range(2):
+            if rep:
+                xh.copy_(oracle.target_input(m, layer, 8200 + m, layers=layers)["x"])
+            got = fused.kernel_fn_host({"x": xh, "config": data["config"]}, state, oh).clone()
+            want = fused.kernel_fn({"x": xh.to(dev), "config": data["config"]}, state).cpu()
+            if not torch.equal(got, want):
+                bad.append(f"kernel_fn_host != kernel_fn: {layer} m={m} rep={rep}")
     # graph replays of the fused path: every rank replays the same graph the same number of times
     # (m = 64: the TMEM kernel's epilogue exchange; m = 32, 8, 1: the register-MMA kernel's lines, with and without token split)
     stream = torch.cuda.Stream(dev)
