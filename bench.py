@@ -349,12 +349,29 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
 
     cfgs = [{"m": m, "n": n, "k": k, "layer": WORKLOAD_LAYER} for m in WORKLOAD_TOKENS]
 
+    # Column-parallel: the recorded host round trip is used only if its first call worked on EVERY rank
+    # (a rank that cannot record it must not leave the others waiting in a fused kernel).
+    fused_host = h.world > 1 and h.fused is not None
+    if fused_host:
+        import torch.distributed as dist
+
+        ok = 1
+        try:
+            with torch.cuda.stream(stream):
+                h.fused.kernel_fn_host({"x": xs_host[0], "config": cfgs[0]}, states[0], outs_host[0])
+        except Exception as e:  # noqa: BLE001
+            print(f"[bench] rank {h.rank}: fused host round trip unavailable: {type(e).__name__}: {e}", file=sys.stderr)
+            ok = 0
+        flag = torch.tensor([ok], device=h.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        fused_host = bool(flag.item())
+
     def one_step():
         for j, (xh, oh) in enumerate(zip(xs_host, outs_host)):
             if h.world == 1:
                 h.proj.kernel_fn_host({"x": xh, "config": cfgs[j]}, states[j], out=oh)
                 continue
-            if h.fused is not None:
+            if fused_host:
                 h.fused.kernel_fn_host({"x": xh, "config": cfgs[j]}, states[j], oh)
                 continue
             xd = xh.to(h.device, non_blocking=True)
@@ -378,7 +395,7 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
                       "synchronised every call; x comes in through a fetch kernel, and up to 8 tokens the projection kernel writes "
                       "the pinned output itself" if h.world == 1 else
                       "FusedColumnParallel.kernel_fn_host(): fetch kernel, column-parallel kernel with its exchange, copy kernel, "
-                      "recorded as a CUDA graph per buffer pair" if h.fused is not None else
+                      "recorded as a CUDA graph per buffer pair" if fused_host else
                       "torch copies around the column-parallel kernel_fn()")}
 
 
