@@ -54,6 +54,23 @@ MAX_COPIES = 160
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "us/call (CUDA-graph, cold L2)"
+# one description of the workload for both arms, so that their `config.workload` strings are equal
+WORKLOAD_TEXT = (f"{WORKLOAD_LAYER} projection: x [m,4096] bf16 ~N(0,1), W [12288,4096] bf16 ~N(0,0.02), "
+                 f"m in {list(WORKLOAD_TOKENS)}; value = mean time of the six calls")
+L2_TEXT = "cold: every call reads a weight copy that is not in cache (604 MB of distinct weights per pass vs 126 MB L2)"
+# Column-parallel calls compared before any timing (layer, m): each exchange protocol and kernel family.
+PARITY_CASES = (("qkv_gate", 1), ("qkv_gate", 8), ("qkv_gate", 16), ("qkv_gate", 32), ("qkv_gate", 64), ("qkv_gate", 256),
+                ("o", 1), ("o", 8), ("o", 32), ("o", 128), ("router", 1), ("router", 8), ("router", 128))
+# DRAM bytes (read + write) per launch from one ncu capture per kernel on ONE GPU (profiles/*.md); a static
+# figure the line carries for comparison with `bytes_per_launch`, not something measured in this run.
+NCU_TRAFFIC = {
+    "fewtok_xreg<32,4,false> qkv_gate m=8": 104474368,
+    "skinny_tc qkv_gate m=32": 104364800,
+    "skinny_tc qkv_gate m=256": 106700000,
+    "gemv1_rows o m=1": 33578496,
+    "skinny_tc router m=128": 5302016,
+    "fewtok_xreg_f32<16,8> router m=32": 4471040,
+}
 
 
 def algorithmic_bytes(layer: str, m: int, n: int, k: int) -> int:
@@ -180,8 +197,7 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": METRIC, "value": us, "unit": "us/call", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": us * len(WORKLOAD_TOKENS) / 1e3, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{WORKLOAD_LAYER} projection [12288,4096] bf16, m in {list(WORKLOAD_TOKENS)}, host CPU",
-                   "l2": "n/a (CPU)"},
+        "config": {"workload": WORKLOAD_TEXT, "l2": L2_TEXT, "arm": "reference CPU path on the host cores (no L2 control)"},
         "cpu_baseline": {"value": us, "unit": "us/call", "cores": info["cores"], "kind": "port", "sample": sample,
                          "per_m_us": info["per_m_us"]},
         "e2e": {"value": us, "unit": "us/call", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -335,6 +351,57 @@ def case_table(h: Harness, layers, steps: int, warmup: int, peak: float, only=No
     return rows
 
 
+def gather_check(h: Harness) -> dict:
+    """Column-parallel only, before any timing: every PARITY_CASES call through the fused exchange and through
+    kernel + NCCL all-gather, both against an FP32 product of the FULL weight on this rank (BF16: rtol 1e-2 /
+    atol 1e-2; router: relative L2 <= 1e-5), and against each other bit for bit where both run the same
+    deterministic plan. Every rank checks its own gathered copy; the verdicts are combined; a mismatch
+    ends the run."""
+    dist = h.dist
+    bad: list[str] = []
+    n_cases = 0
+    worst = 0.0
+    for layer in dict.fromkeys(c[0] for c in PARITY_CASES):
+        n, k = LAYERS[layer]
+        full = make_weight(layer, h.device, SEED).float()
+        state = h.states(layer, 1)[0]
+        for m in (c[1] for c in PARITY_CASES if c[0] == layer):
+            x = make_x(layer, m, h.device, 4000 + m)
+            want = x.float() @ full.T
+            outs = {}
+            if h.fused is not None:
+                outs["fused"] = h.call(layer, x, state, "best").clone()
+            outs["nccl"] = h.call(layer, x, state, "nccl")
+            for tag, got in outs.items():
+                n_cases += 1
+                if layer in FP32_LAYERS:
+                    err = float((got.double() - want.double()).norm() / want.double().norm())
+                    ok = err <= 1e-5
+                else:
+                    err = float((got.float() - want).abs().max())
+                    ok = bool(torch.allclose(got.float(), want, rtol=1e-2, atol=1e-2))
+                worst = max(worst, err) if layer not in FP32_LAYERS else worst
+                if not ok:
+                    bad.append(f"{tag} {layer} m={m}: error {err:.3e}")
+            if len(outs) == 2:
+                local = (n // h.world, k)
+                plan = h.proj.plan_for(state, layer, m, *local)
+                if plan == h.proj.plan_for(state, layer, m, *local, fused=True) and getattr(plan, "groups", 1) == 1:
+                    n_cases += 1
+                    if not torch.equal(outs["fused"], outs["nccl"]):
+                        bad.append(f"fused != nccl bitwise: {layer} m={m}")
+        h.proj.check_status(state)
+        del state, full
+        torch.cuda.empty_cache()
+    flag = torch.tensor([len(bad)], device=h.device, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.SUM)
+    for line in bad:
+        print(f"[bench] rank {h.rank}: parity: {line}", file=sys.stderr, flush=True)
+    return {"cases": n_cases, "ok": int(flag.item()) == 0, "ranks": h.world, "max_abs_err_bf16": worst,
+            "what": "fused exchange and kernel + NCCL all-gather vs FP32 x @ W_full.T on every rank, and vs each other "
+                    "bitwise where the plan is the same"}
+
+
 def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
     """The same six calls through the public API from HOST buffers: per call, x is copied from pinned
     host memory, the projection runs, and the result is copied back to pinned host memory and waited
@@ -399,16 +466,6 @@ def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
                       "torch copies around the column-parallel kernel_fn()")}
 
 
-def load_traffic() -> dict:
-    p = ROOT / "profiles" / "ncu_traffic.json"
-    if p.exists():
-        try:
-            return json.loads(p.read_text())
-        except Exception:  # noqa: BLE001
-            return {}
-    return {}
-
-
 def run_ours(args) -> None:
     # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line there.
     real_stdout = os.dup(1)
@@ -443,6 +500,15 @@ def run_ours(args) -> None:
         if rank == 0:
             emit({"case": rows[0], "clocks": sampler.summary()})
         return
+
+    parity = None
+    if world > 1:
+        parity = gather_check(h)
+        if not parity["ok"]:
+            if rank == 0:
+                emit({"error": "column-parallel output mismatch before timing", "parity_checked": parity})
+            dist.destroy_process_group()
+            raise SystemExit(3)
 
     # ---- headline: K steps of the six-call graph
     states = h.states(WORKLOAD_LAYER, len(WORKLOAD_TOKENS))
@@ -489,7 +555,7 @@ def run_ours(args) -> None:
     for r in work:
         share[r["kernel"]] = share.get(r["kernel"], 0.0) + r.get("kernel_us", r["us"])
     dom = max((r for r in work if r["kernel"] == max(share, key=share.get)), key=lambda r: r["m"]) if work else None
-    traffic = load_traffic()
+    traffic = NCU_TRAFFIC
     if dom is not None:
         dur_us = dom.get("kernel_us", dom["us"])
         achieved = dom["bytes"] / dur_us / 1e3
@@ -498,7 +564,9 @@ def run_ours(args) -> None:
                     "share_of_step": {kf: round(v / sum(share.values()), 3) for kf, v in share.items()},
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
-                    "traffic": (tr / world if tr else None), "bytes_per_launch": dom["bytes"], "us_per_launch": dur_us,
+                    "traffic": (tr / world if tr else None),
+                    "traffic_kind": "static: ncu dram bytes of one 1-GPU launch of this kernel (profiles/), divided by the world size",
+                    "bytes_per_launch": dom["bytes"], "us_per_launch": dur_us,
                     "frac_of_8tbs": achieved / NOMINAL_HBM_GBS}
     else:
         by = sum(algorithmic_bytes(WORKLOAD_LAYER, m, n // world, k) for m in WORKLOAD_TOKENS) / len(WORKLOAD_TOKENS)
@@ -510,9 +578,8 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": value, "unit": "us/call", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": f"{WORKLOAD_LAYER} projection: x [m,4096] bf16 ~N(0,1), W [12288,4096] bf16 ~N(0,0.02), "
-                               f"m in {list(WORKLOAD_TOKENS)}; one step = the six calls in one CUDA graph",
-                   "l2": "cold: inputs larger than L2 (each call reads its own 100.7 MB weight copy, 604 MB per step vs 126 MB L2); no flush in the timed region",
+        "config": {"workload": WORKLOAD_TEXT, "l2": L2_TEXT,
+                   "arm": "one step = the six calls in one CUDA graph, each on its own weight copy; no flush in the timed region",
                    "parallelism": ("single GPU" if world == 1 else
                                    f"column-parallel x{world} (rows sharded), all-gather fused into the kernel (peer stores over NVLink)"
                                    if h.fused is not None else
@@ -527,6 +594,8 @@ def run_ours(args) -> None:
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if parity is not None:
+        line["parity_checked"] = parity
     emit(line)
     if world > 1:
         dist.destroy_process_group()

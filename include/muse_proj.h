@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 13
+#define MUSE_PROJ_ABI_VERSION 14
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -92,11 +92,15 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
  * block of 8 or 16 tokens, and W is read from HBM once and a second time from L2. Otherwise
  * tok_split = 1. `peers` (NULL on one GPU) makes the call column-parallel (the self-validating
  * lines described at muse_peer_sync_t): only the register-resident form, m <= MUSE_LL_TOKENS,
- * N % 8 == 0 and col0 % 8 == 0 (-8 otherwise). Serves the smallest of the m <= 32
+ * N % 8 == 0 and col0 % 8 == 0 (-8 otherwise). The register-resident form deals the rows that remain
+ * after the last full round of 8-row groups out row by row, so every CTA streams the same bytes to within
+ * one row; those short groups store 2-byte elements. whole_groups != 0 keeps whole 8-row groups instead
+ * (all stores 16-byte vectors when N % 8 == 0 and out is 16-byte aligned: for an `out` in page-locked host
+ * memory, where every store is a PCIe write). Serves the smallest of the m <= 32
  * calls that the reference gives to _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337,
  * :236-257). -5 = x does not fit in shared memory (muse_fewtok_smem_bytes > 227 KB). */
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream);
+                    int unroll, int tok_split, int whole_groups, int* status, const muse_peer_sync_t* peers, void* stream);
 long long muse_fewtok_smem_bytes(int m, int K, int warps);
 
 /* The same walk over an FP32 weight with FP32 output (the MoE router) for m = 1..8 * tok_split tokens:
@@ -170,54 +174,25 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
                    int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
                    int out_is_f32, const muse_peer_sync_t* peers, void* stream);
 
-/* The same product as muse_skinny_tc for tall weights at up to 64 tokens (ntok 16, 32 or 64), as a
- * persistent "stream-K" launch: `grid` CTAs (one per SM is the intended use) each take an equal,
- * contiguous share of all (tile, K chunk) units, so every SM streams the same number of weight
- * bytes and set-up is paid once per SM. Tiles shared by several CTAs are summed through workspace
- * slots in K order (bit-reproducible); the workspace (muse_streamk_ws_floats floats) needs no
- * zeroing, the counters (muse_skinny_tiles ints) must be zero before the first call and are left
- * zero. Same tensor maps, x, out, status and peers arguments as muse_skinny_tc. Replaces the same
- * reference code (best_submissions/muse_bf16_proj.py:215-287). */
-int muse_streamk_smem_bytes(int ntok, int hilo, int stages);
-int muse_streamk_max_contrib(int m, int n, int k, int ntok, int grid);
-long long muse_streamk_ws_floats(int m, int n, int k, int ntok, int grid);
-int muse_streamk_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt, int* status,
-                    int m, int n, int k, int ld_x, int ld_out, int ntok, int grid, int stages, int out_is_f32,
-                    const muse_peer_sync_t* peers, void* stream);
-
-/* muse_skinny_tc for callers that must not allocate device memory. No counterpart in the reference.
- *
- * Some hosts of this library cannot hand it a workspace: an inference server that gave every byte
- * of HBM to its own pool at start-up and forbids later cudaMalloc calls (they would fail, or
- * stall every stream while the driver maps memory); a plug-in slot whose contract is "inputs and
- * outputs only"; code running inside a latency-critical loop where an allocation is a
- * device-wide synchronisation. For them the split-K scratch (partial sums + tile counters) lives in
- * the library itself: a fixed array in device memory that exists on every GPU that loads the library,
- * from load until the process exits. Its capacity is muse_static_scratch_floats() floats
- * (1 Mi = 4 MiB) and muse_static_scratch_tiles() counters (4096): a launch needs
- * muse_skinny_ws_floats(m, n, ntok) floats and muse_skinny_tiles(m, n, ntok) counters, and a shape
- * that needs more is rejected with MUSE_ERR_STATIC_SCRATCH (-20) before anything is launched.
- * The caller still passes x, out and the status word; everything else is as for muse_skinny_tc.
- *
- * The first call on a device looks up the array's device address (once per device, with that device
- * current); make that first call outside any stream capture. The entry point itself never calls
- * cudaMalloc, cudaFree or any allocating library routine. All calls in the process share the one
- * array, and it keeps what the previous call left: when groups > 1 this entry point clears the part
- * it is about to accumulate into (two stream-ordered memsets) before the kernel; with groups == 1 the
- * array is not touched. Two calls that can overlap on the GPU (different streams, no ordering between
- * them) race on it: order them, or give one of them its own workspace through muse_skinny_tc. */
+/* muse_skinny_tc for callers that must not allocate device memory (a server whose pool owns all of
+ * HBM and bans cudaMalloc after start-up, a plug-in slot that passes inputs and outputs only). No
+ * counterpart in the reference. The split-K scratch is a fixed array inside the library, present on every
+ * GPU that loads it until the process exits: muse_static_scratch_floats() floats (1 Mi = 4 MiB) and
+ * muse_static_scratch_tiles() counters (4096). A launch with groups > 1 needs
+ * muse_skinny_ws_floats(m, n, ntok) floats and muse_skinny_tiles(m, n, ntok) counters; more than the
+ * array holds is refused with MUSE_ERR_STATIC_SCRATCH. groups == 1 uses no scratch and runs at any size.
+ * Every argument is checked before anything reaches the stream; the entry point calls no cudaMalloc,
+ * cudaFree or allocating library routine. The first call on a device looks up the array's address
+ * (once per device, that device current): make it outside a stream capture, and not concurrently with
+ * another first call. All calls share the array, which keeps the last call's contents: with groups > 1
+ * the part about to be used is cleared on the stream before the kernel. Calls that can overlap on the
+ * GPU race on it: order them, or give one its own workspace through muse_skinny_tc. */
 #define MUSE_ERR_STATIC_SCRATCH (-20)
 long long muse_static_scratch_floats(void);
 int muse_static_scratch_tiles(void);
 int muse_skinny_tc_noalloc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, int* status, int m, int n,
                            int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages, int out_is_f32,
                            void* stream);
-
-/* Diagnostics: while `device_buffer` is non-NULL every CTA of the following muse_skinny_tc launches
- * writes 16 unsigned 64-bit phase stamps (SM cycle counter; slot 15 = global nanosecond timer at
- * entry) at device_buffer[16 * linear CTA index]; the caller sizes it for the largest grid. NULL
- * (the default) turns stamping off. No counterpart in the reference. */
-void muse_skinny_set_trace(void* device_buffer);
 
 /* Launches an empty kernel on `stream`: the calibration point for the fixed cost of replaying a
  * one-kernel CUDA graph, which the benchmark reports beside every per-call time. Replaces the `nop`

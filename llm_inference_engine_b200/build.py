@@ -16,8 +16,11 @@ from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
-LIB_PATH = PKG_DIR / "libmuse_proj.so"
-SOURCES = ["gemv1.cu", "fewtok_mma.cu", "skinny_tc.cu", "streamk_tc.cu", "capi.cu"]
+# MUSE_TRACE=1 in the environment builds (and _capi loads) a separate diagnostic library whose kernels
+# stamp their phases; the ordinary library carries none of that code.
+TRACE = bool(os.environ.get("MUSE_TRACE"))
+LIB_PATH = PKG_DIR / ("libmuse_proj_trace.so" if TRACE else "libmuse_proj.so")
+SOURCES = ["gemv1.cu", "fewtok_mma.cu", "skinny_tc.cu", "capi.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -45,8 +48,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not _stale():
         return LIB_PATH
     nvcc = _nvcc()
-    compile_flags = [f for f in NVCC_FLAGS if f != "--shared"] + (["-Xptxas", "-v"] if verbose else [])
-    objs = [CSRC / (Path(s).stem + ".o") for s in SOURCES]
+    compile_flags = ([f for f in NVCC_FLAGS if f != "--shared"] + (["-Xptxas", "-v"] if verbose else [])
+                     + (["-DMUSE_TRACE"] if TRACE else []))
+    objs = [CSRC / (Path(s).stem + (".trace.o" if TRACE else ".o")) for s in SOURCES]
 
     def compile_one(src_obj):
         src, obj = src_obj

@@ -19,19 +19,17 @@ int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, co
                               int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                               int stages, int out_f32, cudaStream_t stream);
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                        int unroll, int tok_split, int* status, const PeerSync* peers, cudaStream_t stream);
+                        int unroll, int tok_split, int whole_groups, int* status, const PeerSync* peers,
+                        cudaStream_t stream);
 size_t fewtok_smem_bytes(int m, int K, int warps);
 int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                         int tok_split, int x_is_f32, cudaStream_t stream);
-int streamk_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
-                        int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int grid, int stages,
-                        int out_f32, const PeerSync* peers, cudaStream_t stream);
-int streamk_smem_bytes(int ntok, int hilo, int stages);
-int streamk_max_contrib(int m, int n, int k, int ntok, int grid);
-long long streamk_ws_floats(int m, int n, int k, int ntok, int grid);
+#ifdef MUSE_TRACE
+cudaError_t skinny_trace_set(unsigned long long* p);
+cudaError_t fewtok_trace_set(unsigned long long* p);
+#endif
 long long skinny_static_ws_floats();
 int skinny_static_cnt_ints();
-void skinny_set_trace(unsigned long long* device_buffer);
 
 // cuTensorMapEncodeTiled is a driver entry point; fetching it through the runtime keeps the
 // library free of a link-time dependency on libcuda (it must load on machines without a driver).
@@ -82,6 +80,16 @@ int muse_nop(void* stream) {
 }
 
 int muse_abi_version(void) { return MUSE_PROJ_ABI_VERSION; }
+
+#ifdef MUSE_TRACE
+// Diagnostic builds only (not part of the ABI in muse_proj.h): the device buffer that the kernels' phase
+// stamps go to, 16 unsigned 64-bit slots per CTA of the largest grid; NULL turns stamping off.
+int muse_trace_set(void* device_buffer) {
+  cudaError_t e = muse::skinny_trace_set(static_cast<unsigned long long*>(device_buffer));
+  if (e == cudaSuccess) e = muse::fewtok_trace_set(static_cast<unsigned long long*>(device_buffer));
+  return static_cast<int>(e);
+}
+#endif
 
 int muse_query(int what) {
   int dev = 0, v = 0;
@@ -138,8 +146,8 @@ int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, 
 }
 
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream) {
-  return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, status,
+                    int unroll, int tok_split, int whole_groups, int* status, const muse_peer_sync_t* peers, void* stream) {
+  return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, whole_groups, status,
                                    reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 
@@ -149,7 +157,7 @@ int muse_fewtok_mma_host(const void* W, const void* x_host, void* x_device, void
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemcpyAsync(x_device, x_host, static_cast<size_t>(m) * K * 2, cudaMemcpyHostToDevice, s);
   if (e != cudaSuccess) return static_cast<int>(e);
-  const int rc = muse::fewtok_mma_dispatch(W, x_device, out_device, m, N, K, K, N, warps, unroll, tok_split, status, nullptr, s);
+  const int rc = muse::fewtok_mma_dispatch(W, x_device, out_device, m, N, K, K, N, warps, unroll, tok_split, 0, status, nullptr, s);
   if (rc != 0) return rc;
   e = cudaMemcpyAsync(out_host, out_device, static_cast<size_t>(m) * N * 2, cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -186,10 +194,6 @@ long long muse_skinny_ws_floats(int m, int n, int ntok) {
 
 int muse_skinny_stage_bytes(int ntok, int hilo) { return muse::skinny_stage_bytes(ntok, hilo); }
 
-void muse_skinny_set_trace(void* device_buffer) {
-  muse::skinny_set_trace(static_cast<unsigned long long*>(device_buffer));
-}
-
 int muse_skinny_smem_bytes(int ntok, int hilo, int stages, int cluster, int m) {
   return muse::skinny_smem_bytes(ntok, hilo, stages, cluster, m);
 }
@@ -214,31 +218,6 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
   return muse::skinny_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
                                   cluster, groups, stages, out_is_f32, reinterpret_cast<const muse::PeerSync*>(peers),
                                   static_cast<cudaStream_t>(stream));
-}
-
-int muse_streamk_smem_bytes(int ntok, int hilo, int stages) { return muse::streamk_smem_bytes(ntok, hilo, stages); }
-int muse_streamk_max_contrib(int m, int n, int k, int ntok, int grid) {
-  return muse::streamk_max_contrib(m, n, k, ntok, grid);
-}
-long long muse_streamk_ws_floats(int m, int n, int k, int ntok, int grid) {
-  return muse::streamk_ws_floats(m, n, k, ntok, grid);
-}
-
-int muse_streamk_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt, int* status,
-                    int m, int n, int k, int ld_x, int ld_out, int ntok, int grid, int stages, int out_is_f32,
-                    const muse_peer_sync_t* peers, void* stream) {
-  if (!tmap_w || !x) return -1;
-  if (ld_x < k || ld_x % 8 != 0) return -2;
-  if (ntok != 16 && ntok != 32 && ntok != 64) return -7;
-  CUtensorMap tx;
-  const int r = muse::encode_2d(&tx, x, m, k, static_cast<long long>(ld_x) * 2, ntok);
-  if (r != 0) return r;
-  CUtensorMap tw, twlo;
-  memcpy(&tw, tmap_w, sizeof(tw));
-  if (tmap_w_lo) memcpy(&twlo, tmap_w_lo, sizeof(twlo));
-  return muse::streamk_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
-                                   grid, stages, out_is_f32, reinterpret_cast<const muse::PeerSync*>(peers),
-                                   static_cast<cudaStream_t>(stream));
 }
 
 long long muse_static_scratch_floats(void) { return muse::skinny_static_ws_floats(); }

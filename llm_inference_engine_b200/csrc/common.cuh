@@ -23,6 +23,19 @@ enum : int {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 500ull * 1000ull * 1000ull;  // 0.5 s
 
+// Phase stamps are a diagnostic of -DMUSE_TRACE builds only. There every translation unit carries a device
+// pointer (set through muse_trace_set, which only such builds export) to a buffer of 16 unsigned 64-bit
+// slots per CTA; in an ordinary build the base is a compile-time null and every stamp site folds away.
+#ifdef MUSE_TRACE
+static __device__ unsigned long long* g_trace_dev = nullptr;
+#define MUSE_TRACE_BASE() (g_trace_dev)
+#define MUSE_TRACE_SETTER(name) \
+  cudaError_t name(unsigned long long* p) { return cudaMemcpyToSymbol(g_trace_dev, &p, sizeof(p)); }
+#else
+#define MUSE_TRACE_BASE() (static_cast<unsigned long long*>(nullptr))
+#define MUSE_TRACE_SETTER(name)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

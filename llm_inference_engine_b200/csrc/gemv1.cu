@@ -96,14 +96,16 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
   if (nb > 0) load_batch<U>(w, wp, lane, nvec);
 
   __syncthreads();  // barrier initialised for everyone
-  if (!mbar_wait(smem_u32(&xbar), 0)) {
-    if (threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
-    return;
-  }
+  // A CTA-uniform verdict on the copy of x: on a time-out nobody multiplies (x is not there), but every
+  // thread still reaches the barriers below and the column-parallel book-keeping, so that the arrival
+  // count and the call number stay consistent for the next call.
+  const bool x_ok = __syncthreads_and(mbar_wait(smem_u32(&xbar), 0)) != 0;
+  if (!x_ok && threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
+  const int nb_run = x_ok ? nb : 0;
 
   const uint8_t* xseg = smem + static_cast<size_t>(seg) * ks * 2;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  for (int b = 0; b < nb; ++b) {
+  for (int b = 0; b < nb_run; ++b) {
     if (b + 1 < nb) load_batch<U>(wn, wp, (b + 1) * 32 * U + lane, nvec);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -142,7 +144,7 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
       for (int s = 1; s < WPR; ++s) acc += part[warp + s];
     }
   }
-  if (live && lane == 0 && seg == 0) store_row<F32W>(ps, out, row, acc);
+  if (x_ok && live && lane == 0 && seg == 0) store_row<F32W>(ps, out, row, acc);
   if (peer_active(ps)) gemv_peer_finish<F32W>(ps, s_epoch, N, status, &s_last);
 }
 
@@ -185,13 +187,13 @@ __global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict_
   uint4 w[U], wn[U];
   if (steps > 0) load_batch<U>(w, row_ptr(0), lane, nvec);
   __syncthreads();
-  if (!mbar_wait(smem_u32(&xbar), 0)) {
-    if (threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
-    return;
-  }
+  // CTA-uniform, and without an early return: see gemv1_kernel.
+  const bool x_ok = __syncthreads_and(mbar_wait(smem_u32(&xbar), 0)) != 0;
+  if (!x_ok && threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
+  const int steps_run = x_ok ? steps : 0;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   int r = 0, b = 0;
-  for (int s = 0; s < steps; ++s) {
+  for (int s = 0; s < steps_run; ++s) {
     int rn = r, bn = b + 1;
     if (bn == nb) { bn = 0; ++rn; }
     if (s + 1 < steps) load_batch<U>(wn, row_ptr(rn), bn * 32 * U + lane, nvec);

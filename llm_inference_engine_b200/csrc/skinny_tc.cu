@@ -132,9 +132,10 @@ __global__ void __launch_bounds__(128)
 skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wlo,
                  const __grid_constant__ CUtensorMap tm_x, void* __restrict__ out, float* __restrict__ ws,
                  int* __restrict__ cnt, int* __restrict__ status, int m, int n, int chunks, int split, int stages,
-                 int out_f32, int ld_out, unsigned long long* __restrict__ trace, const __grid_constant__ PeerSync ps) {
+                 int out_f32, int ld_out, const __grid_constant__ PeerSync ps) {
   using Cfg = SkinnyCfg<NTOK, HILO>;
-  // Optional per-CTA phase stamps (SM cycle counter; slot 15 / 11 = global nanosecond timer at entry / exit).
+  // Per-CTA phase stamps of diagnostic builds (SM cycle counter; slot 15 / 11 = global nanosecond timer at entry / exit).
+  unsigned long long* const trace = MUSE_TRACE_BASE();
   unsigned long long* const tr =
       trace ? trace + 16ull * (blockIdx.x + gridDim.x * (blockIdx.y + static_cast<size_t>(gridDim.y) * blockIdx.z)) : nullptr;
 #define MUSE_STAMP(slot) do { if (tr) tr[slot] = static_cast<unsigned long long>(clock64()); } while (0)
@@ -493,9 +494,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
 // ---------------------------------------------------------------- host side
 
-static unsigned long long* g_trace = nullptr;  // device buffer the next launches stamp into (diagnostics)
-void skinny_set_trace(unsigned long long* device_buffer) { g_trace = device_buffer; }
-unsigned long long* skinny_get_trace() { return g_trace; }
+MUSE_TRACE_SETTER(skinny_trace_set)
 
 int skinny_stage_bytes(int ntok, int hilo) { return TILE_ROWS * BK * 2 * (hilo ? 2 : 1) + ntok * BK * 2; }
 
@@ -579,7 +578,7 @@ static cudaError_t launch_with(const CUtensorMap* tw, const CUtensorMap* twlo, c
   cudaLaunchAttribute attr[1];
   fill_config<NTOK, HILO>(&cfg, attr, m, n, cluster, groups, smem, stream);
   return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<NTOK, HILO, PEERS>, *tw, HILO ? *twlo : *tw, *tx, out, ws, cnt, status, m, n,
-                            chunks, cluster * groups, stages, out_f32, ld_out, g_trace, ps);
+                            chunks, cluster * groups, stages, out_f32, ld_out, ps);
 }
 
 // How many clusters of this shape the device can hold at once (0 = the shape cannot launch).
@@ -621,6 +620,24 @@ int skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster) {
   return -7;
 }
 
+// Everything skinny_tc_dispatch rejects that can be decided without touching the device: returns 0 or the
+// negative code. `ps` = the peer descriptor already copied (world <= 1: single GPU).
+static int skinny_check_args(const CUtensorMap* tw, const CUtensorMap* tx, const void* out, const float* ws, const int* cnt,
+                             const int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
+                             int stages, const PeerSync& ps) {
+  if (!tw || !tx || !out || !status || m <= 0 || n <= 0 || k <= 0) return -1;
+  if (k % 8 != 0) return -2;
+  const int chunks = (k + BK - 1) / BK;
+  if (cluster < 1 || cluster > MAX_CLUSTER || groups < 1) return -3;
+  const long long split = static_cast<long long>(cluster) * groups;
+  if (split > chunks || split > 65535 || chunks > 65535) return -3;
+  if (groups > 1 && (!ws || !cnt)) return -4;
+  if (stages < 1 || stages > MAX_STAGES) return -5;
+  if (ld_out < n + ps.col0) return -6;
+  if (ntok != 16 && ntok != 32 && ntok != 64 && ntok != 128 && ntok != 256) return -7;
+  return 0;
+}
+
 // Negative = argument error, positive = cudaError_t, 0 = launched.
 int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
                        int* cnt, int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
@@ -633,15 +650,9 @@ int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUt
       if (!ps.out[p] || !ps.flags[p]) return -8;
     out = ps.out[ps.rank];
   }
-  if (!tw || !tx || !out || !status || m <= 0 || n <= 0 || k <= 0) return -1;
-  if (k % 8 != 0) return -2;
+  const int bad = skinny_check_args(tw, tx, out, ws, cnt, status, m, n, k, ld_out, ntok, cluster, groups, stages, ps);
+  if (bad) return bad;
   const int chunks = (k + BK - 1) / BK;
-  if (cluster < 1 || cluster > MAX_CLUSTER || groups < 1) return -3;
-  const long long split = static_cast<long long>(cluster) * groups;
-  if (split > chunks || split > 65535 || chunks > 65535) return -3;
-  if (groups > 1 && (!ws || !cnt)) return -4;
-  if (stages < 1 || stages > MAX_STAGES) return -5;
-  if (ld_out < n + ps.col0) return -6;
   const bool hilo = twlo != nullptr;
 #define L_T(NT) static_cast<int>(launch<NT, true>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups, stages, out_f32, ld_out, ps, stream))
 #define L_F(NT) static_cast<int>(launch<NT, false>(tw, twlo, tx, out, ws, cnt, status, m, n, chunks, cluster, groups, stages, out_f32, ld_out, ps, stream))
@@ -664,38 +675,48 @@ long long skinny_static_ws_floats() { return STATIC_WS_FLOATS; }
 int skinny_static_cnt_ints() { return STATIC_CNT_INTS; }
 
 // In host code `g_static_scratch` is only a handle for the symbol, not an address a kernel can use.
-// The device address is looked up once per device, with that device current, and cached.
+// The device address is looked up once per device, with that device current, and cached. Two threads
+// making the first call on a device at the same time both look it up and store the same value.
 static cudaError_t static_scratch_address(unsigned char** out) {
-  static unsigned char* addr[64] = {nullptr};
+  static unsigned char* volatile addr[64] = {nullptr};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!addr[dev]) {
+  unsigned char* a = addr[dev];
+  if (!a) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_static_scratch);
     if (e != cudaSuccess) return e;
-    addr[dev] = static_cast<unsigned char*>(p);
+    addr[dev] = a = static_cast<unsigned char*>(p);
   }
-  *out = addr[dev];
+  *out = a;
   return cudaSuccess;
 }
 
 // Same launch as skinny_tc_dispatch with the workspace and counters taken from g_static_scratch.
-// -20: the shape needs more scratch than the library carries. Calls nothing that allocates.
+// -20: the shape needs more scratch than the library carries (only launches with groups > 1 use any).
+// Every argument is validated before anything is put on the stream. Calls nothing that allocates.
 int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out,
                               int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                               int stages, int out_f32, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || ntok <= 0) return -1;
   const long long tiles = static_cast<long long>((n + TILE_ROWS - 1) / TILE_ROWS) * ((m + ntok - 1) / ntok);
   const long long floats = tiles * TILE_ROWS * ntok;
-  if (floats > STATIC_WS_FLOATS || tiles > STATIC_CNT_INTS) return -20;
+  if (groups > 1 && (floats > STATIC_WS_FLOATS || tiles > STATIC_CNT_INTS)) return -20;
   unsigned char* base = nullptr;
   cudaError_t e = static_scratch_address(&base);
   if (e != cudaSuccess) return static_cast<int>(e);
   float* ws = reinterpret_cast<float*>(base);
   int* cnt = reinterpret_cast<int*>(base + STATIC_WS_FLOATS * 4);
+  const int bad = skinny_check_args(tw, tx, out, ws, cnt, status, m, n, k, ld_out, ntok, cluster, groups, stages, PeerSync{});
+  if (bad) return bad;
   if (groups > 1) {
+    // The shared-memory fit is the one check left to the launch itself; decide it before the clears too.
+    int dev = 0, room = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaDeviceGetAttribute(&room, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return static_cast<int>(e);
+    if (skinny_smem_bytes(ntok, twlo != nullptr, stages, cluster, m) + 512 > room) return static_cast<int>(cudaErrorInvalidValue);
     // The array keeps whatever the previous call (of anyone in this process) left. A completed call
     // leaves zeros, an aborted one may not: clear exactly what this launch will accumulate into.
     if ((e = cudaMemsetAsync(ws, 0, static_cast<size_t>(floats) * 4, stream)) != cudaSuccess) return static_cast<int>(e);

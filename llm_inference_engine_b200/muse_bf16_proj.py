@@ -7,11 +7,16 @@
 `{"x": BF16 [m, K], "config": {"m", "n", "k", "layer"}}`; the result is a new [m, n] tensor. `n` may be
 smaller than W's row count (the unpooler's per-GPU slice at up to 8 tokens, bf16_proj/reference.py:37-41).
 
-Dispatch (shape-only, so a call is CUDA-graph capturable and replays identically):
-  m == 1   streaming GEMV (csrc/gemv1.cu); the router reads its FP32 weights as they are
-  m >= 2   swap-AB split-K TMA + tcgen05 kernel (csrc/skinny_tc.cu), K slices reduced inside thread-block
-           clusters through distributed shared memory; the router runs its BF16 hi + lo pair (split
-           once here, as the reference does at :346-349) into one FP32 accumulator
+Dispatch (shape-only: plan.py; a call is CUDA-graph capturable and replays identically):
+  m == 1          streaming GEMV (csrc/gemv1.cu); the router reads its FP32 weights as they are
+                  (the tall qkv_gate weight takes the register-MMA walk at m = 1 too)
+  few tokens      persistent register-MMA walk over the weight (csrc/fewtok_mma.cu): up to 16 tokens on
+                  the big weights, up to 64 on the small ones, up to 32 for the FP32 router (hi + lo
+                  split in registers)
+  everything else swap-AB split-K TMA + tcgen05 kernel (csrc/skinny_tc.cu), K slices reduced inside
+                  thread-block clusters through distributed shared memory; the router runs its BF16
+                  hi + lo pair (split once here, as the reference does at :346-349) into one FP32
+                  accumulator
 Every path is hand-written sm_100a CUDA reached through the C ABI (include/muse_proj.h); there is no
 cuBLAS, Triton, PyTorch-matmul or CPU fallback: a non-CUDA tensor or a missing library raises.
 """
@@ -241,8 +246,10 @@ def _kernel_fn_f32_input(x: torch.Tensor, n: int, layer: str, state, out, peers)
 
 
 def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: int, out_ptr: int, ld_out: int, peers,
-            stream: int, device) -> None:
-    """One C-ABI call: the kernel `plan` names, on validated arguments."""
+            stream: int, device, out_on_host: bool = False) -> None:
+    """One C-ABI call: the kernel `plan` names, on validated arguments. `out_on_host`: the destination is
+    page-locked host memory, where every store is a PCIe write (the register-MMA walk then keeps whole
+    8-row groups so that all of its stores are 16-byte vectors)."""
     lib = _capi.load()
     f32 = layer in FP32_LAYERS
     w = state[layer]
@@ -253,7 +260,7 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
         return
     if isinstance(plan, FewTokPlan):
         _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x_ptr, out_ptr, m, n, k, ld_x, ld_out, plan.warps, plan.unroll,
-                                        plan.tok_split, status, _peer_ptr(peers), stream),
+                                        plan.tok_split, int(out_on_host), status, _peer_ptr(peers), stream),
                     f"muse_fewtok_mma({layer}, m={m}, n={n}, k={k}, {plan})")
         return
     if isinstance(plan, GemvPlan):
@@ -340,7 +347,7 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record:
             else:
                 x_dev.copy_(x, non_blocking=True)
             _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out.data_ptr() if direct else out_dev.data_ptr(), n, None,
-                    rec, w.device)
+                    rec, w.device, out_on_host=direct)
             if not direct and STORE_OUT_BY_KERNEL and out.data_ptr() % 16 == 0 and (out.numel() * out.element_size()) % 16 == 0:
                 _capi.check(lib.muse_fetch_host(out.data_ptr(), out_dev.data_ptr(), out.numel() * out.element_size(), rec),
                             "muse_fetch_host (copy-out)")

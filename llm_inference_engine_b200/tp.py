@@ -165,16 +165,23 @@ class FusedColumnParallel(ColumnParallelProjection):
         local = {"x": data["x"], "config": self.local_config(data["config"])}
         return self._kernel_fn(local, state, out=out, peers=self._peers[layer])
 
+    HOST_GRAPH_SLOTS = 64   # recorded round trips kept (oldest dropped first)
+
     def kernel_fn_host(self, data: dict, state, out: torch.Tensor) -> torch.Tensor:
         """kernel_fn for activations in page-locked HOST memory: x [m, K] BF16 comes in through a small
         fetch kernel, the column-parallel kernel runs (exchange included), and the gathered [m, N] is
         copied into `out` (page-locked, contiguous) by the same small kernel; the three launches are
-        recorded once per (layer, m, x, out) as a CUDA graph, replayed and synchronised on every call.
-        Every rank must make the same calls in the same order, as for kernel_fn."""
+        recorded once per (state, layer, m, x, out) as a CUDA graph, replayed and synchronised on every call.
+
+        Every rank must make the same calls in the same order, as for kernel_fn. A call runs exactly one
+        exchange whether it finds its recording or not: the first call of a buffer pair runs the three
+        launches in the open and then records them WITHOUT replaying, so a rank that alone lost its
+        entry (say it re-pinned a buffer) stays in step with its peers. Time-outs of the exchange are
+        reported through muse_bf16_proj.check_status(state), which the caller polls outside the hot loop."""
         x = data["x"]
         layer = data["config"]["layer"]
         m, k = x.shape
-        key = (layer, m, x.data_ptr(), out.data_ptr())
+        key = (id(state), layer, m, int(data["config"]["n"]), x.data_ptr(), out.data_ptr())
         entry = self._host_graphs.get(key)
         if entry is None:
             n = self.rows[layer]
@@ -194,12 +201,16 @@ class FusedColumnParallel(ColumnParallelProjection):
                                  "muse_fetch_host (copy-out)")
 
             cur = torch.cuda.current_stream(device)
-            body(cur.cuda_stream)          # once in the open: every lazily created resource exists before the recording
+            body(cur.cuda_stream)          # this call's result; every lazily created resource exists afterwards
             cur.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph):  # recorded for the next calls, not run now
                 body(torch.cuda.current_stream(device).cuda_stream)
-            entry = self._host_graphs[key] = (graph, x, out, x_dev, device)
+            if len(self._host_graphs) >= self.HOST_GRAPH_SLOTS:
+                self._host_graphs.pop(next(iter(self._host_graphs)))
+            # the state and the tensors stay alive as long as their addresses are baked in
+            self._host_graphs[key] = (graph, x, out, x_dev, device, state)
+            return out
         entry[0].replay()
         torch.cuda.current_stream(entry[4]).synchronize()
         return out

@@ -1,16 +1,7 @@
-"""The allocation-free entry point, muse_skinny_tc_noalloc, against the ordinary muse_skinny_tc.
-
-Who needs it: a host that has no device memory to give (a server whose pool owns all of HBM and
-bans cudaMalloc after start-up, a plug-in slot that passes inputs and outputs only, a loop where an
-allocation would stall every stream). Such a caller hands over x, out and the status word; the
-split-K scratch is a fixed array inside the library. This file checks, through the C ABI only, that
-the result equals the ordinary entry point's (which is given a caller-owned workspace) on two calls
-in a row -- the second call finds the shared array as the first one left it -- and that a shape
-beyond the array's stated capacity is refused before anything is launched.
-
-Kept in a file that sorts last so that a run stopping at the first failure has already run every
-other test; it also passes alone in a fresh process (nothing here depends on earlier tests).
-"""
+"""muse_skinny_tc_noalloc (split-K scratch inside the library, for hosts that may not allocate device
+memory) against muse_skinny_tc with a caller-owned workspace, through the C ABI: equal results on two
+calls in a row, refusal beyond the stated capacity. Sorts last so that a run that stops at the first
+failure has run every other test; passes alone in a fresh process too."""
 
 from __future__ import annotations
 
@@ -102,3 +93,14 @@ def test_noalloc_refuses_shapes_beyond_its_scratch():
     assert rc == -20                                 # MUSE_ERR_STATIC_SCRATCH: nothing was launched
     torch.cuda.synchronize(dev)
     assert float(out.abs().max()) == 0.0
+    # a rejected argument (13 stages) is refused before the clears of the shared array are enqueued
+    rc = lib.muse_skinny_tc_noalloc(maps[0].ptr, None, x.data_ptr(), out.data_ptr(), status.data_ptr(), 8, 1024, k, k, n,
+                                    16, 1, 2, 13, 0, torch.cuda.current_stream(dev).cuda_stream)
+    assert rc == -5
+    # with one cluster per tile the scratch is not used, so the same large shape runs
+    rc = lib.muse_skinny_tc_noalloc(maps[0].ptr, None, x.data_ptr(), out.data_ptr(), status.data_ptr(), m, n, k, k, n,
+                                    ntok, 1, 1, 3, 0, torch.cuda.current_stream(dev).cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize(dev)
+    exact = x.double() @ keep[0].double().T
+    assert float((out.double() - exact).norm() / exact.norm()) < 5e-3 and int(status.item()) == 0
