@@ -301,7 +301,7 @@ def copies_for(layer: str, world: int) -> int:
 
 def kernel_family(h: Harness, state, layer: str, m: int, n_local: int, k: int) -> str:
     """Which of the library's kernels the planner gives this call (the name the ncu summaries use)."""
-    from llm_inference_engine_b200.plan import FewTokPlan, GemvPlan
+    from llm_inference_engine_b200.plan import FewTokPlan, GemmPlan, GemvPlan
 
     plan = h.proj.plan_for(state, layer, m, n_local, k, fused=h.world > 1 and h.fused is not None)
     if isinstance(plan, GemvPlan):
@@ -311,7 +311,7 @@ def kernel_family(h: Harness, state, layer: str, m: int, n_local: int, k: int) -
     if isinstance(plan, FewTokPlan):
         name = "fewtok_xreg" if plan.warps * plan.unroll * 32 >= k else "fewtok_mma"
         return f"{name}<{plan.warps},{plan.unroll},{'true' if m > 8 * plan.tok_split else 'false'}>"
-    return "skinny_tc"
+    return "gemm_tc" if isinstance(plan, GemmPlan) else "skinny_tc"
 
 
 def case_table(h: Harness, layers, steps: int, warmup: int, peak: float, only=None) -> list[dict]:

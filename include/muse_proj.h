@@ -92,15 +92,11 @@ int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f
  * block of 8 or 16 tokens, and W is read from HBM once and a second time from L2. Otherwise
  * tok_split = 1. `peers` (NULL on one GPU) makes the call column-parallel (the self-validating
  * lines described at muse_peer_sync_t): only the register-resident form, m <= MUSE_LL_TOKENS,
- * N % 8 == 0 and col0 % 8 == 0 (-8 otherwise). The register-resident form deals the rows that remain
- * after the last full round of 8-row groups out row by row, so every CTA streams the same bytes to within
- * one row; those short groups store 2-byte elements. whole_groups != 0 keeps whole 8-row groups instead
- * (all stores 16-byte vectors when N % 8 == 0 and out is 16-byte aligned: for an `out` in page-locked host
- * memory, where every store is a PCIe write). Serves the smallest of the m <= 32
+ * N % 8 == 0 and col0 % 8 == 0 (-8 otherwise). Serves the smallest of the m <= 32
  * calls that the reference gives to _swab / _swab_kernel (best_submissions/muse_bf16_proj.py:323-337,
  * :236-257). -5 = x does not fit in shared memory (muse_fewtok_smem_bytes > 227 KB). */
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int tok_split, int whole_groups, int* status, const muse_peer_sync_t* peers, void* stream);
+                    int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream);
 long long muse_fewtok_smem_bytes(int m, int K, int warps);
 
 /* The same walk over an FP32 weight with FP32 output (the MoE router) for m = 1..8 * tok_split tokens:
@@ -173,6 +169,36 @@ int muse_skinny_max_clusters(int ntok, int hilo, int m, int stages, int cluster)
 int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, void* out, float* ws, int* cnt,
                    int* status, int m, int n, int k, int ld_x, int ld_out, int ntok, int cluster, int groups, int stages,
                    int out_is_f32, const muse_peer_sync_t* peers, void* stream);
+
+/* out[m, n] = x[m, K] . W[n, K]^T, BF16 out, for many tokens (the m > 32 GEMM): TMA + tcgen05 as in
+ * muse_skinny_tc, but a CTA multiplies a PAIR of 128-row weight tiles (pair != 0) against one copy of the
+ * x chunk (two accumulators in tensor memory), which halves the L2 -> shared-memory traffic that bounds
+ * these shapes; pair == 0 keeps one tile per CTA (small weights: more CTAs).
+ *   tmap_w   tensor map of W[:n] with box_rows = 128 (muse_tmap_encode_2d)
+ *   x, out   as for muse_skinny_tc; out is BF16
+ *   ntok     tokens per tile = MMA N: any multiple of 16 up to 256 (m > ntok runs ceil(m / ntok) token tiles)
+ *   cluster  K slices as the CTAs of one thread-block cluster (1 .. 16), summed through distributed shared
+ *            memory; no workspace
+ *   split    K slices as independent CTAs (1 .. 64) that exchange their partial sums through `ws` (plain
+ *            16-byte stores and loads that stay in L2, no atomics) and count themselves in and out on `cnt`;
+ *            they wait for one another, so the whole grid must be resident at once: row units x split x token
+ *            tiles <= SM count (-10 otherwise). One of cluster, split must be 1; cluster * split <= ceil(K / 64).
+ *            Either way the sum has a fixed order: bit-reproducible.
+ *   ws, cnt  for split > 1: muse_gemm_tc_ws_floats floats (16-byte aligned, contents irrelevant) and
+ *            muse_gemm_tc_cnt_ints counters, zero before the first call and left zero; else may be NULL
+ *   stages   pipeline depth 1 .. 8
+ *   warpgroups  1 .. 4: CTA size in units of 128 threads; all of them read the accumulators out, push and store
+ * One CTA per SM (the launch asks for at least 116 KB of shared memory). muse_gemm_tc_smem_bytes = the
+ * dynamic shared memory of a launch; muse_gemm_tc_max_clusters = how many of its clusters the current
+ * device holds at once (0: does not fit). Replaces the cuBLAS call x @ W[:n].T of
+ * best_submissions/muse_bf16_proj.py:390. */
+int muse_gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
+int muse_gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
+long long muse_gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split);
+int muse_gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split);
+int muse_gemm_tc(const void* tmap_w, const void* x, void* out, float* ws, int* cnt, int* status, int m, int n, int k, int ld_x,
+                 int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
+                 const muse_peer_sync_t* peers, void* stream);
 
 /* muse_skinny_tc for callers that must not allocate device memory (a server whose pool owns all of
  * HBM and bans cudaMalloc after start-up, a plug-in slot that passes inputs and outputs only). No

@@ -19,14 +19,21 @@ int skinny_tc_static_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, co
                               int* status, int m, int n, int k, int ld_out, int ntok, int cluster, int groups,
                               int stages, int out_f32, cudaStream_t stream);
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                        int unroll, int tok_split, int whole_groups, int* status, const PeerSync* peers,
-                        cudaStream_t stream);
+                        int unroll, int tok_split, int* status, const PeerSync* peers, cudaStream_t stream);
 size_t fewtok_smem_bytes(int m, int K, int warps);
 int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                         int tok_split, int x_is_f32, cudaStream_t stream);
+int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m, int n,
+                     int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
+                     const PeerSync* peers, cudaStream_t stream);
+long long gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split);
+int gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split);
+int gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
+int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
 #ifdef MUSE_TRACE
 cudaError_t skinny_trace_set(unsigned long long* p);
 cudaError_t fewtok_trace_set(unsigned long long* p);
+cudaError_t gemm_trace_set(unsigned long long* p);
 #endif
 long long skinny_static_ws_floats();
 int skinny_static_cnt_ints();
@@ -87,6 +94,7 @@ int muse_abi_version(void) { return MUSE_PROJ_ABI_VERSION; }
 int muse_trace_set(void* device_buffer) {
   cudaError_t e = muse::skinny_trace_set(static_cast<unsigned long long*>(device_buffer));
   if (e == cudaSuccess) e = muse::fewtok_trace_set(static_cast<unsigned long long*>(device_buffer));
+  if (e == cudaSuccess) e = muse::gemm_trace_set(static_cast<unsigned long long*>(device_buffer));
   return static_cast<int>(e);
 }
 #endif
@@ -146,8 +154,8 @@ int muse_copy_d2h_sync(void* dst_host, const void* src_device, long long bytes, 
 }
 
 int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                    int unroll, int tok_split, int whole_groups, int* status, const muse_peer_sync_t* peers, void* stream) {
-  return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, whole_groups, status,
+                    int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream) {
+  return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, status,
                                    reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 
@@ -157,7 +165,7 @@ int muse_fewtok_mma_host(const void* W, const void* x_host, void* x_device, void
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemcpyAsync(x_device, x_host, static_cast<size_t>(m) * K * 2, cudaMemcpyHostToDevice, s);
   if (e != cudaSuccess) return static_cast<int>(e);
-  const int rc = muse::fewtok_mma_dispatch(W, x_device, out_device, m, N, K, K, N, warps, unroll, tok_split, 0, status, nullptr, s);
+  const int rc = muse::fewtok_mma_dispatch(W, x_device, out_device, m, N, K, K, N, warps, unroll, tok_split, status, nullptr, s);
   if (rc != 0) return rc;
   e = cudaMemcpyAsync(out_host, out_device, static_cast<size_t>(m) * N * 2, cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -218,6 +226,39 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
   return muse::skinny_tc_dispatch(&tw, tmap_w_lo ? &twlo : nullptr, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok,
                                   cluster, groups, stages, out_is_f32, reinterpret_cast<const muse::PeerSync*>(peers),
                                   static_cast<cudaStream_t>(stream));
+}
+
+int muse_gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups) {
+  if (ntok < 16 || ntok > 256 || ntok % 16 || stages < 1 || cluster < 1 || m < 1 || warpgroups < 1 || warpgroups > 4) return -1;
+  return muse::gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, warpgroups);
+}
+
+int muse_gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups) {
+  return muse::gemm_tc_max_clusters(ntok, pair, stages, cluster, m, warpgroups);
+}
+
+long long muse_gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split) {
+  if (m < 1 || n < 1 || ntok < 16 || ntok > 256 || ntok % 16 || split < 1) return -1;
+  return muse::gemm_tc_ws_floats(m, n, ntok, pair, split);
+}
+int muse_gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split) {
+  if (m < 1 || n < 1 || ntok < 16 || ntok > 256 || ntok % 16 || split < 1) return -1;
+  return muse::gemm_tc_cnt_ints(m, n, ntok, pair, split);
+}
+
+int muse_gemm_tc(const void* tmap_w, const void* x, void* out, float* ws, int* cnt, int* status, int m, int n, int k, int ld_x,
+                 int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
+                 const muse_peer_sync_t* peers, void* stream) {
+  if (!tmap_w || !x) return -1;
+  if (ld_x < k || ld_x % 8 != 0) return -2;
+  if (ntok < 16 || ntok > 256 || ntok % 16) return -7;
+  CUtensorMap tx;   // x moves between calls: its map is encoded per call and rides in the kernel parameters
+  const int r = muse::encode_2d(&tx, x, m, k, static_cast<long long>(ld_x) * 2, ntok);
+  if (r != 0) return r;
+  CUtensorMap tw;
+  memcpy(&tw, tmap_w, sizeof(tw));
+  return muse::gemm_tc_dispatch(&tw, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok, pair, cluster, split, stages, warpgroups,
+                                reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 
 long long muse_static_scratch_floats(void) { return muse::skinny_static_ws_floats(); }

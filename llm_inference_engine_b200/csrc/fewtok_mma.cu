@@ -36,55 +36,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 MUSE_TRACE_SETTER(fewtok_trace_set)
 
 constexpr int FEWTOK_X_PAD = 64;   // bytes added to each x row in shared memory
-
-// Which rows CTA c of a walk of C CTAs takes, group by group. Rounds in which every CTA has a whole 8-row
-// group go round robin (group c + i C), so that at any moment the grid reads one contiguous stretch of W.
-// What is left after the last such round (fewer than 8 C rows) is dealt out row by row, base or base + 1
-// rows to each CTA as one short group, so that every CTA streams the same number of bytes to within one
-// row. `whole` keeps the remainder in whole groups instead (some CTAs then run one more group than the
-// others): for stores that must all be aligned 16-byte vectors and for the column-parallel lines.
-struct RowWalk {
-  int step8, row8, full, my_groups;   // rows between a CTA's groups, its first row, its whole groups, all its groups
-  __device__ RowWalk(int N, int C, int c, bool whole) : step8(C * 8), row8(c * 8) {
-    int row0, nrows;
-    last(N, C, c, whole, row0, nrows);
-    if (whole) {
-      const int groups = (N + 7) >> 3;
-      my_groups = c < groups ? (groups - c + C - 1) / C : 0;
-      full = my_groups - (nrows > 0 ? 1 : 0);
-    } else {
-      full = N / step8;
-      my_groups = full + (nrows > 0 ? 1 : 0);
-    }
-  }
-  // The short group of CTA c (nrows = 0: it has none). Recomputed from the launch parameters where it is
-  // needed (twice per CTA) rather than kept in registers across the walk.
-  static __device__ __forceinline__ void last(int N, int C, int c, bool whole, int& row0, int& nrows) {
-    if (whole) {   // the one group that can be short is the weight's last, when N is not a multiple of 8
-      const int groups = (N + 7) >> 3;
-      nrows = ((N & 7) != 0 && c == (groups - 1) % C) ? (N & 7) : 0;
-      row0 = (groups - 1) * 8;
-    } else {
-      const int full_rows = N / (C * 8) * (C * 8);
-      const int rem = N - full_rows, base = rem / C, extra = rem - base * C;
-      nrows = base + (c < extra ? 1 : 0);
-      row0 = full_rows + c * base + (c < extra ? c : extra);
-    }
-  }
-};
-// Group i of a walk: whole groups by counting, the short one looked up again. The empty volatile asm keeps
-// the compiler from hoisting that look-up (and its registers) out of the caller's loop.
-#define MUSE_WALK_GROUP(walk, i, N, C, c, whole, row0, nrows)          \
-  do {                                                                 \
-    if ((i) < (walk).full) {                                           \
-      row0 = (walk).row8 + (i) * (walk).step8;                         \
-      nrows = 8;                                                       \
-    } else {                                                           \
-      int n_opaque = (N);                                              \
-      asm volatile("" : "+r"(n_opaque));                               \
-      RowWalk::last(n_opaque, (C), (c), (whole), row0, nrows);         \
-    }                                                                  \
-  } while (0)
 static inline bool peer_active_host(const PeerSync& ps) { return ps.world > 1; }
 
 // HI = tokens 8..15 exist (second half of the A fragment); otherwise those MMA rows are fed zeros.
@@ -205,8 +156,7 @@ template <int NW, int U, bool HI, bool PEERS, bool VEC>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ x,
                                                               __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
-                                                              int ld_out, int tok_split, int whole_groups,
-                                                              int* __restrict__ status,
+                                                              int ld_out, int tok_split, int* __restrict__ status,
                                                               const __grid_constant__ PeerSync ps) {
   unsigned long long* const trace = MUSE_TRACE_BASE();
   // Diagnostic builds, the exchange (PEERS only): per CTA 16 slots of the global nanosecond timer, 0 entry,
@@ -233,18 +183,15 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
     if (!PEERS && m <= 0) return;
   }
   const int kblocks = K >> 5;
-  const bool whole = whole_groups != 0 || PEERS;
-  const RowWalk walk(N, C, c, whole);
-  const int my_groups = m > 0 ? walk.my_groups : 0;
+  const int groups = (N + 7) >> 3;
+  const int my_groups = (c < groups && m > 0) ? (groups - c + C - 1) / C : 0;
   const int first = warp * U;                    // this warp's 64-byte pieces of every row: first .. first + U - 1
   auto load = [&](uint4 (&w)[U], int i) {
-    int row0, nrows;
-    MUSE_WALK_GROUP(walk, i, N, C, c, whole, row0, nrows);
-    const bool live = g < nrows;                 // rows a short group does not have issue no loads
-    const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row0 + (live ? g : 0)) * K) + q;
+    int row = (c + i * C) * 8 + g;
+    row = row < N ? row : N - 1;
+    const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K) + q;
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-      w[u] = live && first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    for (int u = 0; u < U; ++u) w[u] = first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
   };
   // One register buffer: a group's loads are re-issued into it as soon as its MMAs have read it, and stay
   // in flight across the reduction below. (A second buffer costs 16 registers the 32-warp CTA does not have.)
@@ -302,24 +249,17 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
 #pragma unroll 8
       for (int wv = 0; wv < NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
       const int t = threadIdx.x >> 3, r = threadIdx.x & 7;
-      int row0, nrows;
-      MUSE_WALK_GROUP(walk, i, N, C, c, whole, row0, nrows);
-      const int grp = row0 >> 3;
+      const int grp = c + i * C, row0 = grp * 8;
       if constexpr (!PEERS && VEC) {
         // 8 rows of a token = 8 neighbouring lanes: one 16-byte store per token and group instead of eight
         // 2-byte ones (what makes an output in page-locked host memory affordable: one PCIe write each).
-        // A short group (the last one of a balanced walk) starts at any row and stores its rows one by one.
         const uint32_t v = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sum)));
         const uint32_t p01 = v | (__shfl_down_sync(0xffffffffu, v, 1) << 16);
         const uint32_t p23 = __shfl_down_sync(0xffffffffu, p01, 2);
         const uint32_t p45 = __shfl_down_sync(0xffffffffu, p01, 4), p67 = __shfl_down_sync(0xffffffffu, p23, 4);
-        if (nrows == 8 && (row0 & 7) == 0) {
-          if (r == 0 && t < m) *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ld_out + row0) = make_uint4(p01, p23, p45, p67);
-        } else if (t < m && r < nrows) {
-          out[static_cast<size_t>(t) * ld_out + row0 + r] = __float2bfloat16_rn(sum);
-        }
+        if (r == 0 && t < m) *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ld_out + row0) = make_uint4(p01, p23, p45, p67);
       } else if constexpr (!PEERS) {
-        if (t < m && r < nrows) out[static_cast<size_t>(t) * ld_out + row0 + r] = __float2bfloat16_rn(sum);
+        if (t < m && row0 + r < N) out[static_cast<size_t>(t) * ld_out + row0 + r] = __float2bfloat16_rn(sum);
       } else {
         // The 8 rows of a token sit in 8 neighbouring lanes: gather them into one 16-byte vector (N % 8 == 0 here).
         const uint32_t v = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sum)));
@@ -386,19 +326,18 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
   m = m - t0 < TOKS ? m - t0 : TOKS;
   if (m <= 0) return;
   const int kblocks = K >> 5;
-  const RowWalk walk(N, C, c, false);
-  const int my_groups = walk.my_groups;
+  const int groups = (N + 7) >> 3;
+  const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
   const int first = warp * U;
   uint4 w[2 * PS], xr[U], xl[XF32 ? U : 1];
   auto load = [&](int i, int h) {
-    int row0, nrows;
-    MUSE_WALK_GROUP(walk, i, N, C, c, false, row0, nrows);
-    const bool live = g < nrows;
-    const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row0 + (live ? g : 0)) * K) + 2 * q;   // 8 FP32 = two vectors
+    int row = (c + i * C) * 8 + g;
+    row = row < N ? row : N - 1;
+    const uint4* p = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K) + 2 * q;   // 8 FP32 = two vectors
 #pragma unroll
     for (int u = 0; u < PS; ++u) {
       const int piece = first + h * PS + u;
-      const bool ok = live && piece < kblocks;
+      const bool ok = piece < kblocks;
       w[2 * u] = ok ? ldg_stream16(p + piece * 8) : make_uint4(0u, 0u, 0u, 0u);
       w[2 * u + 1] = ok ? ldg_stream16(p + piece * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
     }
@@ -466,10 +405,9 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
       float sum = 0.f;
 #pragma unroll 8
       for (int wv = 0; wv < NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
-      const int t = threadIdx.x >> 3, r = threadIdx.x & 7;
-      int row0, nrows;
-      MUSE_WALK_GROUP(walk, i, N, C, c, false, row0, nrows);
-      if (t < m && r < nrows) out[static_cast<size_t>(t) * ld_out + row0 + r] = sum;
+      const int t = threadIdx.x >> 3;
+      const int row = (c + i * C) * 8 + (threadIdx.x & 7);
+      if (t < m && row < N) out[static_cast<size_t>(t) * ld_out + row] = sum;
     }
   }
 }
@@ -513,7 +451,7 @@ static cudaError_t launch_fewtok(const void* W, const void* x, void* out, int m,
 
 template <int NW, int U, bool HI, bool PEERS, bool VEC>
 static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
-                                    int tok_split, int whole_groups, int* status, const PeerSync& ps, cudaStream_t s) {
+                                    int tok_split, int* status, const PeerSync& ps, cudaStream_t s) {
   auto kern = fewtok_xreg_kernel<NW, U, HI, PEERS, VEC>;
   static int per_sm[64] = {0}, sms[64] = {0};
   int dev = 0;
@@ -528,24 +466,24 @@ static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int
     per_sm[dev] = resident;
   }
   int walkers = sms[dev] * per_sm[dev] / tok_split;   // CTAs per copy of the walk
-  const int most = PEERS || whole_groups ? (N + 7) / 8 : N;   // a CTA needs a group, or at least a row, of its own
-  if (walkers > most) walkers = most;
+  const int groups = (N + 7) / 8;
+  if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
                                                reinterpret_cast<const __nv_bfloat16*>(x),
                                                reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
-                                               whole_groups, status, ps);
+                                               status, ps);
   return cudaGetLastError();
 }
 
 // The single-GPU instantiation carries no exchange code.
 template <int NW, int U, bool HI>
 static cudaError_t launch_xreg(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
-                               int tok_split, int whole_groups, int* status, const PeerSync& ps, cudaStream_t s) {
-  if (peer_active_host(ps)) return launch_xreg_with<NW, U, HI, true, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, 1, status, ps, s);
+                               int tok_split, int* status, const PeerSync& ps, cudaStream_t s) {
+  if (peer_active_host(ps)) return launch_xreg_with<NW, U, HI, true, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s);
   const bool vec = N % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | (static_cast<uintptr_t>(ld_out) * 2)) & 15) == 0;
-  return vec ? launch_xreg_with<NW, U, HI, false, true>(W, x, out, m, N, K, ld_x, ld_out, tok_split, whole_groups, status, ps, s)
-             : launch_xreg_with<NW, U, HI, false, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, whole_groups, status, ps, s);
+  return vec ? launch_xreg_with<NW, U, HI, false, true>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s)
+             : launch_xreg_with<NW, U, HI, false, false>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, s);
 }
 
 template <int NW, int U, bool XF32>
@@ -565,7 +503,8 @@ static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int 
     per_sm[dev] = resident;
   }
   int walkers = sms[dev] * per_sm[dev] / tok_split;
-  if (walkers > N) walkers = N;   // a CTA needs at least a row of its own
+  const int groups = (N + 7) / 8;
+  if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), x, reinterpret_cast<float*>(out), m, N, K,
                                                ld_x, ld_out, tok_split);
@@ -603,8 +542,7 @@ static bool xreg_serves(int toks, int K, int warps, int unroll) {
 // 1..16 tokens, BF16 weight and output; warps in {16, 32}, unroll in {1, 2, 4}, and 8 with 16 warps when
 // that covers a whole row (K <= 4096). Negative = argument error.
 int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int warps,
-                        int unroll, int tok_split, int whole_groups, int* status, const PeerSync* peers,
-                        cudaStream_t stream) {
+                        int unroll, int tok_split, int* status, const PeerSync* peers, cudaStream_t stream) {
   PeerSync ps = {};
   if (peers && peers->world > 1) {
     ps = *peers;
@@ -626,7 +564,7 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
   if (xreg_serves(toks, K, warps, unroll)) {   // a whole row per batch: the A fragments stay in registers
 #define MUSE_XREG(NW_, U_, HI_)                                 \
     if (warps == NW_ && unroll == U_ && (toks > 8) == HI_)      \
-      e = launch_xreg<NW_, U_, HI_>(W, x, out, m, N, K, ld_x, ld_out, tok_split, whole_groups, status, ps, stream);
+      e = launch_xreg<NW_, U_, HI_>(W, x, out, m, N, K, ld_x, ld_out, tok_split, status, ps, stream);
     MUSE_XREG(32, 1, false) MUSE_XREG(32, 2, false) MUSE_XREG(32, 4, false) MUSE_XREG(32, 1, true) MUSE_XREG(32, 2, true)
     MUSE_XREG(16, 1, false) MUSE_XREG(16, 2, false) MUSE_XREG(16, 4, false) MUSE_XREG(16, 8, false)
     MUSE_XREG(16, 1, true) MUSE_XREG(16, 2, true) MUSE_XREG(16, 4, true) MUSE_XREG(16, 8, true)

@@ -30,7 +30,8 @@ import ctypes
 import torch
 
 from . import _capi
-from .plan import FEWTOK_BUCKETS, DeviceFacts, FewTokPlan, fewtok_fused_plan, GemvPlan, SkinnyPlan, fewtok_plan, gemv_plan, gemv_valid, skinny_plan
+from .plan import (FEWTOK_BUCKETS, GEMM_MIN_TOKENS, DeviceFacts, FewTokPlan, GemmPlan, GemvPlan, SkinnyPlan, fewtok_fused_plan,
+                   fewtok_plan, gemm_plan, gemv_plan, gemv_valid, skinny_plan)
 
 FP32_LAYERS = {"router"}
 # Workspace rule: sized once in prepare() so that every layer at up to this many tokens can split K;
@@ -106,7 +107,9 @@ def prepare(weights: dict[str, torch.Tensor], warmup: bool = True):
             hi, lo = split_hi_lo(state[name])
             state[f"_{name}_hi"], state[f"_{name}_lo"] = hi, lo
         n_max = max(-(-w.shape[0] // 128) * 128 for w in weights.values())
-        state["_ws_floats"] = n_max * WS_MAX_TOKENS
+        # muse_skinny_tc with groups > 1 needs n x tokens floats; muse_gemm_tc with `split` slices meeting in the
+        # workspace (split - 1) times that: room for four slices of the tallest weight, and never less than 16 MB.
+        state["_ws_floats"] = max(3 * n_max * WS_MAX_TOKENS, 4 << 20)
         state["_ws_by_stream"] = {}
         state["_status"] = torch.zeros(1, device=device, dtype=torch.int32)
         state["_tmaps"] = {}
@@ -150,10 +153,10 @@ def _weight_maps(state, layer: str, n: int):
     return maps
 
 
-def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> GemvPlan | FewTokPlan | SkinnyPlan:
+def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> GemvPlan | FewTokPlan | SkinnyPlan | GemmPlan:
     """The (cached) launch plan of a shape; `state["_override"][(layer, m)]` = dict(cluster=, groups=, stages=),
-    dict(wpr=, unroll=) or dict(warps=, unroll=) forces values for tuning sweeps. `fused` = the call carries a
-    peer descriptor."""
+    dict(wpr=, unroll=), dict(warps=, unroll=) or dict(pair=, cluster=, stages=) forces values for tuning
+    sweeps. `fused` = the call carries a peer descriptor."""
     key = (layer, m, n, k, fused)
     ov = state["_override"].get((layer, m))
     if ov is None and key in state["_plans"]:
@@ -167,8 +170,15 @@ def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> 
         few = fewtok_fused_plan(m, n, k, f32)
     elif ov is None and m <= FEWTOK_BUCKETS[-1]:
         few = fewtok_plan(m, n, k, f32, dev)
+    gemm = None
+    if few is None and not f32 and (ov is None or "pair" in ov) and (m >= GEMM_MIN_TOKENS or ov):
+        lib = _capi.load()
+        fit = lambda ntok, pair, stages, cluster, m_, wgs: lib.muse_gemm_tc_max_clusters(ntok, int(pair), stages, cluster, m_, wgs)
+        gemm = gemm_plan(m, n, k, dev, max_clusters=fit, ws_floats_cap=state["_ws_floats"], cnt_cap=CNT_INTS, **(ov or {}))
     if few is not None:
         plan = few
+    elif gemm is not None:
+        plan = gemm
     elif m == 1 and any(gemv_valid(k, f32, w) for w in (1, 2, 4, 8)):
         plan = GemvPlan(**ov) if ov else gemv_plan(n, k, f32, dev)
     else:
@@ -246,10 +256,8 @@ def _kernel_fn_f32_input(x: torch.Tensor, n: int, layer: str, state, out, peers)
 
 
 def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: int, out_ptr: int, ld_out: int, peers,
-            stream: int, device, out_on_host: bool = False) -> None:
-    """One C-ABI call: the kernel `plan` names, on validated arguments. `out_on_host`: the destination is
-    page-locked host memory, where every store is a PCIe write (the register-MMA walk then keeps whole
-    8-row groups so that all of its stores are 16-byte vectors)."""
+            stream: int, device) -> None:
+    """One C-ABI call: the kernel `plan` names, on validated arguments."""
     lib = _capi.load()
     f32 = layer in FP32_LAYERS
     w = state[layer]
@@ -260,7 +268,7 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
         return
     if isinstance(plan, FewTokPlan):
         _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x_ptr, out_ptr, m, n, k, ld_x, ld_out, plan.warps, plan.unroll,
-                                        plan.tok_split, int(out_on_host), status, _peer_ptr(peers), stream),
+                                        plan.tok_split, status, _peer_ptr(peers), stream),
                     f"muse_fewtok_mma({layer}, m={m}, n={n}, k={k}, {plan})")
         return
     if isinstance(plan, GemvPlan):
@@ -268,6 +276,16 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
                                    int(plan.persistent), status, _peer_ptr(peers), stream), f"muse_gemv1({layer}, n={n}, k={k})")
         return
     maps = _weight_maps(state, layer, n)
+    if isinstance(plan, GemmPlan):
+        ws_ptr = cnt_ptr = None
+        if plan.split > 1:
+            ws, cnt = _stream_workspace(state, device)
+            ws_ptr, cnt_ptr = ws.data_ptr(), cnt.data_ptr()
+        _capi.check(lib.muse_gemm_tc(maps[0].ptr, x_ptr, out_ptr, ws_ptr, cnt_ptr, status, m, n, k, ld_x, ld_out, plan.ntok,
+                                     int(plan.pair), plan.cluster, plan.split, plan.stages, plan.warpgroups, _peer_ptr(peers),
+                                     stream),
+                    f"muse_gemm_tc({layer}, m={m}, n={n}, k={k}, {plan})")
+        return
     ws_ptr = cnt_ptr = None
     if plan.groups > 1:
         ws, cnt = _stream_workspace(state, device)
@@ -347,7 +365,7 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record:
             else:
                 x_dev.copy_(x, non_blocking=True)
             _launch(state, layer, plan, m, n, k, x_dev.data_ptr(), k, out.data_ptr() if direct else out_dev.data_ptr(), n, None,
-                    rec, w.device, out_on_host=direct)
+                    rec, w.device)
             if not direct and STORE_OUT_BY_KERNEL and out.data_ptr() % 16 == 0 and (out.numel() * out.element_size()) % 16 == 0:
                 _capi.check(lib.muse_fetch_host(out.data_ptr(), out_dev.data_ptr(), out.numel() * out.element_size(), rec),
                             "muse_fetch_host (copy-out)")

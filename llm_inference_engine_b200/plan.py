@@ -60,6 +60,157 @@ class SkinnyPlan:
         return self.tiles * self.split
 
 
+@dataclass(frozen=True)
+class GemmPlan:
+    """Many tokens through muse_gemm_tc: one token tile as wide as the call, K split so that the CTAs fill the SMs."""
+    ntok: int       # tokens per tile (MMA N): a multiple of 16 up to 256
+    pair: bool      # two 128-row weight tiles per CTA sharing each x chunk
+    cluster: int    # K slices as one thread-block cluster, reduced through distributed shared memory
+    split: int      # K slices as independent CTAs, reduced through the global workspace (one of the two is 1)
+    stages: int     # shared-memory pipeline depth
+    warpgroups: int = 4   # CTA size / 128 threads; all of them work in the epilogue
+
+    @property
+    def slices(self) -> int:
+        return self.cluster * self.split
+
+
+GEMM_MAX_STAGES = 8
+GEMM_MAX_SPLIT = 64
+GEMM_SUB = 16                 # owner blocks of the K-slice reduction are multiples of this many tokens
+GEMM_MIN_SMEM = 116 * 1024    # one CTA per SM (mirrors the C side)
+GEMM_MIN_TOKENS = 33          # below: the register-MMA walk and muse_skinny_tc
+GEMM_WARPGROUPS = 4
+GEMM_BUCKETS = (48, 64, 128, 256)
+
+
+def _gemm_owner_block(mpad: int, slices: int) -> int:
+    return -(-(-(-mpad // slices)) // GEMM_SUB) * GEMM_SUB
+
+
+def gemm_smem_bytes(ntok: int, pair: bool, stages: int, cluster: int, m: int, warpgroups: int = GEMM_WARPGROUPS) -> int:
+    """Dynamic shared memory of a muse_gemm_tc launch (mirrors muse_gemm_tc_smem_bytes); `cluster` = the slices
+    that meet in distributed shared memory (slices that meet in the global workspace need no receive area)."""
+    rows = TILE_ROWS * (2 if pair else 1)
+    mpad = -(-min(m, ntok) // GEMM_SUB) * GEMM_SUB
+    t = _gemm_owner_block(mpad, cluster) if cluster > 1 else mpad
+    rx = (cluster - 1) * rows * t * 4 if cluster > 1 else 0
+    after = rx + warpgroups * GEMM_SUB * rows * 4
+    ring = stages * (TILE_ROWS * BK * 2 * (2 if pair else 1) + ntok * BK * 2)
+    return max(max(ring, after) + 1024, GEMM_MIN_SMEM)
+
+
+def gemm_ws_floats(m: int, n: int, ntok: int, pair: bool, split: int) -> int:
+    """Workspace floats of a launch whose `split` slices meet in global memory (mirrors muse_gemm_tc_ws_floats)."""
+    if split <= 1:
+        return 0
+    rows = TILE_ROWS * (2 if pair else 1)
+    units = -(-n // rows) * -(-m // ntok)
+    mpad = -(-min(m, ntok) // GEMM_SUB) * GEMM_SUB
+    return units * split * (split - 1) * rows * _gemm_owner_block(mpad, split)
+
+
+def gemm_ntok(m: int) -> int:
+    """Equal token tiles, as few as 256 tokens each allow, rounded up to the MMA's multiple of 16."""
+    tiles = -(-m // 256)
+    return -(-(-(-m // tiles)) // 16) * 16
+
+
+def gemm_plan(m: int, n: int, k: int, dev: DeviceFacts = DeviceFacts(), max_clusters=None, ws_floats_cap: int = 0,
+              cnt_cap: int = 0, ntok: int | None = None, pair: bool | None = None, cluster: int | None = None,
+              split: int | None = None, stages: int | None = None) -> GemmPlan | None:
+    """(Row units x K slices x token tiles) CTAs filling the SMs in one wave, one CTA per SM.
+
+    Shapes that were swept on a B200 take their measured best (TUNED_GEMM). Otherwise the slices form one
+    cluster (its receive area overlays the ring and must fit; `max_clusters(ntok, pair, stages, cluster, m,
+    warpgroups)`, the device's occupancy query, caps it: clusters pack into GPCs, so fewer CTAs fit than there
+    are SMs), and pairs of weight tiles (half the x traffic per weight byte, half the units) are taken unless
+    they leave a quarter of the single-tile CTAs idle. A split through the global workspace is used only where
+    the table says so and the workspace (`ws_floats_cap`, `cnt_cap`) and the SM count allow it. Explicit ntok /
+    pair / cluster / split / stages override (tuning sweeps). None: the shape cannot run here."""
+    if k % 8 != 0 or m < 1:
+        return None
+    forced = ntok is not None or pair is not None or cluster is not None or split is not None
+    if ntok is None:
+        ntok = gemm_ntok(m)
+    if ntok % 16 or not 16 <= ntok <= 256:
+        raise ValueError(f"ntok={ntok}: a multiple of 16 up to 256")
+    chunks = -(-k // BK)
+    tok_tiles = -(-m // ntok)
+    limit = dev.smem_optin - 512
+    if not forced:
+        # the first measured bucket that holds the token tile
+        tuned = next((TUNED_GEMM[(n, k, b)] for b in GEMM_BUCKETS if b >= ntok and (n, k, b) in TUNED_GEMM), None) \
+            if tok_tiles == 1 else None
+        if tuned:
+            pair, cluster, split = tuned[0], tuned[1], tuned[2]
+            if stages is None:
+                stages = tuned[3]
+            units = -(-n // (TILE_ROWS * (2 if pair else 1)))
+            if split > 1 and (units * split > dev.sms or gemm_ws_floats(m, n, ntok, pair, split) > ws_floats_cap
+                              or 2 * units > cnt_cap):
+                pair = cluster = split = None   # the workspace route is closed here: plan a cluster instead
+            elif cluster > 1 and (units * cluster > dev.sms or (
+                    max_clusters is not None and max_clusters(ntok, pair, stages, cluster, m, GEMM_WARPGROUPS) < units)):
+                pair = cluster = split = None   # this device does not hold the measured launch in one wave
+
+    def deepest(pr: bool, cl: int) -> int:
+        best = 0
+        for st in range(1, GEMM_MAX_STAGES + 1):
+            if gemm_smem_bytes(ntok, pr, st, cl, m) <= limit:
+                best = st
+        return best
+
+    def widest(pr: bool) -> int:
+        units = -(-n // (TILE_ROWS * (2 if pr else 1))) * tok_tiles
+        cl = max(1, min(dev.sms // units, MAX_CLUSTER, chunks))
+        while cl > 1 and (deepest(pr, cl) < 2 or (max_clusters is not None and
+                                                  max_clusters(ntok, pr, min(deepest(pr, cl), 4), cl, m, GEMM_WARPGROUPS) < units)):
+            cl -= 1
+        return cl
+
+    if split is None:
+        split = 1
+    if pair is None:
+        if cluster is not None or split > 1:
+            pair = True
+        else:
+            cp, cs = widest(True), widest(False)
+            ctas_p = -(-n // (2 * TILE_ROWS)) * tok_tiles * cp
+            ctas_s = -(-n // TILE_ROWS) * tok_tiles * cs
+            pair = ctas_p * 4 >= ctas_s * 3
+    if cluster is None:
+        cluster = 1 if split > 1 else widest(pair)
+    cluster = max(1, min(cluster, MAX_CLUSTER, chunks))
+    split = max(1, min(split, GEMM_MAX_SPLIT, chunks))
+    if cluster > 1 and split > 1:
+        raise ValueError("muse_gemm_tc reduces its K slices either in a cluster or through the workspace, not both")
+    most = deepest(pair, cluster)
+    if most < 1:
+        return None
+    longest = -(-chunks // (cluster * split))
+    stages = max(1, min(stages if stages is not None else 6, most, longest))
+    return GemmPlan(ntok=ntok, pair=bool(pair), cluster=cluster, split=split, stages=stages)
+
+
+# Measured on B200 (CUDA-graph replay, cold L2, in-stream): (n, k, token bucket) -> (pair, cluster, split, stages).
+# The figure after the slash is what the shape took before this kernel (muse_skinny_tc, or the register-MMA walk).
+TUNED_GEMM: dict[tuple[int, int, int], tuple[bool, int, int, int]] = {
+    (12288, 4096, 48): (True, 2, 1, 4),     # qkv_gate 23.7 us
+    (12288, 4096, 64): (True, 2, 1, 4),     # 23.9 / 26.5
+    (12288, 4096, 128): (True, 2, 1, 4),    # 25.4 / 25.6
+    (12288, 4096, 256): (False, 1, 1, 4),   # 30.4 / 31.1
+    (4096, 4096, 48): (False, 4, 1, 6),     # o 12.2
+    (4096, 4096, 64): (False, 4, 1, 6),     # 12.3 / 15.5
+    (4096, 4096, 128): (False, 4, 1, 6),    # 13.9 / 18.5
+    (4096, 4096, 256): (False, 1, 4, 4),    # 16.5 / 23.9
+    (1024, 4096, 128): (False, 8, 1, 4),    # pooler 10.2 / 11.4
+    (1024, 4096, 256): (False, 1, 16, 4),   # 12.6 / 17.3
+    (4096, 1024, 64): (False, 4, 1, 4),     # unpooler 8.0 / 9.1
+    (4096, 1024, 128): (False, 3, 1, 4),    # 8.95 / 9.35
+    (4096, 1024, 256): (False, 2, 1, 4),    # 11.0 / 10.6
+}
+
 # Measured on B200 (CUDA-graph replay, cold L2, in-stream): (n, k, w_is_f32) -> (wpr, unroll, persistent).
 TUNED_GEMV: dict[tuple[int, int, bool], tuple[int, int, bool]] = {
     (12288, 4096, False): (1, 4, True),    # qkv_gate 18.3 us (19.8 non-persistent)
@@ -86,7 +237,6 @@ TUNED_FEWTOK: dict[tuple[int, int, int], tuple[int, ...]] = {
     (4096, 1024, 8): (16, 2),     # unpooler 3.9 / 6.1-6.2
     (4096, 1024, 16): (16, 2),    # 4.2 / 6.4
     (4096, 1024, 32): (16, 2, 2),  # 5.4 / 7.0
-    (4096, 1024, 64): (16, 2, 4),  # 7.2 / 9.5
 }
 # FP32 weights (the router), split to BF16 hi + lo in registers: (n, k, token bucket) -> (unroll, tok_split);
 # 16 warps, up to 8 tokens per copy of the walk.

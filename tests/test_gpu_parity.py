@@ -158,7 +158,15 @@ REPLAY_CASES = [
     ("router", 32, dict(cluster=1, groups=37, stages=2)),
     ("router", 16, dict(cluster=8, groups=8, stages=1)),
     ("o", 5, dict(cluster=16, groups=1, stages=3)),
+    # muse_gemm_tc: the planner's choices (cluster of four; four slices through the workspace; sixteen of them)
+    # and forced ones (pairs of tiles with a cluster of two / three slices through the workspace; a ragged token tile)
+    ("o", 128, None), ("o", 256, None), ("pooler", 256, None), ("qkv_gate", 64, None),
+    ("qkv_gate", 256, dict(pair=True, cluster=2, stages=3)),
+    ("qkv_gate", 100, dict(pair=True, split=3, stages=4)),
+    ("unpooler", 200, dict(pair=False, split=4, stages=2)),
 ]
+REPLAYS = 300
+REPLAYS_WORKSPACE = 1500   # plans whose K slices meet in global memory: the depth of bf16_proj/stress.py:125
 
 
 @pytest.mark.parametrize("layer,m,forced", REPLAY_CASES, ids=lambda v: str(v).replace(" ", ""))
@@ -185,7 +193,10 @@ def test_graph_replays_are_stable_and_leave_workspace_clean(oracle, proj, dev, t
             changed = torch.zeros((), device=dev, dtype=torch.int32)
             limit = 2e-5 if layer == "router" else 5e-3
             first = None
-            for i in range(300):
+            from llm_inference_engine_b200.plan import GemmPlan
+            uses_ws = getattr(plan, "groups", 1) > 1 or (isinstance(plan, GemmPlan) and plan.split > 1)
+            replays = REPLAYS_WORKSPACE if uses_ws else REPLAYS
+            for i in range(replays):
                 if i % 2 == 0:
                     timer.flush.fill_(i & 0xFF)
                 graph.replay()
@@ -196,13 +207,15 @@ def test_graph_replays_are_stable_and_leave_workspace_clean(oracle, proj, dev, t
                 else:
                     changed += (holder["out"] != first).any().int()
             timer.stream.synchronize()
-            assert int(bad) == 0, f"{layer} m={m} {plan}: {int(bad)}/300 bad replays"
+            assert int(bad) == 0, f"{layer} m={m} {plan}: {int(bad)}/{replays} bad replays"
             groups = getattr(plan, "groups", 1)   # the register-MMA plans have no global workspace either
-            if groups == 1:
+            if groups == 1:   # (muse_gemm_tc sums its slices in a fixed order whichever way they meet)
                 assert int(changed) == 0, f"{layer} m={m} {plan}: output changed between replays"
-            if groups > 1:   # only these plans touch (and therefore create) the stream's workspace
+            if uses_ws:   # only these plans touch (and therefore create) the stream's workspace
                 ws, cnt = state["_ws_by_stream"][timer.stream.cuda_stream]
-                assert float(ws.abs().max()) == 0.0 and int(cnt.abs().max()) == 0
+                assert int(cnt.abs().max()) == 0
+                if groups > 1:   # muse_skinny_tc accumulates into it and must leave zeros; muse_gemm_tc only overwrites
+                    assert float(ws.abs().max()) == 0.0
     finally:
         state["_override"].pop((layer, m), None)
     proj.check_status(state)
@@ -219,6 +232,79 @@ def test_rejects_what_it_cannot_run(proj, dev, target_setup):
         proj.kernel_fn({"x": torch.zeros((1, 4096), dtype=torch.float16, device=dev), "config": cfg}, state)
     with pytest.raises(ValueError):
         proj.kernel_fn({"x": torch.zeros((1, 4096), dtype=torch.bfloat16, device=dev), "config": dict(cfg, n=2048)}, state)
+
+
+GEMM_CASES = [  # (m, n, k, ntok, pair, cluster, split, stages, warpgroups)
+    (16, 128, 64, 16, False, 1, 1, 1, 1), (16, 256, 128, 16, True, 1, 1, 2, 4), (64, 512, 1024, 64, True, 4, 1, 2, 4),
+    (100, 1000, 2048, 112, True, 3, 1, 3, 2), (256, 1024, 4096, 256, False, 4, 1, 4, 4), (128, 12288, 4096, 128, True, 2, 1, 4, 4),
+    (256, 12288, 4096, 256, False, 1, 1, 4, 4), (128, 4096, 4096, 128, False, 4, 1, 6, 4), (300, 4096, 1024, 160, True, 4, 1, 3, 4),
+    (33, 1030, 4096, 48, False, 8, 1, 4, 3), (1000, 777, 512, 256, True, 2, 1, 2, 4),
+    (64, 512, 1024, 64, True, 1, 4, 2, 4), (100, 1000, 2048, 112, True, 1, 3, 3, 1), (256, 12288, 4096, 256, True, 1, 3, 3, 4),
+    (256, 4096, 4096, 256, False, 1, 4, 4, 4), (256, 1024, 4096, 256, False, 1, 16, 4, 4), (40, 700, 4096, 48, False, 1, 20, 3, 2),
+]
+
+
+@pytest.mark.parametrize("case", GEMM_CASES, ids=lambda c: "m{}_n{}_k{}_t{}_p{}_c{}_s{}".format(c[0], c[1], c[2], c[3], int(c[4]), c[5], c[6]))
+def test_gemm_entry_point_matches_oracle_and_is_bit_stable(dev, case):
+    """muse_gemm_tc (the m > 32 GEMM: pairs of weight tiles, K slices meeting in a cluster or in the workspace)
+    through the C ABI: FP64 product within the BF16 tolerance, ragged N and m, strided x and out, columns
+    beyond n untouched, identical bits on repeated calls, counters back to zero, and no dependence on what the
+    workspace held before (it is filled with NaN)."""
+    from llm_inference_engine_b200 import _capi
+    from llm_inference_engine_b200._capi import TensorMap
+
+    m, n, k, ntok, pair, cluster, split, stages, wgs = case
+    lib = _capi.load()
+    g = torch.Generator(device=dev).manual_seed(m * 13 + n)
+    w = (torch.randn((n, k), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    x = torch.randn((m, k + 24), generator=g, device=dev).to(torch.bfloat16)[:, :k]
+    ref = x.double() @ w.double().T
+    tm = TensorMap.for_matrix(w.data_ptr(), n, k, k * 2, 128)
+    ws = torch.full((max(1, lib.muse_gemm_tc_ws_floats(m, n, ntok, int(pair), split)),), float("nan"), device=dev)
+    cnt = torch.zeros(max(1, lib.muse_gemm_tc_cnt_ints(m, n, ntok, int(pair), split)), device=dev, dtype=torch.int32)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    if cluster > 1 and lib.muse_gemm_tc_max_clusters(ntok, int(pair), stages, cluster, m, wgs) < 1:
+        pytest.skip("this cluster shape does not fit the device")
+    outs = []
+    for _ in range(3):
+        out = torch.full((m, n + 8), 3.0, device=dev, dtype=torch.bfloat16)
+        _capi.check(lib.muse_gemm_tc(tm.ptr, x.data_ptr(), out.data_ptr(), ws.data_ptr(), cnt.data_ptr(), status.data_ptr(), m, n, k,
+                                     x.stride(0), out.stride(0), ntok, int(pair), cluster, split, stages, wgs, None,
+                                     torch.cuda.current_stream(dev).cuda_stream), "muse_gemm_tc")
+        torch.cuda.synchronize(dev)
+        outs.append(out)
+    assert int(status.item()) == 0 and int(cnt.abs().max()) == 0
+    assert bool((outs[0][:, n:] == 3.0).all())
+    err = float((outs[0][:, :n].double() - ref).norm() / ref.norm())
+    assert err < 5e-3, err
+    row_err = ((outs[0][:, :n].double() - ref).norm(dim=1) / ref.norm(dim=1).clamp(min=1e-6)).max()
+    assert float(row_err) < 1e-2
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+
+
+def test_gemm_rejections(dev):
+    from llm_inference_engine_b200 import _capi
+    from llm_inference_engine_b200._capi import TensorMap
+
+    lib = _capi.load()
+    w = torch.zeros((4096, 1024), device=dev, dtype=torch.bfloat16)
+    x = torch.zeros((64, 1024), device=dev, dtype=torch.bfloat16)
+    out = torch.zeros((64, 4096), device=dev, dtype=torch.bfloat16)
+    ws = torch.zeros(1 << 22, device=dev)
+    cnt = torch.zeros(64, device=dev, dtype=torch.int32)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    tm = TensorMap.for_matrix(w.data_ptr(), 4096, 1024, 2048, 128)
+    call = lambda ntok=64, pair=0, cluster=1, split=1, stages=2, wgs=4, ws_=ws: lib.muse_gemm_tc(
+        tm.ptr, x.data_ptr(), out.data_ptr(), None if ws_ is None else ws_.data_ptr(), cnt.data_ptr(), status.data_ptr(), 64, 4096,
+        1024, 1024, 4096, ntok, pair, cluster, split, stages, wgs, None, None)
+    assert call(ntok=40) == -7                      # tokens per tile: multiples of 16
+    assert call(cluster=2, split=2) == -3           # slices meet in a cluster or in the workspace, not both
+    assert call(cluster=17) == -3 and call(split=17) == -3   # more slices than 64-wide chunks of K
+    assert call(split=4, ws_=None) == -4            # a workspace split needs the workspace
+    assert call(split=8) == -10                     # 32 units x 8 slices cannot all be resident at once
+    assert call(stages=9) == -5 and call(wgs=5) == -9
+    torch.cuda.synchronize(dev)
+    assert int(status.item()) == 0 and float(out.abs().max()) == 0.0
 
 
 FEWTOK_CASES = [  # (m, n, k, warps, unroll) + optional tok_split
@@ -246,11 +332,10 @@ def test_fewtok_entry_point_matches_oracle_and_is_bit_stable(dev, case):
     ref = x.double() @ w.double().T
     status = torch.zeros(1, device=dev, dtype=torch.int32)
     outs = []
-    for rep in range(4):   # the last repetition with whole 8-row groups: same bits, another deal of the rows
+    for _ in range(3):
         out = torch.full((m, n + 5), 3.0, device=dev, dtype=torch.bfloat16)
         _capi.check(lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), out.stride(0), warps,
-                                        unroll, tok_split, int(rep == 3), status.data_ptr(), None,
-                                        torch.cuda.current_stream(dev).cuda_stream),
+                                        unroll, tok_split, status.data_ptr(), None, torch.cuda.current_stream(dev).cuda_stream),
                     "muse_fewtok_mma")
         torch.cuda.synchronize(dev)
         outs.append(out)
@@ -272,7 +357,7 @@ def test_fewtok_rejections(dev):
     out = torch.zeros((17, 64), device=dev, dtype=torch.bfloat16)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
     call = lambda m, n, k, ldx, ldo, warps, unroll, split=1: lib.muse_fewtok_mma(
-        w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, ldx, ldo, warps, unroll, split, 0, status.data_ptr(), None, None)
+        w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k, ldx, ldo, warps, unroll, split, status.data_ptr(), None, None)
     assert call(17, 64, 4096, 4096, 64, 16, 4) == -9        # more than 16 tokens per copy of the walk
     assert call(17, 64, 4096, 4096, 64, 16, 4, split=2) == -9   # x in shared memory: one CTA holds all tokens
     assert call(4, 64, 4096, 4096, 64, 32, 4, split=5) == -9

@@ -49,7 +49,7 @@ def test_line_exchange_gives_up_on_a_silent_peer(dev):
     ps, keep = _absent_peer(_capi, dev, 32, 2 * n_loc, n_loc, torch.bfloat16)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
     t0 = time.perf_counter()
-    rc = lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), None, m, n_loc, k, k, 2 * n_loc, 16, 2, 1, 0, status.data_ptr(),
+    rc = lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), None, m, n_loc, k, k, 2 * n_loc, 16, 2, 1, status.data_ptr(),
                              ctypes.addressof(ps), torch.cuda.current_stream(dev).cuda_stream)
     assert rc == 0
     torch.cuda.synchronize(dev)
@@ -63,7 +63,7 @@ def test_line_exchange_gives_up_on_a_silent_peer(dev):
     # the context is usable: an ordinary call right after
     out = torch.empty((m, n_loc), device=dev, dtype=torch.bfloat16)
     status.zero_()
-    assert lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n_loc, k, k, n_loc, 16, 2, 1, 0, status.data_ptr(), None,
+    assert lib.muse_fewtok_mma(w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n_loc, k, k, n_loc, 16, 2, 1, status.data_ptr(), None,
                                torch.cuda.current_stream(dev).cuda_stream) == 0
     torch.cuda.synchronize(dev)
     assert int(status.item()) == 0 and float((out.double() - ref).norm() / ref.norm()) < 5e-3

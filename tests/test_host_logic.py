@@ -85,6 +85,47 @@ def test_tuned_entries_are_launchable():
         assert plan.fewtok_plan(bucket, n, k, False) == plan.FewTokPlan(warps, unroll, tok_split)
 
 
+@pytest.mark.parametrize("name", [k for k, v in SHAPES.items() if not v[2]])
+@pytest.mark.parametrize("m", [33, 48, 64, 100, 128, 256, 257, 300, 1000])
+def test_gemm_plan_respects_every_kernel_limit(name, m):
+    n, k, _ = SHAPES[name]
+    dev = plan.DeviceFacts()
+    p = plan.gemm_plan(m, n, k, dev, ws_floats_cap=3 * 12288 * 256, cnt_cap=4096)
+    chunks = -(-k // plan.BK)
+    assert p.ntok % 16 == 0 and 16 <= p.ntok <= 256 and -(-m // p.ntok) == -(-m // 256)   # as few token tiles as possible
+    assert (p.cluster == 1 or p.split == 1) and 1 <= p.cluster <= plan.MAX_CLUSTER and 1 <= p.slices <= chunks
+    assert 1 <= p.stages <= plan.GEMM_MAX_STAGES and 1 <= p.warpgroups <= 4
+    assert plan.gemm_smem_bytes(p.ntok, p.pair, p.stages, p.cluster, m, p.warpgroups) + 512 <= plan.SMEM_PER_CTA_MAX
+    units = -(-n // (256 if p.pair else 128)) * -(-m // p.ntok)
+    if p.slices > 1:   # one wave, one CTA per SM: K slices wait for one another
+        assert units * p.slices <= dev.sms
+    if p.split > 1:
+        assert plan.gemm_ws_floats(m, n, p.ntok, p.pair, p.split) <= 3 * 12288 * 256 and 2 * units <= 4096
+    bounds = [s * chunks // p.slices for s in range(p.slices + 1)]
+    assert all(b > a for a, b in zip(bounds, bounds[1:]))
+
+
+def test_gemm_plan_falls_back_to_a_cluster_without_workspace_room():
+    tuned = plan.gemm_plan(256, 4096, 4096, ws_floats_cap=1 << 30, cnt_cap=4096)
+    assert tuned.split == 4 and tuned.cluster == 1
+    small = plan.gemm_plan(256, 4096, 4096, ws_floats_cap=1000, cnt_cap=4096)
+    assert small.split == 1 and small.cluster >= 1
+    assert plan.gemm_plan(256, 4096, 4096, plan.DeviceFacts(sms=100), ws_floats_cap=1 << 30, cnt_cap=4096).split == 1
+    capped = plan.gemm_plan(128, 4096, 4096, max_clusters=lambda *a: 0)     # a device that holds no cluster of this shape
+    assert capped.cluster == 1 and capped.split == 1
+    with pytest.raises(ValueError):
+        plan.gemm_plan(128, 4096, 4096, cluster=2, split=2)
+
+
+def test_gemm_tuned_entries_are_launchable():
+    for (n, k, bucket), (pair, cluster, split, stages) in plan.TUNED_GEMM.items():
+        assert bucket in plan.GEMM_BUCKETS and (cluster == 1 or split == 1)
+        p = plan.gemm_plan(bucket, n, k, ws_floats_cap=3 * 12288 * 256, cnt_cap=4096)
+        longest = -(-(-(-k // plan.BK)) // (cluster * split))
+        assert (p.pair, p.cluster, p.split, p.stages) == (pair, cluster, split, min(stages, longest))
+        assert -(-n // (256 if pair else 128)) * cluster * split <= 148
+
+
 def test_fewtok_f32_table_is_consistent():
     for (n, k, bucket), (unroll, tok_split) in plan.TUNED_FEWTOK_F32.items():
         assert bucket in plan.FEWTOK_BUCKETS and unroll in (2, 4, 8) and k % 32 == 0 and k // 32 <= 16 * unroll
