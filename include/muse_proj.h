@@ -110,6 +110,35 @@ long long muse_fewtok_smem_bytes(int m, int K, int warps);
 int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                     int tok_split, int x_is_f32, void* stream);
 
+/* The post-attention boundary of the reference's decode layer, the producer of the pooler's and the router's
+ * input (_attn_boundary_kernel, best_submissions/muse_decode_layer.py:694-712; decode_layer/reference.py:452-454),
+ * per token over the hidden width d:
+ *     stream1 = alpha * stream + beta * attn_out * rsqrt(mean(attn_out^2) + 1e-8)
+ *     h       = stream1 * rsqrt(mean(stream1^2) + 1e-5) * (1 + norm_w)
+ * stream, stream1, h_f32: FP32 [m, d]; attn_out, h: BF16 [m, d]; alpha, beta: FP32 [d] (the residual
+ * coefficients of the gate); norm_w: BF16 [d]. All contiguous, 16-byte aligned, d % 8 == 0. */
+typedef struct muse_boundary {
+  const float* stream;
+  const void* attn_out;
+  const float* alpha;
+  const float* beta;
+  const void* norm_w;
+  float* stream1;   /* outputs: any of the three may be NULL (not written) */
+  void* h;
+  float* h_f32;
+} muse_boundary_t;
+/* Stand-alone: one CTA per token, d <= 8192, at least one output. */
+int muse_attn_boundary(const muse_boundary_t* bd, int m, int d, void* stream);
+/* Fused: out[m, N] = h . W[N, K]^T with the boundary as the projection's prologue instead of a kernel of its
+ * own (K = d <= 4096, K % 32 == 0, m <= 8, N >= 8 m): the register-MMA walk of muse_fewtok_mma (16 warps x 8
+ * loads), where every CTA rebuilds h in shared memory while its first weight loads are in flight and takes its
+ * x fragments from there; CTA t also writes token t's stream1 / h / h_f32 where those pointers are given.
+ * w_is_f32 = 0: BF16 W, h rounded to BF16 as the MMA input, BF16 out (the pooler; `status` as for
+ * muse_fewtok_mma). w_is_f32 != 0: FP32 W and out, h kept FP32 and split to BF16 hi + lo like the weight (the
+ * router's FP32-input mode, muse_fewtok_f32 with x_is_f32). */
+int muse_fewtok_boundary(const void* W, int w_is_f32, const muse_boundary_t* bd, void* out, int m, int N, int K, int ld_out,
+                         int* status, void* stream);
+
 /* Staging for callers whose activations live in HOST memory (page-locked for the copies to be
  * asynchronous): x goes host -> device on `stream` before the projection is launched there, and
  * muse_copy_d2h_sync brings the result back and returns once it has landed (it synchronises the

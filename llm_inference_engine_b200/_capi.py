@@ -39,6 +39,9 @@ SIGNATURES = {
     "muse_fewtok_smem_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "muse_fewtok_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_int, C.c_void_p]),
+    "muse_attn_boundary": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "muse_fewtok_boundary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                       C.c_void_p, C.c_void_p]),
     "muse_gemm_tc_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_gemm_tc_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_gemm_tc_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
@@ -99,6 +102,13 @@ class PeerSync(C.Structure):
 
     _fields_ = [("world", C.c_int), ("rank", C.c_int), ("col0", C.c_int), ("reserved", C.c_int),
                 ("out", C.c_void_p * MAX_WORLD), ("flags", C.c_void_p * MAX_WORLD), ("ll", C.c_void_p * MAX_WORLD)]
+
+
+class Boundary(C.Structure):
+    """muse_boundary_t: the operands of the post-attention boundary (muse_proj.h)."""
+
+    _fields_ = [("stream", C.c_void_p), ("attn_out", C.c_void_p), ("alpha", C.c_void_p), ("beta", C.c_void_p),
+                ("norm_w", C.c_void_p), ("stream1", C.c_void_p), ("h", C.c_void_p), ("h_f32", C.c_void_p)]
 
 
 class TensorMap:

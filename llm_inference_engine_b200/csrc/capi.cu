@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include "../../include/muse_proj.h"
+#include "boundary.cuh"
 #include "common.cuh"
 
 namespace muse {
@@ -23,6 +24,9 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
 size_t fewtok_smem_bytes(int m, int K, int warps);
 int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                         int tok_split, int x_is_f32, cudaStream_t stream);
+int attn_boundary_dispatch(const BoundaryArgs& bd, int m, int D, cudaStream_t stream);
+int fewtok_boundary_dispatch(const void* W, int w_is_f32, const BoundaryArgs& bd, void* out, int m, int N, int K, int ld_out,
+                             int* status, cudaStream_t stream);
 int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m, int n,
                      int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
                      const PeerSync* peers, cudaStream_t stream);
@@ -120,6 +124,19 @@ int muse_query(int what) {
 }
 
 static_assert(sizeof(muse_peer_sync_t) == sizeof(muse::PeerSync), "muse_peer_sync_t must mirror PeerSync");
+static_assert(sizeof(muse_boundary_t) == sizeof(muse::BoundaryArgs), "muse_boundary_t must mirror BoundaryArgs");
+
+int muse_attn_boundary(const muse_boundary_t* bd, int m, int d, void* stream) {
+  if (!bd) return -1;
+  return muse::attn_boundary_dispatch(*reinterpret_cast<const muse::BoundaryArgs*>(bd), m, d, static_cast<cudaStream_t>(stream));
+}
+
+int muse_fewtok_boundary(const void* W, int w_is_f32, const muse_boundary_t* bd, void* out, int m, int N, int K, int ld_out,
+                         int* status, void* stream) {
+  if (!bd) return -1;
+  return muse::fewtok_boundary_dispatch(W, w_is_f32, *reinterpret_cast<const muse::BoundaryArgs*>(bd), out, m, N, K, ld_out, status,
+                                        static_cast<cudaStream_t>(stream));
+}
 
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,
                int* status, const muse_peer_sync_t* peers, void* stream) {

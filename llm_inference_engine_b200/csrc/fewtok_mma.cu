@@ -21,6 +21,7 @@
 // those registers, which a 32-warp CTA only has for U <= 2; 16 warps x 8 loads serve K = 4096 there.
 // That kernel also runs column-parallel (self-validating lines into the peers' staging) and as several
 // interleaved walks over disjoint token blocks; fewtok_xreg_f32_kernel is its FP32-weight form.
+#include "boundary.cuh"
 #include "common.cuh"
 
 namespace muse {
@@ -152,12 +153,16 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 // output and sends them to every peer's staging as self-validating lines; when its groups are done it
 // unpacks its share of the lines the peers sent here. No fence, no flag, no wait on another CTA.
 // VEC (one GPU) = 16-byte output stores: the caller guarantees N % 8 == 0 and 16-byte aligned rows of out.
-template <int NW, int U, bool HI, bool PEERS, bool VEC>
+// BND = x is not read but rebuilt by the post-attention boundary prologue (boundary.cuh) from `bd`: up to 8
+// tokens, one walk, one GPU; `x` and `ld_x` are ignored.
+template <int NW, int U, bool HI, bool PEERS, bool VEC, bool BND = false>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ x,
                                                               __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
                                                               int ld_out, int tok_split, int* __restrict__ status,
-                                                              const __grid_constant__ PeerSync ps) {
+                                                              const __grid_constant__ PeerSync ps,
+                                                              const __grid_constant__ BoundaryArgs bd) {
+  static_assert(!BND || (!HI && !PEERS && NW * 32 >= 256), "the boundary prologue serves one 8-token walk on one GPU");
   unsigned long long* const trace = MUSE_TRACE_BASE();
   // Diagnostic builds, the exchange (PEERS only): per CTA 16 slots of the global nanosecond timer, 0 entry,
   // 1 first group stored, 2 groups done, 3 peers' lines unpacked; first group: 5 multiplied, 6 synchronised, 7 stored locally.
@@ -197,7 +202,23 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
   // in flight across the reduction below. (A second buffer costs 16 registers the 32-warp CTA does not have.)
   uint4 w[U], xr[U], xh[HI ? U : 1];
   if (my_groups > 0) load(w, 0);
-  {
+  if constexpr (BND) {
+    // The first weight loads are in flight; every CTA now rebuilds h for all tokens and takes its fragments from it.
+    extern __shared__ __align__(16) float bnd_s1[];
+    __shared__ float bnd_red[NW][BND_TOKENS];
+    __shared__ float bnd_inv1[BND_TOKENS], bnd_inv2[BND_TOKENS];
+    boundary_prologue<NW * 32>(bd, m, K, bnd_s1, bnd_red, bnd_inv1, bnd_inv2);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      xr[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (g < m && first + u < kblocks) {
+        float h[8];
+        boundary_h8(bd, bnd_s1, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
+        xr[u] = make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+      }
+    }
+    xh[0] = make_uint4(0u, 0u, 0u, 0u);
+  } else {
     const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
 #pragma unroll
     for (int u = 0; u < U; ++u)
@@ -311,10 +332,13 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
 // best_submissions/muse_decode_layer.py:165-200): x is FP32, split the same way once into registers, and
 // out = x_hi (hi + lo) + x_lo hi, three MMAs per step. Its x fragments take twice the registers, so a
 // group's weights then pass through in two halves (one half in flight at a time).
-template <int NW, int U, bool XF32>
+// BND (with XF32) = the FP32 x is rebuilt by the post-attention boundary prologue from `bd` (up to 8 tokens).
+template <int NW, int U, bool XF32, bool BND = false>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* __restrict__ W, const void* __restrict__ xv,
                                                                   float* __restrict__ out, int m, int N, int K, int ld_x,
-                                                                  int ld_out, int tok_split) {
+                                                                  int ld_out, int tok_split,
+                                                                  const __grid_constant__ BoundaryArgs bd) {
+  static_assert(!BND || XF32, "the boundary hands the router FP32 activations");
   constexpr int OUTS = 64, TOKS = 8;
   constexpr int SUBS = XF32 && U > 1 ? 2 : 1, PS = U / SUBS;   // weight sub-batches of a group, pieces in each
   __shared__ __align__(16) float red[2][NW][OUTS];
@@ -352,7 +376,24 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
     const __nv_bfloat162 l = __floats2bfloat162_rn(ra, rb);
     lo = *reinterpret_cast<const uint32_t*>(&l);
   };
-  if constexpr (XF32) {
+  if constexpr (BND) {
+    extern __shared__ __align__(16) float bnd_s1[];
+    __shared__ float bnd_red[NW][BND_TOKENS];
+    __shared__ float bnd_inv1[BND_TOKENS], bnd_inv2[BND_TOKENS];
+    boundary_prologue<NW * 32>(bd, m, K, bnd_s1, bnd_red, bnd_inv1, bnd_inv2);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      xr[u] = xl[XF32 ? u : 0] = make_uint4(0u, 0u, 0u, 0u);
+      if (g < m && first + u < kblocks) {
+        float h[8];
+        boundary_h8(bd, bnd_s1, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
+        split(__float_as_uint(h[0]), __float_as_uint(h[1]), xr[u].x, xl[XF32 ? u : 0].x);
+        split(__float_as_uint(h[2]), __float_as_uint(h[3]), xr[u].y, xl[XF32 ? u : 0].y);
+        split(__float_as_uint(h[4]), __float_as_uint(h[5]), xr[u].z, xl[XF32 ? u : 0].z);
+        split(__float_as_uint(h[6]), __float_as_uint(h[7]), xr[u].w, xl[XF32 ? u : 0].w);
+      }
+    }
+  } else if constexpr (XF32) {
     const float* xf = reinterpret_cast<const float*>(xv) + static_cast<size_t>(t0 + (g < m ? g : 0)) * ld_x;
     const uint4* px = reinterpret_cast<const uint4*>(xf) + 2 * q;
 #pragma unroll
@@ -472,7 +513,7 @@ static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
                                                reinterpret_cast<const __nv_bfloat16*>(x),
                                                reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
-                                               status, ps);
+                                               status, ps, BoundaryArgs{});
   return cudaGetLastError();
 }
 
@@ -507,7 +548,7 @@ static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int 
   if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), x, reinterpret_cast<float*>(out), m, N, K,
-                                               ld_x, ld_out, tok_split);
+                                               ld_x, ld_out, tok_split, BoundaryArgs{});
   return cudaGetLastError();
 }
 
@@ -530,6 +571,165 @@ int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, i
 }
 
 size_t fewtok_smem_bytes(int m, int K, int warps) { return fewtok_smem(K, m, warps); }
+
+// ---------------------------------------------------------------- the post-attention boundary
+
+// Stand-alone form, one CTA of 256 threads per token; D % 8 == 0 and D <= 8192 (four 8-element chunks per thread,
+// held in registers between the two reductions).
+__global__ void __launch_bounds__(256) attn_boundary_kernel(const __grid_constant__ BoundaryArgs bd, int D) {
+  constexpr int NT = 256, CH = 4;
+  __shared__ float red[NT / 32];
+  __shared__ float s_inv;
+  const int t = blockIdx.x, cpt = D >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto block_inv = [&](float v, float eps) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      float r = lane < NT / 32 ? red[lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+      if (lane == 0) s_inv = rsqrtf(r / static_cast<float>(D) + eps);
+    }
+    __syncthreads();
+    return s_inv;
+  };
+  float v[CH][8], a[CH][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + j * NT;
+    if (c < cpt) {
+      bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a[j]);
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c);
+      const float4 s1 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c + 1);
+      const float4 a0 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * c), a1 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * c + 1);
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(bd.beta) + 2 * c), b1 = __ldg(reinterpret_cast<const float4*>(bd.beta) + 2 * c + 1);
+      const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float be[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        ss = fmaf(a[j][i], a[j][i], ss);
+        v[j][i] = al[i] * sv[i];
+        a[j][i] *= be[i];
+      }
+    }
+  }
+  const float r1 = block_inv(ss, BND_POST_EPS);
+  ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + j * NT;
+    if (c < cpt) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[j][i] = fmaf(a[j][i], r1, v[j][i]);
+        ss = fmaf(v[j][i], v[j][i], ss);
+      }
+      if (bd.stream1) {
+        float4* gp = reinterpret_cast<float4*>(bd.stream1 + static_cast<size_t>(t) * D) + 2 * c;
+        gp[0] = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+        gp[1] = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+      }
+    }
+  }
+  const float r2 = block_inv(ss, BND_RMS_EPS);
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + j * NT;
+    if (c < cpt) {
+      float w[8], h[8];
+      bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.norm_w) + c), w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = v[j][i] * r2 * (1.f + w[i]);
+      if (bd.h)
+        reinterpret_cast<uint4*>(bd.h + static_cast<size_t>(t) * D)[c] =
+            make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+      if (bd.h_f32) {
+        float4* gp = reinterpret_cast<float4*>(bd.h_f32 + static_cast<size_t>(t) * D) + 2 * c;
+        gp[0] = make_float4(h[0], h[1], h[2], h[3]);
+        gp[1] = make_float4(h[4], h[5], h[6], h[7]);
+      }
+    }
+  }
+}
+
+static int boundary_args_ok(const BoundaryArgs& bd, int m, int D) {
+  if (!bd.stream || !bd.attn || !bd.alpha || !bd.beta || !bd.norm_w || m < 1 || D < 8 || D % 8) return -1;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(bd.stream) | reinterpret_cast<uintptr_t>(bd.attn) |
+                        reinterpret_cast<uintptr_t>(bd.alpha) | reinterpret_cast<uintptr_t>(bd.beta) |
+                        reinterpret_cast<uintptr_t>(bd.norm_w) | reinterpret_cast<uintptr_t>(bd.stream1) |
+                        reinterpret_cast<uintptr_t>(bd.h) | reinterpret_cast<uintptr_t>(bd.h_f32);
+  return (all & 15) ? -2 : 0;   // contiguous rows of 16-byte vectors
+}
+
+int attn_boundary_dispatch(const BoundaryArgs& bd, int m, int D, cudaStream_t stream) {
+  const int bad = boundary_args_ok(bd, m, D);
+  if (bad) return bad;
+  if (D > 8192) return -2;
+  if (!bd.stream1 && !bd.h && !bd.h_f32) return -1;
+  attn_boundary_kernel<<<m, 256, 0, stream>>>(bd, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The projection with the boundary as its prologue: 16 warps x 8 loads (K <= 4096), up to 8 tokens, and at least
+// as many 8-row groups as tokens (CTA t publishes token t). f32w = the router's FP32 weight and output.
+template <bool F32W>
+static cudaError_t launch_boundary(const void* W, void* out, int m, int N, int K, int ld_out, int* status, const BoundaryArgs& bd,
+                                   cudaStream_t s) {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  const size_t smem = boundary_smem_bytes(K);
+  if (!sms[dev]) {
+    int v = 0;
+    if ((e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    if constexpr (F32W) {
+      if ((e = cudaFuncSetAttribute(fewtok_xreg_f32_kernel<16, 8, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
+    } else {
+      if ((e = cudaFuncSetAttribute(fewtok_xreg_kernel<16, 8, false, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
+      if ((e = cudaFuncSetAttribute(fewtok_xreg_kernel<16, 8, false, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
+    }
+    sms[dev] = v;
+  }
+  int walkers = sms[dev];   // 512 threads with up to 128 registers and 128 KB of shared memory: one CTA per SM
+  const int groups = (N + 7) / 8;
+  if (walkers > groups) walkers = groups;
+  if constexpr (F32W) {
+    fewtok_xreg_f32_kernel<16, 8, true, true><<<walkers, 512, smem, s>>>(reinterpret_cast<const float*>(W), nullptr,
+                                                                         reinterpret_cast<float*>(out), m, N, K, K, ld_out, 1, bd);
+  } else {
+    const bool vec = N % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | (static_cast<uintptr_t>(ld_out) * 2)) & 15) == 0;
+    if (vec)
+      fewtok_xreg_kernel<16, 8, false, false, true, true><<<walkers, 512, smem, s>>>(
+          reinterpret_cast<const __nv_bfloat16*>(W), nullptr, reinterpret_cast<__nv_bfloat16*>(out), m, N, K, K, ld_out, 1, status,
+          PeerSync{}, bd);
+    else
+      fewtok_xreg_kernel<16, 8, false, false, false, true><<<walkers, 512, smem, s>>>(
+          reinterpret_cast<const __nv_bfloat16*>(W), nullptr, reinterpret_cast<__nv_bfloat16*>(out), m, N, K, K, ld_out, 1, status,
+          PeerSync{}, bd);
+  }
+  return cudaGetLastError();
+}
+
+int fewtok_boundary_dispatch(const void* W, int w_is_f32, const BoundaryArgs& bd, void* out, int m, int N, int K, int ld_out,
+                             int* status, cudaStream_t stream) {
+  if (!W || !out || N <= 0 || (!w_is_f32 && !status)) return -1;
+  const int bad = boundary_args_ok(bd, m, K);
+  if (bad) return bad;
+  if (m > BND_TOKENS || (N + 7) / 8 < m) return -9;
+  if (K % 32 != 0 || K / 32 > 128 || ld_out < N || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
+  const cudaError_t e = w_is_f32 ? launch_boundary<true>(W, out, m, N, K, ld_out, status, bd, stream)
+                                 : launch_boundary<false>(W, out, m, N, K, ld_out, status, bd, stream);
+  return static_cast<int>(e);
+}
 
 // Whether (warps, unroll) has a register-resident instantiation for CTAs of `toks` (8 or 16) tokens.
 static bool xreg_serves(int toks, int K, int warps, int unroll) {

@@ -296,6 +296,88 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
                 f"muse_skinny_tc({layer}, m={m}, n={n}, k={k}, {plan})")
 
 
+# ---- the post-attention boundary in front of the pooler and the router ------------------------------------
+RESIDUAL_TEMPERATURE = 0.3
+RESIDUAL_GATE_EPS = 1e-3
+BOUNDARY_FUSED_MAX_TOKENS = 8
+ROUTER_FP32_INPUT_MAX_TOKENS = 8
+
+
+def prepare_boundary(state, attn_residual_gate: torch.Tensor, pre_ffn_norm: torch.Tensor) -> None:
+    """Once per layer: the residual coefficients of the gate, alpha and beta as FP32 vectors
+    (decode_layer/reference.py:339-344; `_residual_coefficients` of best_submissions/muse_decode_layer.py), and
+    the BF16 norm weight, kept in `state` for attn_boundary() and kernel_fn_boundary()."""
+    _require_cuda(attn_residual_gate, "attn_residual_gate")
+    _require_cuda(pre_ffn_norm, "pre_ffn_norm")
+    w = attn_residual_gate.float() / RESIDUAL_TEMPERATURE
+    beta = torch.sigmoid(w)
+    alpha = torch.sqrt(torch.clamp(torch.sigmoid(-w) * (1.0 + beta), min=RESIDUAL_GATE_EPS))
+    state["_boundary"] = (alpha.contiguous(), beta.contiguous(), pre_ffn_norm.to(torch.bfloat16).contiguous())
+
+
+def _boundary_args(state, stream_in: torch.Tensor, attn_out: torch.Tensor, stream1, h, h_f32) -> _capi.Boundary:
+    if "_boundary" not in state:
+        raise RuntimeError("prepare_boundary(state, attn_residual_gate, pre_ffn_norm) has not been called")
+    alpha, beta, norm_w = state["_boundary"]
+    _require_cuda(stream_in, "stream")
+    _require_cuda(attn_out, "attn_out")
+    m, d = stream_in.shape
+    if (stream_in.dtype != torch.float32 or attn_out.dtype != torch.bfloat16 or tuple(attn_out.shape) != (m, d)
+            or not stream_in.is_contiguous() or not attn_out.is_contiguous() or alpha.numel() != d or d % 8):
+        raise TypeError("stream must be contiguous FP32 [m, D] and attn_out contiguous BF16 [m, D], D as prepared and a multiple of 8")
+    bd = _capi.Boundary()
+    bd.stream, bd.attn_out, bd.alpha, bd.beta, bd.norm_w = (stream_in.data_ptr(), attn_out.data_ptr(), alpha.data_ptr(),
+                                                            beta.data_ptr(), norm_w.data_ptr())
+    for name, t, dt in (("stream1", stream1, torch.float32), ("h", h, torch.bfloat16), ("h_f32", h_f32, torch.float32)):
+        if t is not None:
+            if not t.is_cuda or t.dtype != dt or tuple(t.shape) != (m, d) or not t.is_contiguous():
+                raise TypeError(f"{name} must be a contiguous CUDA {dt} [m, D] tensor")
+            setattr(bd, name, t.data_ptr())
+    return bd
+
+
+def attn_boundary(stream_in: torch.Tensor, attn_out: torch.Tensor, state):
+    """The boundary as a kernel of its own (any m, D <= 8192): returns (stream1 FP32, h BF16, h FP32 or None);
+    the FP32 copy of h is made up to 8 tokens, where the router takes FP32 activations
+    (best_submissions/muse_decode_layer.py:694-712 and its call at :855-858)."""
+    m, d = stream_in.shape
+    stream1 = torch.empty_like(stream_in)
+    h = torch.empty((m, d), device=stream_in.device, dtype=torch.bfloat16)
+    h_f32 = torch.empty_like(stream_in) if m <= ROUTER_FP32_INPUT_MAX_TOKENS else None
+    bd = _boundary_args(state, stream_in, attn_out, stream1, h, h_f32)
+    _capi.check(_capi.load().muse_attn_boundary(ctypes.addressof(bd), m, d, torch.cuda.current_stream(stream_in.device).cuda_stream),
+                f"muse_attn_boundary(m={m}, d={d})")
+    return stream1, h, h_f32
+
+
+def kernel_fn_boundary(data, state, stream1: torch.Tensor | None = None, h: torch.Tensor | None = None,
+                       h_f32: torch.Tensor | None = None) -> torch.Tensor:
+    """kernel_fn for the pooler or the router with the post-attention boundary fused in as the projection's
+    prologue: data = {"stream": FP32 [m, K], "attn_out": BF16 [m, K], "config": {"layer", "m", "n", "k"}} with
+    m <= 8 and K <= 4096; returns h @ W[:n].T (BF16; FP32 for the router, which takes h in FP32). `stream1`,
+    `h`, `h_f32` (optional, preallocated) are filled with the boundary's own outputs, which the rest of the
+    layer needs. Larger m or K: attn_boundary() followed by kernel_fn()."""
+    cfg = data["config"]
+    layer, n = cfg["layer"], int(cfg["n"])
+    if layer not in state or layer.startswith("_"):
+        raise KeyError(f"unknown layer {layer!r}")
+    w = state[layer]
+    stream_in, attn_out = data["stream"], data["attn_out"]
+    m, k = stream_in.shape
+    if k != w.shape[1] or not 0 < n <= w.shape[0]:
+        raise ValueError(f"{layer}: stream {tuple(stream_in.shape)} / n={n} do not fit W {tuple(w.shape)}")
+    if m > BOUNDARY_FUSED_MAX_TOKENS or k > 4096 or k % 32 or -(-n // 8) < m:
+        raise ValueError(f"the fused boundary serves m <= {BOUNDARY_FUSED_MAX_TOKENS}, K <= 4096 in whole 32-element pieces "
+                         f"and n >= 8 m; got m={m}, K={k}, n={n}")
+    f32 = layer in FP32_LAYERS
+    out = torch.empty((m, n), device=stream_in.device, dtype=torch.float32 if f32 else torch.bfloat16)
+    bd = _boundary_args(state, stream_in, attn_out, stream1, h, h_f32)
+    _capi.check(_capi.load().muse_fewtok_boundary(w.data_ptr(), int(f32), ctypes.addressof(bd), out.data_ptr(), m, n, k, n,
+                                                  state["_status"].data_ptr(), torch.cuda.current_stream(stream_in.device).cuda_stream),
+                f"muse_fewtok_boundary({layer}, m={m}, n={n}, k={k})")
+    return out
+
+
 FETCH_X_BY_KERNEL = True
 STORE_OUT_BY_KERNEL = True   # the copy-out of the larger calls by the same small kernel (786 KB: 5 us less than the copy engine)
 FETCH_MAX_TOKENS = 32       # x up to 256 KB: the fetch kernel beats the copy engine at every size measured

@@ -11,8 +11,10 @@ It restates, in plain PyTorch on the CPU, the reference's problem definition and
   bf16_proj/baseline.py    what the reference is timed against (:46-65), restated without sglang:
                            BF16 layers are a plain x @ W.T; the router is F.linear in FP32 up to 8
                            tokens and two products on the BF16 hi/lo halves above
+  decode_layer/reference.py  the post-attention boundary that produces the pooler's and the router's input
+                           (_rms :189-191, residual_coefficients :339-344, ref_front :452-454)
 Parity is PINNED: tests/test_oracle_golden.py checks every function here against vectors produced
-by importing the reference itself (tests/golden/make_golden.py wrote them).
+by importing the reference itself (tests/golden/make_golden.py and make_boundary_golden.py wrote them).
 
 Beside the reference's own geometry (per-GPU TP8 slices of an 8192-hidden model) this module
 carries the 4096-hidden geometry the benchmark is quoted on (TARGET_LAYERS) with its own input
@@ -237,6 +239,54 @@ def router_f32_input_model(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def router_f32_input_reference(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """FP64 product of the FP32 inputs as given: the yardstick of the mode above."""
     return (x.double() @ w.double().T)
+
+
+# ---- the post-attention boundary, the producer of the pooler's and the router's input ----------------------
+# decode_layer/reference.py: RMS_EPS :39, POST_NORM_EPS :40, RESIDUAL_TEMPERATURE :54, RESIDUAL_GATE_EPS :55.
+RMS_EPS = 1e-5
+POST_NORM_EPS = 1e-8
+RESIDUAL_TEMPERATURE = 0.3
+RESIDUAL_GATE_EPS = 1e-3
+ROUTER_FP32_INPUT_UP_TO_TOKENS = 8   # best_submissions/muse_decode_layer.py: ROUTER_FP32_MAX_TOKENS
+
+
+def rms(x: torch.Tensor, eps: float = RMS_EPS) -> torch.Tensor:
+    """decode_layer/reference.py:189-191."""
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def residual_coefficients(gate: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """decode_layer/reference.py:339-344 (the norm-preserving residual): new = alpha * stream + beta * branch."""
+    w = gate.float() / RESIDUAL_TEMPERATURE
+    beta = torch.sigmoid(w)
+    alpha = torch.sqrt(torch.clamp(torch.sigmoid(-w) * (1.0 + beta), min=RESIDUAL_GATE_EPS))
+    return alpha, beta
+
+
+def attn_boundary(stream: torch.Tensor, attn_out: torch.Tensor, gate: torch.Tensor, pre_ffn_norm: torch.Tensor):
+    """decode_layer/reference.py:452-454 (ref_front after the `o` projection): the residual stream after the
+    attention block and the normalised input of the pooler and the router, both FP32:
+        stream1 = alpha * stream + beta * rms(attn_out, 1e-8);  h = rms(stream1, 1e-5) * (1 + pre_ffn_norm).
+    The submission's kernel for it (best_submissions/muse_decode_layer.py:694-712) takes attn_out in BF16 (the
+    projection's output type) and writes h as BF16 and, up to 8 tokens, as FP32 for the router."""
+    alpha, beta = residual_coefficients(gate)
+    stream1 = alpha * stream.float() + beta * rms(attn_out, POST_NORM_EPS)
+    h = rms(stream1) * (1.0 + pre_ffn_norm.float())
+    return stream1, h
+
+
+def boundary_inputs(m: int, d: int, seed: int, device: str = "cpu"):
+    """Seeded inputs of the boundary in the shapes and types the decode layer hands over: FP32 stream with a
+    shared mean direction (rows are far from zero-mean, as in decode_layer/reference.py:132-137), BF16
+    attention output, a residual gate ~ N(0, 0.3) and a norm weight ~ N(0, 0.1) in BF16."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    mean = torch.randn((d,), generator=g, device=device)
+    stream = 0.7 * mean + torch.randn((m, d), generator=g, device=device)
+    attn_out = (0.5 * torch.randn((m, d), generator=g, device=device)).to(torch.bfloat16)
+    gate = 0.3 * torch.randn((d,), generator=g, device=device)
+    norm_w = (0.1 * torch.randn((d,), generator=g, device=device)).to(torch.bfloat16)
+    return stream, attn_out, gate, norm_w
 
 
 # ---- the benchmark's own synthetic data and acceptance rule ---------------------------------------

@@ -463,3 +463,60 @@ def test_router_takes_fp32_activations(oracle, proj, dev, target_setup, m):
         proj.kernel_fn({"x": torch.zeros((33, 4096), device=dev), "config": dict(cfg, m=33)}, state)   # beyond 32 tokens
     with pytest.raises(TypeError):
         proj.kernel_fn({"x": torch.zeros((2, 4096), device=dev), "config": {"m": 2, "n": 1024, "k": 4096, "layer": "pooler"}}, state)
+
+
+@pytest.mark.parametrize("m", [8, 32])
+def test_router_on_a_side_stream_beside_the_pooler(oracle, proj, dev, target_setup, m):
+    """The decode layer's use of the path (best_submissions/muse_decode_layer.py:226-233, :861-869): the router
+    runs on a side stream while the pooler runs on the main one, each through a plan that reduces in the
+    global workspace, so the two calls overlap on the GPU with a workspace each. Fork and join are captured in
+    one CUDA graph; 200 cold replays; both outputs against the oracle every time, and both streams'
+    workspaces and counters zero afterwards."""
+    from llm_inference_engine_b200.graph_timer import ColdReplayTimer
+
+    w_cpu, state = target_setup
+    timer = ColdReplayTimer(dev, flush_bytes=256 << 20)
+    main, side = timer.stream, torch.cuda.Stream(dev)
+    pool = oracle.target_input(m, "pooler", 6100 + m, device="cpu")
+    rout = oracle.target_input(m, "router", 6200 + m, device="cpu")
+    xp, xr = pool["x"].to(dev), rout["x"].to(dev)
+    want_p = (pool["x"].double() @ w_cpu["pooler"].double().T).to(dev)
+    want_r = (rout["x"].double() @ w_cpu["router"].double().T).to(dev)
+    state["_override"][("pooler", m)] = dict(cluster=2, groups=9, stages=3)
+    state["_override"][("router", m)] = dict(cluster=1, groups=37, stages=2)
+    hold = {}
+
+    def both():
+        side.wait_stream(torch.cuda.current_stream(dev))
+        hold["p"] = proj.kernel_fn({"x": xp, "config": pool["config"]}, state)
+        with torch.cuda.stream(side):
+            hold["r"] = proj.kernel_fn({"x": xr, "config": rout["config"]}, state)
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    try:
+        with torch.cuda.stream(main):
+            both()                      # in the open first: each stream's workspace is made outside the capture
+            main.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=main):
+                both()
+            bad = torch.zeros((), device=dev, dtype=torch.int32)
+            for i in range(200):
+                if i % 2 == 0:
+                    timer.flush.fill_(i & 0xFF)
+                graph.replay()
+                ep = (hold["p"].double() - want_p).norm() / want_p.norm()
+                er = (hold["r"].double() - want_r).norm() / want_r.norm()
+                bad += ((ep > 5e-3) | (er > 2e-5)).int()
+            main.synchronize()
+        assert int(bad) == 0, f"{int(bad)}/200 replays with a wrong pooler or router output"
+        assert hold["p"].dtype == torch.bfloat16 and hold["r"].dtype == torch.float32
+        pools = state["_ws_by_stream"]
+        assert main.cuda_stream in pools and side.cuda_stream in pools and pools[main.cuda_stream][0] is not pools[side.cuda_stream][0]
+        for key in (main.cuda_stream, side.cuda_stream):
+            ws, cnt = pools[key]
+            assert float(ws.abs().max()) == 0.0 and int(cnt.abs().max()) == 0
+    finally:
+        state["_override"].pop(("pooler", m), None)
+        state["_override"].pop(("router", m), None)
+    proj.check_status(state)

@@ -134,3 +134,26 @@ def test_target_generators_and_rule(oracle):
     hilo = dr["x"].float() @ hi.float().T + dr["x"].float() @ lo.float().T
     assert oracle.target_check(dr, hilo, w)[0]          # the hi + lo pair meets 1e-5
     assert not oracle.target_check(dr, dr["x"].float() @ hi.float().T, w)[0]  # hi alone does not
+
+
+BOUNDARY = json.loads((Path(__file__).parent / "golden" / "boundary_vectors.json").read_text())
+
+
+def test_boundary_constants_match_reference(oracle):
+    c = BOUNDARY["constants"]
+    assert (oracle.RMS_EPS, oracle.POST_NORM_EPS, oracle.RESIDUAL_TEMPERATURE, oracle.RESIDUAL_GATE_EPS) == (
+        c["RMS_EPS"], c["POST_NORM_EPS"], c["RESIDUAL_TEMPERATURE"], c["RESIDUAL_GATE_EPS"])
+    assert oracle.ROUTER_FP32_INPUT_UP_TO_TOKENS == c["SLICED_MAX_TOKENS"] == 8
+
+
+@pytest.mark.parametrize("rec", BOUNDARY["cases"], ids=lambda r: "m{}_d{}".format(r["m"], r["d"]))
+def test_boundary_restatement_is_bit_identical(oracle, rec):
+    """The post-attention boundary (decode_layer/reference.py:452-454 with :189-191 and :339-344) as restated
+    in the oracle, on inputs regenerated from the recorded seeds."""
+    stream, attn_out, gate, norm_w = oracle.boundary_inputs(rec["m"], rec["d"], rec["seed"])
+    assert digest(torch.cat([stream.flatten(), attn_out.float().flatten(), gate, norm_w.float()])) == rec["inputs_sha256"]
+    alpha, beta = oracle.residual_coefficients(gate)
+    assert digest(alpha) == rec["alpha_sha256"] and digest(beta) == rec["beta_sha256"] and head(alpha) == rec["alpha_head"]
+    stream1, h = oracle.attn_boundary(stream, attn_out, gate, norm_w)
+    assert head(stream1) == rec["stream1_head"] and digest(stream1) == rec["stream1_sha256"]
+    assert head(h) == rec["h_head"] and digest(h) == rec["h_sha256"]
