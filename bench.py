@@ -402,6 +402,64 @@ def gather_check(h: Harness) -> dict:
                     "bitwise where the plan is the same"}
 
 
+def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
+    """The path's first caller beyond the five projections (one GPU): the decode layer's post-attention boundary
+    feeding the pooler and, up to 8 tokens in FP32, the router. Per token count, one graph per variant over
+    rotating cold weight copies: the boundary as a kernel of its own in front of the two projections, and the
+    boundary fused into both as their prologue; each with the router after the pooler on one stream and with
+    the router forked to a side stream as the reference's layer does."""
+    proj = h.proj
+    layers = ("pooler", "router")
+    copies = 80
+    gate = torch.randn(LAYERS["pooler"][1], device=h.device, generator=torch.Generator(device=h.device).manual_seed(3)) * 0.3
+    norm_w = (torch.randn(LAYERS["pooler"][1], device=h.device, generator=torch.Generator(device=h.device).manual_seed(4)) * 0.1).bfloat16()
+    states = []
+    for i in range(copies):
+        st = proj.prepare({name: make_weight(name, h.device, SEED + 31 * i + j) for j, name in enumerate(layers)}, warmup=(i == 0))
+        proj.prepare_boundary(st, gate, norm_w)
+        states.append(st)
+    side = torch.cuda.Stream(h.device)
+    rows = []
+    for m in (1, 4, 8):
+        k = LAYERS["pooler"][1]
+        g = torch.Generator(device=h.device).manual_seed(50 + m)
+        stream_in = torch.randn((m, k), device=h.device, generator=g)
+        attn_out = (torch.randn((m, k), device=h.device, generator=g) * 0.5).bfloat16()
+        cfgs = {name: {"m": m, "n": LAYERS[name][0], "k": k, "layer": name} for name in layers}
+        s1 = torch.empty_like(stream_in)
+        row = {"m": m, "copies": copies}
+        for fused in (False, True):
+            for fork in (False, True):
+                keep = []
+
+                def fn(fused=fused, fork=fork, keep=keep):
+                    keep.clear()
+                    for st in states:
+                        if fused:
+                            if fork:
+                                side.wait_stream(torch.cuda.current_stream(h.device))
+                            keep.append(proj.kernel_fn_boundary({"stream": stream_in, "attn_out": attn_out, "config": cfgs["pooler"]}, st, stream1=s1))
+                            with torch.cuda.stream(side if fork else torch.cuda.current_stream(h.device)):
+                                keep.append(proj.kernel_fn_boundary({"stream": stream_in, "attn_out": attn_out, "config": cfgs["router"]}, st))
+                        else:
+                            _, hb, hf = proj.attn_boundary(stream_in, attn_out, st)
+                            if fork:
+                                side.wait_stream(torch.cuda.current_stream(h.device))
+                            keep.append(proj.kernel_fn({"x": hb, "config": cfgs["pooler"]}, st))
+                            with torch.cuda.stream(side if fork else torch.cuda.current_stream(h.device)):
+                                keep.append(proj.kernel_fn({"x": hf, "config": cfgs["router"]}, st))
+                        if fork:
+                            torch.cuda.current_stream(h.device).wait_stream(side)
+
+                row[("fused" if fused else "separate") + ("_fork_us" if fork else "_us")] = 1e3 * h.time_graph(fn, steps, warmup) / copies
+        rows.append(row)
+    for st in states:
+        proj.check_status(st)
+    del states
+    torch.cuda.empty_cache()
+    return rows
+
+
 def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
     """The same six calls through the public API from HOST buffers: per call, x is copied from pinned
     host memory, the projection runs, and the result is copied back to pinned host memory and waited
@@ -493,6 +551,13 @@ def run_ours(args) -> None:
     sampler = ClockSampler(physical_gpu_index(local))
     n, k = LAYERS[WORKLOAD_LAYER]
 
+    if args.boundary_only:
+        with sampler:
+            table = boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
+        if rank == 0:
+            emit({"boundary_pooler_router": table, "clocks": sampler.summary()})
+        return
+
     if args.case:  # single case, few launches: the command ncu wraps
         layer, m = args.case.split(":")
         with sampler:
@@ -531,9 +596,12 @@ def run_ours(args) -> None:
     value = 1e3 * ms_per_step / len(WORKLOAD_TOKENS)
 
     rows = []
+    boundary_rows = []
     if not args.no_table:
         with sampler:
             rows = case_table(h, list(CASES), max(5, min(args.steps, 20)), args.warmup, peak)
+            if world == 1:
+                boundary_rows = boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -592,6 +660,11 @@ def run_ours(args) -> None:
         "clocks": sampler.summary(),
         "cases": [{k2: (round(v, 4) if isinstance(v, float) else v) for k2, v in r.items()} for r in rows],
     }
+    if boundary_rows:
+        line["boundary_pooler_router"] = {
+            "what": "us per (post-attention boundary -> pooler + router) of the decode layer, cold weights: boundary as its own "
+                    "kernel (separate) or as the prologue of both projections (fused); _fork = router on a side stream",
+            "rows": [{k2: (round(v, 3) if isinstance(v, float) else v) for k2, v in r.items()} for r in boundary_rows]}
     if cpu is not None:
         line["cpu_baseline"] = cpu
     if parity is not None:
@@ -610,6 +683,7 @@ def main() -> None:
     ap.add_argument("--case", default=None, help="layer:m -- time one case only (the command ncu wraps)")
     ap.add_argument("--no-table", action="store_true", help="skip the per-case table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--boundary-only", action="store_true", help="time only the boundary -> pooler + router table")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

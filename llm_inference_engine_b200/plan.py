@@ -121,13 +121,12 @@ def gemm_plan(m: int, n: int, k: int, dev: DeviceFacts = DeviceFacts(), max_clus
               split: int | None = None, stages: int | None = None) -> GemmPlan | None:
     """(Row units x K slices x token tiles) CTAs filling the SMs in one wave, one CTA per SM.
 
-    Shapes that were swept on a B200 take their measured best (TUNED_GEMM). Otherwise the slices form one
-    cluster (its receive area overlays the ring and must fit; `max_clusters(ntok, pair, stages, cluster, m,
-    warpgroups)`, the device's occupancy query, caps it: clusters pack into GPCs, so fewer CTAs fit than there
-    are SMs), and pairs of weight tiles (half the x traffic per weight byte, half the units) are taken unless
-    they leave a quarter of the single-tile CTAs idle. A split through the global workspace is used only where
-    the table says so and the workspace (`ws_floats_cap`, `cnt_cap`) and the SM count allow it. Explicit ntok /
-    pair / cluster / split / stages override (tuning sweeps). None: the shape cannot run here."""
+    Shapes that were swept on a B200 take their measured best (TUNED_GEMM). Otherwise one weight tile per CTA
+    (pairs pay only on the tallest weight) and: up to 128 tokens the slices form one cluster of about a hundred
+    CTAs in all (`max_clusters(ntok, pair, stages, cluster, m, warpgroups)`, the device's occupancy query, caps
+    it: clusters pack into GPCs, so fewer CTAs fit than there are SMs); above, they meet in the global
+    workspace, one CTA per SM, where the workspace (`ws_floats_cap`, `cnt_cap`) allows it. Explicit ntok / pair /
+    cluster / split / stages override (tuning sweeps). None: the shape cannot run here."""
     if k % 8 != 0 or m < 1:
         return None
     forced = ntok is not None or pair is not None or cluster is not None or split is not None
@@ -161,26 +160,30 @@ def gemm_plan(m: int, n: int, k: int, dev: DeviceFacts = DeviceFacts(), max_clus
                 best = st
         return best
 
-    def widest(pr: bool) -> int:
+    def cluster_for(pr: bool) -> int:
+        """About a hundred CTAs (measured on the per-GPU shard shapes: beyond that the wider reduction costs more
+        than the idle SMs), at least four chunks of K per slice, and no more clusters than the device holds."""
         units = -(-n // (TILE_ROWS * (2 if pr else 1))) * tok_tiles
-        cl = max(1, min(dev.sms // units, MAX_CLUSTER, chunks))
+        cl = max(1, min(100 // units, 12, chunks // 4, dev.sms // units))
         while cl > 1 and (deepest(pr, cl) < 2 or (max_clusters is not None and
                                                   max_clusters(ntok, pr, min(deepest(pr, cl), 4), cl, m, GEMM_WARPGROUPS) < units)):
             cl -= 1
         return cl
 
+    if pair is None:
+        pair = cluster is not None or (split or 1) > 1   # a forced slice count alone means pairs (tuning sweeps)
     if split is None:
         split = 1
-    if pair is None:
-        if cluster is not None or split > 1:
-            pair = True
-        else:
-            cp, cs = widest(True), widest(False)
-            ctas_p = -(-n // (2 * TILE_ROWS)) * tok_tiles * cp
-            ctas_s = -(-n // TILE_ROWS) * tok_tiles * cs
-            pair = ctas_p * 4 >= ctas_s * 3
+        if cluster is None and ntok > 128 and tok_tiles == 1:
+            # Wide token tiles: the slices of a tile meet in the workspace (no GPC packing, so every SM can
+            # take one), as long as the workspace holds them.
+            units = -(-n // (TILE_ROWS * (2 if pair else 1)))
+            want = min(dev.sms // units, chunks // 6 if chunks >= 48 else chunks // 4)
+            while want > 1 and (gemm_ws_floats(m, n, ntok, pair, want) > ws_floats_cap or 2 * units > cnt_cap):
+                want -= 1
+            split = max(1, want)
     if cluster is None:
-        cluster = 1 if split > 1 else widest(pair)
+        cluster = 1 if split > 1 else cluster_for(pair)
     cluster = max(1, min(cluster, MAX_CLUSTER, chunks))
     split = max(1, min(split, GEMM_MAX_SPLIT, chunks))
     if cluster > 1 and split > 1:

@@ -110,7 +110,10 @@ def test_gemm_plan_falls_back_to_a_cluster_without_workspace_room():
     assert tuned.split == 4 and tuned.cluster == 1
     small = plan.gemm_plan(256, 4096, 4096, ws_floats_cap=1000, cnt_cap=4096)
     assert small.split == 1 and small.cluster >= 1
-    assert plan.gemm_plan(256, 4096, 4096, plan.DeviceFacts(sms=100), ws_floats_cap=1 << 30, cnt_cap=4096).split == 1
+    fewer = plan.gemm_plan(256, 4096, 4096, plan.DeviceFacts(sms=100), ws_floats_cap=1 << 30, cnt_cap=4096)
+    assert fewer.split == 3 and 32 * fewer.split <= 100     # the measured split does not fit 100 SMs: the rule's own choice
+    untuned = plan.gemm_plan(256, 2048, 4096, ws_floats_cap=1 << 30, cnt_cap=4096)
+    assert untuned.split == 9 and not untuned.pair and plan.gemm_plan(128, 2048, 4096).cluster == 6
     capped = plan.gemm_plan(128, 4096, 4096, max_clusters=lambda *a: 0)     # a device that holds no cluster of this shape
     assert capped.cluster == 1 and capped.split == 1
     with pytest.raises(ValueError):
