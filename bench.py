@@ -402,6 +402,62 @@ def gather_check(h: Harness) -> dict:
                     "bitwise where the plan is the same"}
 
 
+def rowpar_table(h: Harness, steps: int, warmup: int) -> dict:
+    """Column-parallel runs only: the `o` projection in its row-parallel layout (K sharded, the reference's real
+    tensor-parallel layout, bf16_proj/reference.py:17) at m = 1 and 8: checked against an FP32 product of the
+    full weight, then timed three ways on rotating cold copies: all-reduce inside the kernel (fused), kernel +
+    NCCL all-reduce, and the local kernel alone."""
+    from llm_inference_engine_b200 import tp
+
+    proj, dist = h.proj, h.dist
+    n, k = LAYERS["o"]
+    k_loc = k // h.world
+    nccl = tp.RowParallelProjection(proj.prepare, proj.kernel_fn)
+    nccl.cols = {"o": k}
+    fused = tp.FusedRowParallel(proj.prepare, proj.kernel_fn)
+    fused.cols = {"o": k}
+    fused._ensure_layer("o", n, h.device)
+    copies = max(6, min(MAX_COPIES, -(-ROTATE_BYTES // (n * k_loc * 2))))
+    states, fulls = [], []
+    for i in range(copies):
+        w = make_weight("o", h.device, SEED + 17 * i)
+        if i == 0:
+            fulls.append(w.float())
+        states.append(proj.prepare({"o": w[:, h.rank * k_loc:(h.rank + 1) * k_loc].contiguous()}, warmup=(i == 0)))
+        del w
+    rows, bad = [], 0
+    for m in (1, 8):
+        x = make_x("o", m, h.device, 3000 + m)
+        xl = x[:, h.rank * k_loc:(h.rank + 1) * k_loc].contiguous()
+        data = {"x": xl, "config": {"m": m, "n": n, "k": k, "layer": "o"}}
+        want = x.float() @ fulls[0].T
+        for impl in (fused, nccl):
+            got = impl.kernel_fn(data, states[0])
+            tight = impl is fused
+            bad += int(not torch.allclose(got.float(), want, rtol=1e-2 if tight else 2e-2, atol=1e-2 if tight else 5e-2))
+        row = {"layer": "o (row-parallel)", "m": m, "n": n, "k_per_gpu": k_loc, "copies": copies}
+        for key, fn_one in (("us", lambda st: fused.kernel_fn(data, st)), ("nccl_us", lambda st: nccl.kernel_fn(data, st)),
+                            ("kernel_us", lambda st: nccl.kernel_fn_local(data, st))):
+            keep = []
+
+            def fn(fn_one=fn_one, keep=keep):
+                keep.clear()
+                for st in states:
+                    keep.append(fn_one(st))
+
+            row[key] = round(1e3 * h.time_graph(fn, steps, warmup) / copies, 3)
+        rows.append(row)
+    for st in states:
+        proj.check_status(st)
+    flag = torch.tensor([bad], device=h.device, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.SUM)
+    del states, fulls
+    torch.cuda.empty_cache()
+    return {"rows": rows, "parity_ok": int(flag.item()) == 0,
+            "what": "o [4096,4096] with K sharded over the GPUs: us = all-reduce inside the kernel (FP32 partials, one NVLink flight), "
+                    "nccl_us = kernel + NCCL all-reduce of BF16 partials, kernel_us = local kernel alone"}
+
+
 def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
     """The path's first caller beyond the five projections (one GPU): the decode layer's post-attention boundary
     feeding the pooler and, up to 8 tokens in FP32, the router. Per token count, one graph per variant over
@@ -597,11 +653,14 @@ def run_ours(args) -> None:
 
     rows = []
     boundary_rows = []
+    rowpar = None
     if not args.no_table:
         with sampler:
             rows = case_table(h, list(CASES), max(5, min(args.steps, 20)), args.warmup, peak)
             if world == 1:
                 boundary_rows = boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
+            elif h.fused is not None:
+                rowpar = rowpar_table(h, max(5, min(args.steps, 20)), args.warmup)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -665,6 +724,8 @@ def run_ours(args) -> None:
             "what": "us per (post-attention boundary -> pooler + router) of the decode layer, cold weights: boundary as its own "
                     "kernel (separate) or as the prologue of both projections (fused); _fork = router on a side stream",
             "rows": [{k2: (round(v, 3) if isinstance(v, float) else v) for k2, v in r.items()} for r in boundary_rows]}
+    if rowpar is not None:
+        line["row_parallel_o"] = rowpar
     if cpu is not None:
         line["cpu_baseline"] = cpu
     if parity is not None:

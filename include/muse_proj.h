@@ -99,6 +99,21 @@ int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K
                     int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream);
 long long muse_fewtok_smem_bytes(int m, int K, int warps);
 
+/* Row-parallel form of muse_fewtok_mma for m = 1..MUSE_RP_TOKENS tokens: W [N, K] and x [m, K] are THIS RANK's
+ * slice of the reduction dimension (the reference's tensor-parallel layout of the `o` projection,
+ * bf16_proj/reference.py:17, whose all-reduce is the identity on its single GPU,
+ * decode_layer/reference.py:451), and out[m, N] (BF16, in this rank's own memory) = the sum over all ranks.
+ * The all-reduce is part of the kernel, one NVLink flight: every CTA sends its FP32 partial sums to every
+ * rank's staging (its own included) as 16-byte lines {sum, call number, sum, call number} and, once its row
+ * groups are done, adds up the lines of all ranks for those groups in rank order (every rank ends with the
+ * same bits). Of `peers` the fields world, rank, flags[] and ll[] are used: ll[p] is rank p's zeroed staging
+ * of 2 x world x MUSE_RP_TOKENS x N x 8 bytes, peer-mapped; out[] is ignored. K <= 4096, K % 32 == 0,
+ * N % 8 == 0. All ranks must make the same sequence of calls; the wait for a peer's lines is bounded
+ * (MUSE_ST_PEER_DONE_TIMEOUT). No counterpart in the reference beyond the layout it names. */
+#define MUSE_RP_TOKENS 8
+int muse_fewtok_rowpar(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int* status,
+                       const muse_peer_sync_t* peers, void* stream);
+
 /* The same walk over an FP32 weight with FP32 output (the MoE router) for m = 1..8 * tok_split tokens:
  * the kernel reads W as FP32 once and splits every element in registers into BF16 hi = bf16(w) and
  * lo = bf16(w - hi), both multiplied into one FP32 accumulator -- the arithmetic of the reference's

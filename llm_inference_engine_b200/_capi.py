@@ -36,6 +36,8 @@ SIGNATURES = {
                                        C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "muse_fewtok_mma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "muse_fewtok_rowpar": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                     C.c_void_p, C.c_void_p, C.c_void_p]),
     "muse_fewtok_smem_bytes": (C.c_longlong, [C.c_int, C.c_int, C.c_int]),
     "muse_fewtok_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                   C.c_int, C.c_int, C.c_void_p]),
@@ -95,6 +97,7 @@ def check(rc: int, what: str) -> None:
 
 MAX_WORLD = 8
 LL_TOKENS = 32   # MUSE_LL_TOKENS: most tokens of a column-parallel muse_fewtok_mma call
+RP_TOKENS = 8    # MUSE_RP_TOKENS: most tokens of a row-parallel muse_fewtok_rowpar call
 
 
 class PeerSync(C.Structure):

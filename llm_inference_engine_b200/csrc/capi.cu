@@ -24,6 +24,8 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
 size_t fewtok_smem_bytes(int m, int K, int warps);
 int fewtok_f32_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                         int tok_split, int x_is_f32, cudaStream_t stream);
+int fewtok_rowpar_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int* status,
+                           const PeerSync* peers, cudaStream_t stream);
 int attn_boundary_dispatch(const BoundaryArgs& bd, int m, int D, cudaStream_t stream);
 int fewtok_boundary_dispatch(const void* W, int w_is_f32, const BoundaryArgs& bd, void* out, int m, int N, int K, int ld_out,
                              int* status, cudaStream_t stream);
@@ -174,6 +176,12 @@ int muse_fewtok_mma(const void* W, const void* x, void* out, int m, int N, int K
                     int unroll, int tok_split, int* status, const muse_peer_sync_t* peers, void* stream) {
   return muse::fewtok_mma_dispatch(W, x, out, m, N, K, ld_x, ld_out, warps, unroll, tok_split, status,
                                    reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
+}
+
+int muse_fewtok_rowpar(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int* status,
+                       const muse_peer_sync_t* peers, void* stream) {
+  return muse::fewtok_rowpar_dispatch(W, x, out, m, N, K, ld_x, ld_out, status, reinterpret_cast<const muse::PeerSync*>(peers),
+                                      static_cast<cudaStream_t>(stream));
 }
 
 int muse_fewtok_mma_host(const void* W, const void* x_host, void* x_device, void* out_device, void* out_host, int m, int N,

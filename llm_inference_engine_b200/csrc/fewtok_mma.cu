@@ -145,6 +145,12 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 #undef FEWTOK_STAMP
 }
 
+constexpr int RP_TOKENS = 8;   // most tokens of a row-parallel call
+// Byte offset, inside a rank's staging, of the lines `src` sends for token t of call e: 8 bytes per output row.
+__device__ __forceinline__ size_t rp_row_offset(int e, int world, int src, int t, int n) {
+  return ((static_cast<size_t>(e & 1) * world + src) * RP_TOKENS + t) * static_cast<size_t>(n) * 8;
+}
+
 // K <= 32 * NW * U: one batch per group, A fragments resident in registers (no shared-memory x).
 // HI = tokens 8..15 exist. With tok_split > 1 the grid is tok_split interleaved copies of the walk, copy j
 // multiplying tokens [j * TOKS, (j + 1) * TOKS): CTAs c and c + 1 stream the same groups at the same time,
@@ -155,7 +161,14 @@ __global__ void __launch_bounds__(NW * 32) fewtok_mma_kernel(const __nv_bfloat16
 // VEC (one GPU) = 16-byte output stores: the caller guarantees N % 8 == 0 and 16-byte aligned rows of out.
 // BND = x is not read but rebuilt by the post-attention boundary prologue (boundary.cuh) from `bd`: up to 8
 // tokens, one walk, one GPU; `x` and `ld_x` are ignored.
-template <int NW, int U, bool HI, bool PEERS, bool VEC, bool BND = false>
+// RP = row-parallel: W and x are this rank's K slice, so every output is a partial sum that has to meet the other
+// ranks' (the reference's tensor-parallel `o` projection, bf16_proj/reference.py:17; its all-reduce is the
+// identity on one GPU, decode_layer/reference.py:451). One-shot all-reduce inside the kernel: every CTA sends
+// its FP32 partial sums to EVERY rank's staging (its own included) as self-validating 16-byte lines
+// {sum, call number, sum, call number}, and when its groups are done it adds up, for the same groups, the lines
+// of all ranks in rank order (so every rank computes the same bits) and stores BF16 into its own `out`.
+// Up to 8 tokens, N % 8 == 0; staging per rank: 2 x world x 8 tokens x N x 8 bytes.
+template <int NW, int U, bool HI, bool PEERS, bool VEC, bool BND = false, bool RP = false>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat16* __restrict__ W,
                                                               const __nv_bfloat16* __restrict__ x,
                                                               __nv_bfloat16* __restrict__ out, int m, int N, int K, int ld_x,
@@ -163,6 +176,7 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
                                                               const __grid_constant__ PeerSync ps,
                                                               const __grid_constant__ BoundaryArgs bd) {
   static_assert(!BND || (!HI && !PEERS && NW * 32 >= 256), "the boundary prologue serves one 8-token walk on one GPU");
+  static_assert(!RP || (!HI && !PEERS && !BND && !VEC), "the row-parallel exchange serves one 8-token walk");
   unsigned long long* const trace = MUSE_TRACE_BASE();
   // Diagnostic builds, the exchange (PEERS only): per CTA 16 slots of the global nanosecond timer, 0 entry,
   // 1 first group stored, 2 groups done, 3 peers' lines unpacked; first group: 5 multiplied, 6 synchronised, 7 stored locally.
@@ -232,7 +246,7 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
       xh[0] = make_uint4(0u, 0u, 0u, 0u);
     }
   }
-  if constexpr (PEERS) {   // after the first loads are in flight: none of this delays them
+  if constexpr (PEERS || RP) {   // after the first loads are in flight: none of this delays them
     if (threadIdx.x == 0) {
       // The call number, and the book-keeping that advances it: the last CTA to get HERE closes the number,
       // because by then every CTA of the grid has read it. Done first so that nothing waits on it at the end.
@@ -279,6 +293,16 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
         const uint32_t p23 = __shfl_down_sync(0xffffffffu, p01, 2);
         const uint32_t p45 = __shfl_down_sync(0xffffffffu, p01, 4), p67 = __shfl_down_sync(0xffffffffu, p23, 4);
         if (r == 0 && t < m) *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ld_out + row0) = make_uint4(p01, p23, p45, p67);
+      } else if constexpr (RP) {
+        // Rows r, r + 1 of a token sit in neighbouring lanes: one line carries both partial sums.
+        const float other = __shfl_down_sync(0xffffffffu, sum, 1);
+        if ((r & 1) == 0 && t < m) {
+          const int e = s_epoch;
+          const size_t off = rp_row_offset(e, ps.world, ps.rank, t, N) + static_cast<size_t>(row0 + r) * 8;
+          for (int p = 0; p < ps.world; ++p)
+            st_volatile_v4(static_cast<char*>(ps.ll[p]) + off, __float_as_uint(sum), static_cast<uint32_t>(e), __float_as_uint(other),
+                           static_cast<uint32_t>(e));
+        }
       } else if constexpr (!PEERS) {
         if (t < m && row0 + r < N) out[static_cast<size_t>(t) * ld_out + row0 + r] = __float2bfloat16_rn(sum);
       } else {
@@ -299,6 +323,36 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
       }
     }
     if (tr && i == 0 && threadIdx.x == 0) tr[1] = global_ns();
+  }
+  if constexpr (RP) {
+    // Add up, for this CTA's own groups, the partial sums of every rank (this rank's own came the same way).
+    // Units of (group, token, row pair): one thread polls `world` lines and stores two BF16 outputs.
+    __syncthreads();
+    const int e = s_epoch;
+    const uint32_t want = static_cast<uint32_t>(e);
+    bool ok = true;
+    for (int u = threadIdx.x; u < my_groups * 32; u += NW * 32) {
+      const int i = u >> 5, t = (u >> 2) & 7, j = u & 3;
+      if (t >= m) continue;
+      const int row = (c + i * C) * 8 + 2 * j;
+      float a0 = 0.f, a1 = 0.f;
+      for (int src = 0; src < ps.world && ok; ++src) {
+        const char* line = static_cast<const char*>(ps.ll[ps.rank]) + rp_row_offset(e, ps.world, src, t, N) + static_cast<size_t>(row) * 8;
+        uint4 v = ld_volatile_v4(line);
+        if (v.y != want || v.w != want) {
+          const unsigned long long t_start = global_ns();
+          for (;;) {
+            v = ld_volatile_v4(line);
+            if (v.y == want && v.w == want) break;
+            if (global_ns() - t_start > WAIT_LIMIT_NS) { ok = false; break; }
+          }
+        }
+        a0 += __uint_as_float(v.x);
+        a1 += __uint_as_float(v.z);
+      }
+      if (ok) *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(t) * ld_out + row) = pack_bf16x2(a0, a1);
+    }
+    if (!ok) atomicOr(status, ST_PEER_DONE_TIMEOUT);
   }
   if constexpr (PEERS) {
     // Unpack this CTA's share of what the peers sent: (sending rank, token, group) units, 16 bytes of output each.
@@ -515,6 +569,51 @@ static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int
                                                reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
                                                status, ps, BoundaryArgs{});
   return cudaGetLastError();
+}
+
+// Row-parallel launch: the same persistent walk, the all-reduce inside (see RP above).
+template <int NW, int U>
+static cudaError_t launch_xreg_rowpar(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out,
+                                      int* status, const PeerSync& ps, cudaStream_t s) {
+  auto kern = fewtok_xreg_kernel<NW, U, false, false, false, false, true>;
+  static int per_sm[64] = {0}, sms[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!per_sm[dev]) {
+    if ((e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    int resident = 0;
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, NW * 32, 0)) != cudaSuccess) return e;
+    if (resident < 1) return cudaErrorInvalidConfiguration;
+    per_sm[dev] = resident;
+  }
+  int walkers = sms[dev] * per_sm[dev];
+  if (walkers > N / 8) walkers = N / 8;
+  kern<<<walkers, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W), reinterpret_cast<const __nv_bfloat16*>(x),
+                                   reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, 1, status, ps, BoundaryArgs{});
+  return cudaGetLastError();
+}
+
+// out[m, N] = sum over ranks of x_r[m, K_r] . W_r[N, K_r]^T, 1..8 tokens; K_r (this rank's slice) <= 4096 in whole
+// 32-element pieces. `peers`: world, rank, flags[] and ll[] (the staging of every rank) are used; out[] is not.
+int fewtok_rowpar_dispatch(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int* status,
+                           const PeerSync* peers, cudaStream_t stream) {
+  if (!W || !x || !out || !status || !peers || N <= 0 || K <= 0) return -1;
+  const PeerSync ps = *peers;
+  if (ps.world < 2 || ps.world > MAX_WORLD || ps.rank < 0 || ps.rank >= ps.world) return -8;
+  for (int p = 0; p < ps.world; ++p)
+    if (!ps.ll[p] || !ps.flags[p] || (reinterpret_cast<uintptr_t>(ps.ll[p]) & 15)) return -8;
+  if (m < 1 || m > RP_TOKENS) return -9;
+  if (K % 32 != 0 || K / 32 > 128 || N % 8 != 0 || ld_x % 8 != 0 || ld_x < K || ld_out < N || ld_out % 2 != 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(out) & 3)) return -2;
+  const int kb = K / 32;
+  cudaError_t e;
+  if (kb <= 16) e = launch_xreg_rowpar<16, 1>(W, x, out, m, N, K, ld_x, ld_out, status, ps, stream);
+  else if (kb <= 32) e = launch_xreg_rowpar<16, 2>(W, x, out, m, N, K, ld_x, ld_out, status, ps, stream);
+  else if (kb <= 64) e = launch_xreg_rowpar<16, 4>(W, x, out, m, N, K, ld_x, ld_out, status, ps, stream);
+  else e = launch_xreg_rowpar<32, 4>(W, x, out, m, N, K, ld_x, ld_out, status, ps, stream);
+  return static_cast<int>(e);
 }
 
 // The single-GPU instantiation carries no exchange code.

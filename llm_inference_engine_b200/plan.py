@@ -277,7 +277,7 @@ TUNED_SKINNY: dict[tuple[int, int, bool, int], tuple[int, int, int, int]] = {
     (256, 4096, True, 32): (32, 16, 1, 3),       # 7.0
     (256, 4096, True, 64): (64, 16, 1, 3),       # 8.1
     (256, 4096, True, 128): (64, 16, 1, 4),      # 8.0
-    (256, 4096, True, 256): (128, 12, 1, 2),     # 14.7
+    (256, 4096, True, 256): (64, 8, 1, 4),       # 10.6 (four token tiles; 16-wide clusters of 8 tiles do not fit in one wave)
 }
 
 

@@ -82,6 +82,139 @@ class ColumnParallelProjection:
         return self.gather(self.kernel_fn_local(data, state))
 
 
+def shard_columns(weights: dict[str, torch.Tensor], world: int, rank: int) -> dict[str, torch.Tensor]:
+    """This rank's block of every weight's K columns (the reduction dimension), as an independent tensor."""
+    out = {}
+    for name, w in weights.items():
+        a, b = shard_bounds(w.shape[1], world, rank)
+        out[name] = w[:, a:b].contiguous()
+    return out
+
+
+class RowParallelProjection:
+    """Row-parallel projections: each rank holds a block of W's K columns and the matching slice of x (in the
+    reference's model the `o` projection, whose input, the attention output, is already split by heads:
+    bf16_proj/reference.py:17), computes a partial [m, N] with the single-GPU kernels, and the partials are
+    summed over the group. This class is the baseline: the local kernel (BF16 partials, as a stock tensor-
+    parallel stack exchanges them) followed by an NCCL all-reduce. The local compute is injected so that the
+    sharding and reduction logic runs with CPU ranks over gloo."""
+
+    def __init__(self, local_prepare: Callable, local_kernel_fn: Callable, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self._prepare = local_prepare
+        self._kernel_fn = local_kernel_fn
+        self.cols: dict[str, int] = {}
+
+    def prepare(self, weights: dict[str, torch.Tensor], already_sharded: bool = False):
+        if already_sharded:
+            shards = weights
+            self.cols = {k: v.shape[1] * self.world for k, v in weights.items()}
+        else:
+            shards = shard_columns(weights, self.world, self.rank)
+            self.cols = {k: v.shape[1] for k, v in weights.items()}
+        return self._prepare(shards)
+
+    def local_x(self, x: torch.Tensor) -> torch.Tensor:
+        """The slice of a full [m, K] activation this rank multiplies (callers that already hold the slice skip this)."""
+        a, b = shard_bounds(x.shape[1], self.world, self.rank)
+        return x[:, a:b]
+
+    def local_config(self, cfg: dict) -> dict:
+        k = int(cfg["k"])
+        if k != self.cols[cfg["layer"]]:
+            raise ValueError(f"row-parallel calls name the whole reduction dimension: k={k} != {self.cols[cfg['layer']]}")
+        return dict(cfg, k=k // self.world)
+
+    def kernel_fn_local(self, data: dict, state) -> torch.Tensor:
+        """This rank's partial [m, N]; data["x"] is the local [m, K / world] slice."""
+        return self._kernel_fn({"x": data["x"], "config": self.local_config(data["config"])}, state)
+
+    def kernel_fn(self, data: dict, state) -> torch.Tensor:
+        part = self.kernel_fn_local(data, state)
+        dist.all_reduce(part, group=self.group)
+        return part
+
+
+class FusedRowParallel(RowParallelProjection):
+    """Row-parallel projections whose all-reduce is part of the kernel (GPUs of one node, up to 8 tokens):
+    muse_fewtok_rowpar sends FP32 partial sums to every rank's staging in symmetric memory as self-validating
+    lines and adds up all ranks' lines itself, so the result is FP32-accumulated across ranks, identical on
+    every rank, and needs one NVLink flight and no collective call. More tokens take the baseline route."""
+
+    def __init__(self, local_prepare: Callable, local_kernel_fn: Callable, group=None):
+        super().__init__(local_prepare, local_kernel_fn, group)
+        from . import _capi
+
+        if self.world > _capi.MAX_WORLD:
+            raise ValueError(f"world {self.world} > {_capi.MAX_WORLD}")
+        self._capi = _capi
+        self._ll: dict[str, torch.Tensor] = {}
+        self._peers: dict[str, object] = {}
+        self._handles: list = []
+        self._flags = None
+        self._flag_ptrs = None
+
+    def _rendezvous(self, t: torch.Tensor):
+        import torch.distributed._symmetric_memory as symm
+
+        hdl = symm.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+        self._handles.append(hdl)
+        off = int(getattr(hdl, "offset", 0) or 0)
+        return [int(p) + off for p in hdl.buffer_ptrs]
+
+    def _ensure_layer(self, name: str, rows: int, device) -> None:
+        if name in self._peers:
+            return
+        import torch.distributed._symmetric_memory as symm
+
+        if self._flags is None:
+            self._flags = symm.empty((32,), dtype=torch.int32, device=device)
+            self._flags.zero_()
+            self._flag_ptrs = self._rendezvous(self._flags)
+        # 2 halves x sending rank x token x output row, 8 bytes each (an FP32 partial sum and its call number)
+        ll = symm.empty((2, self.world, self._capi.RP_TOKENS, rows, 2), dtype=torch.int32, device=device)
+        ll.zero_()
+        ll_ptrs = self._rendezvous(ll)
+        ps = self._capi.PeerSync()
+        ps.world, ps.rank, ps.col0 = self.world, self.rank, 0
+        for p in range(self.world):
+            ps.flags[p] = self._flag_ptrs[p]
+            ps.ll[p] = ll_ptrs[p]
+        self._ll[name], self._peers[name] = ll, ps
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)   # every rank's staging is zero and mapped before anyone launches
+
+    def prepare(self, weights: dict[str, torch.Tensor], already_sharded: bool = False):
+        state = super().prepare(weights, already_sharded)
+        for name, w in weights.items():
+            if w.dtype == torch.bfloat16:
+                self._ensure_layer(name, w.shape[0], w.device)
+        return state
+
+    def kernel_fn(self, data: dict, state) -> torch.Tensor:
+        import ctypes
+
+        x, cfg = data["x"], self.local_config(data["config"])
+        layer, n, k_loc = cfg["layer"], int(cfg["n"]), int(cfg["k"])
+        m = x.shape[0]
+        w = state[layer]
+        if (layer not in self._peers or m > self._capi.RP_TOKENS or k_loc % 32 or k_loc > 4096 or n != w.shape[0] or n % 8
+                or x.dtype != torch.bfloat16):
+            return super().kernel_fn(data, state)
+        if tuple(x.shape) != (m, k_loc) or not x.is_cuda:
+            raise ValueError(f"{layer}: x must be this rank's CUDA [m, {k_loc}] slice, got {tuple(x.shape)} on {x.device}")
+        if x.stride(1) != 1 or x.data_ptr() % 16 or (m > 1 and (x.stride(0) % 8 or x.stride(0) < k_loc)):
+            x = x.contiguous().clone()
+        out = torch.empty((m, n), device=x.device, dtype=torch.bfloat16)
+        self._capi.check(self._capi.load().muse_fewtok_rowpar(
+            w.data_ptr(), x.data_ptr(), out.data_ptr(), m, n, k_loc, x.stride(0) if m > 1 else k_loc, n,
+            state["_status"].data_ptr(), ctypes.addressof(self._peers[layer]), torch.cuda.current_stream(x.device).cuda_stream),
+            f"muse_fewtok_rowpar({layer}, m={m}, n={n}, k={k_loc})")
+        return out
+
+
 class FusedColumnParallel(ColumnParallelProjection):
     """Column-parallel projections whose all-gather is part of the kernel (GPUs of one node).
 

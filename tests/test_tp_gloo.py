@@ -1,4 +1,4 @@
-"""Column-parallel sharding + all-gather over CPU ranks (gloo, world size 2 and 4). The local
+"""Column-parallel sharding + all-gather, and row-parallel sharding + all-reduce, over CPU ranks (gloo, world size 2 and 4). The local
 compute is the CPU oracle's baseline restatement, so what is under test is the host logic: who owns
 which rows, the gather, and the layout of the reassembled [m, N]."""
 
@@ -50,6 +50,24 @@ def _worker(rank: int, world: int, port: int, q):
                 ok &= torch.allclose(part.float(), want[:, a:b].float(), rtol=1e-2, atol=1e-3)
         try:
             cp.kernel_fn({"x": data["x"], "config": dict(data["config"], n=8)}, state)
+            ok = False
+        except ValueError:
+            pass
+        # row-parallel: K columns sharded, partial products summed over the group
+        rp = tp.RowParallelProjection(oracle.cpu_prepare, oracle.cpu_kernel_fn)
+        bf16 = {k: v for k, v in full.items() if k != "router"}
+        rstate = rp.prepare(bf16)
+        for layer in bf16:
+            a, b = tp.shard_bounds(layers[layer][1], world, rank)
+            ok &= torch.equal(rstate[layer], bf16[layer][:, a:b]) and rstate[layer].is_contiguous()
+            for m in (1, 5):
+                data = oracle.target_input(m, layer, 80 + m, layers=layers)
+                got = rp.kernel_fn({"x": rp.local_x(data["x"]), "config": data["config"]}, rstate)
+                want = oracle.fp32_reference(data, bf16)
+                ok &= tuple(got.shape) == tuple(want.shape) and got.dtype == torch.bfloat16
+                ok &= torch.allclose(got.float(), want, rtol=2e-2, atol=2e-2)     # BF16 partials, summed in BF16
+        try:
+            rp.kernel_fn({"x": rp.local_x(data["x"]), "config": dict(data["config"], k=8)}, rstate)
             ok = False
         except ValueError:
             pass

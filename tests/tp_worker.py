@@ -87,6 +87,51 @@ def main() -> None:
             stream.synchronize()
         if float(worst) > 0.05:
             bad.append(f"fused graph replays at m={m}: max abs error {float(worst):.3e}")
+    # row-parallel `o`: K sharded, one-shot all-reduce inside the kernel (up to 8 tokens) against the FP32 product
+    # of the full weight, against the NCCL route, identical on every rank, and under graph replay
+    o_full = {"o": w_gpu["o"]}
+    rp_nccl = tp.RowParallelProjection(proj.prepare, proj.kernel_fn)
+    rp_state = rp_nccl.prepare(o_full)
+    rp_fused = tp.FusedRowParallel(proj.prepare, proj.kernel_fn)
+    rp_fused.cols = dict(rp_nccl.cols)
+    rp_fused._ensure_layer("o", w_gpu["o"].shape[0], dev)
+    for m in (1, 3, 8, 16):
+        data = oracle.target_input(m, "o", 9000 + m, layers=layers)
+        want = oracle.fp32_reference(data, w_cpu).to(dev)
+        xl = rp_nccl.local_x(data["x"].to(dev)).contiguous()
+        a = rp_fused.kernel_fn({"x": xl, "config": data["config"]}, rp_state)
+        b = rp_nccl.kernel_fn({"x": xl, "config": data["config"]}, rp_state)
+        proj.check_status(rp_state)
+        for tag, out in (("fused", a), ("nccl", b)):
+            tight = tag == "fused" and m <= 8    # beyond 8 tokens the fused class takes the NCCL route: BF16 partials, BF16 sums
+            if not torch.allclose(out.float(), want, rtol=1e-2 if tight else 2e-2, atol=1e-2 if tight else 5e-2):
+                bad.append(f"row-parallel {tag} o m={m}: max abs error {float((out.float() - want).abs().max()):.3e}")
+        if m <= 8:   # FP32 partials summed in rank order: tighter than the BF16 exchange, and the same bits everywhere
+            if float((a.float() - want).norm() / want.norm()) > 3e-3:
+                bad.append(f"row-parallel fused o m={m}: relative L2 {float((a.float() - want).norm() / want.norm()):.3e}")
+            gathered = [torch.empty_like(a) for _ in range(world)]
+            dist.all_gather(gathered, a)
+            if any(not torch.equal(g, a) for g in gathered):
+                bad.append(f"row-parallel fused o m={m}: ranks disagree")
+    for m in (8, 1):
+        data = oracle.target_input(m, "o", 9100 + m, layers=layers)
+        want = oracle.fp32_reference(data, w_cpu).to(dev)
+        xl = rp_nccl.local_x(data["x"].to(dev)).contiguous()
+        hold = {}
+        with torch.cuda.stream(stream):
+            hold["o"] = rp_fused.kernel_fn({"x": xl, "config": data["config"]}, rp_state)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                hold["o"] = rp_fused.kernel_fn({"x": xl, "config": data["config"]}, rp_state)
+            worst = torch.zeros((), device=dev)
+            for _ in range(200):
+                g.replay()
+                worst = torch.maximum(worst, (hold["o"].float() - want).abs().max())
+            stream.synchronize()
+        if float(worst) > 0.05:
+            bad.append(f"row-parallel fused graph replays at m={m}: max abs error {float(worst):.3e}")
+    proj.check_status(rp_state)
     proj.check_status(state)
     flag = torch.tensor([len(bad)], device=dev)
     dist.all_reduce(flag)
