@@ -218,7 +218,10 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
  * muse_skinny_tc, but a CTA multiplies a PAIR of 128-row weight tiles (pair != 0) against one copy of the
  * x chunk (two accumulators in tensor memory), which halves the L2 -> shared-memory traffic that bounds
  * these shapes; pair == 0 keeps one tile per CTA (small weights: more CTAs).
- *   tmap_w   tensor map of W[:n] with box_rows = 128 (muse_tmap_encode_2d)
+ *   tmap_w   tensor map of W[:n] with box_rows = tile_rows (muse_tmap_encode_2d)
+ *   tile_rows  weight rows per CTA when pair == 0: a multiple of 8 up to 128 (must be 128 with pair). A short
+ *            tile lets a weight of any height fill the SMs in one wave without any K split (12288 rows = 140
+ *            CTAs of 88): the MMA stays M = 128 and the surplus accumulator lanes are not read. For few tokens.
  *   x, out   as for muse_skinny_tc; out is BF16
  *   ntok     tokens per tile = MMA N: any multiple of 16 up to 256 (m > ntok runs ceil(m / ntok) token tiles)
  *   cluster  K slices as the CTAs of one thread-block cluster (1 .. 16), summed through distributed shared
@@ -230,18 +233,21 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
  *            Either way the sum has a fixed order: bit-reproducible.
  *   ws, cnt  for split > 1: muse_gemm_tc_ws_floats floats (16-byte aligned, contents irrelevant) and
  *            muse_gemm_tc_cnt_ints counters, zero before the first call and left zero; else may be NULL
- *   stages   pipeline depth 1 .. 8
+ *   stages   pipeline depth 1 .. 12
+ *   k_atoms  64-wide pieces of K per pipeline stage, 1 .. 8 (each its own 128-byte-swizzled TMA box): one step then
+ *            asks DRAM for k_atoms x 128 contiguous bytes of every weight row. K slices are whole steps:
+ *            cluster * split <= ceil(ceil(K / 64) / k_atoms)
  *   warpgroups  1 .. 4: CTA size in units of 128 threads; all of them read the accumulators out, push and store
  * One CTA per SM (the launch asks for at least 116 KB of shared memory). muse_gemm_tc_smem_bytes = the
  * dynamic shared memory of a launch; muse_gemm_tc_max_clusters = how many of its clusters the current
  * device holds at once (0: does not fit). Replaces the cuBLAS call x @ W[:n].T of
  * best_submissions/muse_bf16_proj.py:390. */
-int muse_gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
-int muse_gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
-long long muse_gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split);
-int muse_gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split);
+int muse_gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int k_atoms);
+int muse_gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int k_atoms);
+long long muse_gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split, int tile_rows);
+int muse_gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split, int tile_rows);
 int muse_gemm_tc(const void* tmap_w, const void* x, void* out, float* ws, int* cnt, int* status, int m, int n, int k, int ld_x,
-                 int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
+                 int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups, int tile_rows, int k_atoms,
                  const muse_peer_sync_t* peers, void* stream);
 
 /* muse_skinny_tc for callers that must not allocate device memory (a server whose pool owns all of

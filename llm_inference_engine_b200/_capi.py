@@ -44,12 +44,13 @@ SIGNATURES = {
     "muse_attn_boundary": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "muse_fewtok_boundary": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                        C.c_void_p, C.c_void_p]),
-    "muse_gemm_tc_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
-    "muse_gemm_tc_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
-    "muse_gemm_tc_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
-    "muse_gemm_tc_cnt_ints": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "muse_gemm_tc_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "muse_gemm_tc_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "muse_gemm_tc_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "muse_gemm_tc_cnt_ints": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_gemm_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
-                               C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+                               C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                               C.c_void_p, C.c_void_p]),
     "muse_static_scratch_floats": (C.c_longlong, []),
     "muse_static_scratch_tiles": (C.c_int, []),
     "muse_skinny_tc_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,

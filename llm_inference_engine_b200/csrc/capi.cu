@@ -30,16 +30,17 @@ int attn_boundary_dispatch(const BoundaryArgs& bd, int m, int D, cudaStream_t st
 int fewtok_boundary_dispatch(const void* W, int w_is_f32, const BoundaryArgs& bd, void* out, int m, int N, int K, int ld_out,
                              int* status, cudaStream_t stream);
 int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m, int n,
-                     int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
-                     const PeerSync* peers, cudaStream_t stream);
-long long gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split);
-int gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split);
-int gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
-int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups);
+                     int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups, int tile_rows,
+                     int katoms, const PeerSync* peers, cudaStream_t stream);
+long long gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split, int tile_rows);
+int gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split, int tile_rows);
+int gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int katoms);
+int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int katoms);
 #ifdef MUSE_TRACE
 cudaError_t skinny_trace_set(unsigned long long* p);
 cudaError_t fewtok_trace_set(unsigned long long* p);
 cudaError_t gemm_trace_set(unsigned long long* p);
+cudaError_t gemm_trace_set_knob(int v);
 #endif
 long long skinny_static_ws_floats();
 int skinny_static_cnt_ints();
@@ -103,6 +104,7 @@ int muse_trace_set(void* device_buffer) {
   if (e == cudaSuccess) e = muse::gemm_trace_set(static_cast<unsigned long long*>(device_buffer));
   return static_cast<int>(e);
 }
+int muse_trace_knob(int v) { return static_cast<int>(muse::gemm_trace_set_knob(v)); }
 #endif
 
 int muse_query(int what) {
@@ -253,26 +255,33 @@ int muse_skinny_tc(const void* tmap_w, const void* tmap_w_lo, const void* x, voi
                                   static_cast<cudaStream_t>(stream));
 }
 
-int muse_gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups) {
-  if (ntok < 16 || ntok > 256 || ntok % 16 || stages < 1 || cluster < 1 || m < 1 || warpgroups < 1 || warpgroups > 4) return -1;
-  return muse::gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, warpgroups);
+static bool gemm_tile_rows_ok(int pair, int tile_rows) {
+  return tile_rows >= 8 && tile_rows <= 128 && tile_rows % 8 == 0 && (!pair || tile_rows == 128);
 }
 
-int muse_gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups) {
-  return muse::gemm_tc_max_clusters(ntok, pair, stages, cluster, m, warpgroups);
+int muse_gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int k_atoms) {
+  if (ntok < 16 || ntok > 256 || ntok % 16 || stages < 1 || cluster < 1 || m < 1 || warpgroups < 1 || warpgroups > 4 ||
+      !gemm_tile_rows_ok(pair, tile_rows) || k_atoms < 1 || k_atoms > 8)
+    return -1;
+  return muse::gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, warpgroups, tile_rows, k_atoms);
 }
 
-long long muse_gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split) {
-  if (m < 1 || n < 1 || ntok < 16 || ntok > 256 || ntok % 16 || split < 1) return -1;
-  return muse::gemm_tc_ws_floats(m, n, ntok, pair, split);
+int muse_gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int k_atoms) {
+  if (!gemm_tile_rows_ok(pair, tile_rows)) return -1;
+  return muse::gemm_tc_max_clusters(ntok, pair, stages, cluster, m, warpgroups, tile_rows, k_atoms);
 }
-int muse_gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split) {
-  if (m < 1 || n < 1 || ntok < 16 || ntok > 256 || ntok % 16 || split < 1) return -1;
-  return muse::gemm_tc_cnt_ints(m, n, ntok, pair, split);
+
+long long muse_gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split, int tile_rows) {
+  if (m < 1 || n < 1 || ntok < 16 || ntok > 256 || ntok % 16 || split < 1 || !gemm_tile_rows_ok(pair, tile_rows)) return -1;
+  return muse::gemm_tc_ws_floats(m, n, ntok, pair, split, tile_rows);
+}
+int muse_gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split, int tile_rows) {
+  if (m < 1 || n < 1 || ntok < 16 || ntok > 256 || ntok % 16 || split < 1 || !gemm_tile_rows_ok(pair, tile_rows)) return -1;
+  return muse::gemm_tc_cnt_ints(m, n, ntok, pair, split, tile_rows);
 }
 
 int muse_gemm_tc(const void* tmap_w, const void* x, void* out, float* ws, int* cnt, int* status, int m, int n, int k, int ld_x,
-                 int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
+                 int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups, int tile_rows, int k_atoms,
                  const muse_peer_sync_t* peers, void* stream) {
   if (!tmap_w || !x) return -1;
   if (ld_x < k || ld_x % 8 != 0) return -2;
@@ -282,7 +291,7 @@ int muse_gemm_tc(const void* tmap_w, const void* x, void* out, float* ws, int* c
   if (r != 0) return r;
   CUtensorMap tw;
   memcpy(&tw, tmap_w, sizeof(tw));
-  return muse::gemm_tc_dispatch(&tw, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok, pair, cluster, split, stages, warpgroups,
+  return muse::gemm_tc_dispatch(&tw, &tx, out, ws, cnt, status, m, n, k, ld_out, ntok, pair, cluster, split, stages, warpgroups, tile_rows, k_atoms,
                                 reinterpret_cast<const muse::PeerSync*>(peers), static_cast<cudaStream_t>(stream));
 }
 

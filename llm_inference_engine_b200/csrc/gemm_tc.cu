@@ -30,7 +30,8 @@ namespace muse {
 
 constexpr int GT_ROWS = 128;       // rows of one weight tile = MMA M
 constexpr int GT_BK = 64;          // K elements per stage
-constexpr int GT_MAX_STAGES = 8;
+constexpr int GT_MAX_STAGES = 12;
+constexpr int GT_MAX_KATOMS = 8;     // 64-wide K atoms per pipeline stage
 constexpr int GT_MAX_CLUSTER = 16;
 constexpr int GT_SUB = 16;         // tokens summed, staged and stored at a time; owner blocks are multiples of it
 constexpr int GT_MIN_SMEM = 116 * 1024;   // more than half of the 228 KB of an SM: one CTA per SM
@@ -71,10 +72,16 @@ template <bool PAIR, bool PEERS>
 __global__ void __launch_bounds__(GT_MAX_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int* __restrict__ cnt, int* __restrict__ status, int m,
-               int n, int chunks, int ntok, int stages, int tmem_cols, int ld_out, const __grid_constant__ PeerSync ps) {
+               int n, int chunks, int ntok, int stages, int tmem_cols, int ld_out, int tile_rows, int katoms,
+               const __grid_constant__ PeerSync ps) {
   constexpr int H = PAIR ? 2 : 1;          // weight tiles (accumulators) per CTA
-  constexpr int ROWS = GT_ROWS * H;        // weight rows per CTA
-  constexpr int A_BYTES = GT_ROWS * GT_BK * 2;
+  constexpr int ROWS = GT_ROWS * H;        // accumulator rows per CTA (row stride of the staging and the slots)
+  // Weight rows this CTA owns: 256 for a pair; else `tile_rows` (a multiple of 8 up to 128 = the box of tm_w). A
+  // short tile lets a weight of any height fill the SMs in one wave without splitting K: the MMA is still M = 128
+  // and reads 128 rows of shared memory, but the rows past the tile are whatever lies there, they only reach
+  // accumulator lanes nobody reads, and the tensor pipe has the time at the few tokens this is used for.
+  const int own_rows = PAIR ? ROWS : tile_rows;
+  const uint32_t A_BYTES = static_cast<uint32_t>(PAIR ? GT_ROWS : tile_rows) * (GT_BK * 2);
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[GT_MAX_STAGES];
   __shared__ __align__(8) uint64_t bar_empty[GT_MAX_STAGES];
@@ -97,11 +104,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   // meet in distributed shared memory, or the launch has no cluster and they meet in the global workspace.
   const bool dsm = gt_cluster_size() > 1;
   const int csize = static_cast<int>(gridDim.y), crank = static_cast<int>(blockIdx.y);
-  const int c0 = static_cast<int>(static_cast<uint32_t>(crank) * static_cast<uint32_t>(chunks) / static_cast<uint32_t>(csize));
-  const int c1 = static_cast<int>((static_cast<uint32_t>(crank) + 1u) * static_cast<uint32_t>(chunks) / static_cast<uint32_t>(csize));
-  const int nchunks = c1 - c0;
+  // A pipeline stage holds `katoms` 64-wide K atoms of every operand (each its own swizzled box), so that one step
+  // asks DRAM for katoms x 128 contiguous bytes of every weight row instead of 128. K is dealt to the slices in
+  // whole steps; atoms past the end of K read as zeros.
+  const int steps = (chunks + katoms - 1) / katoms;
+  const int c0 = static_cast<int>(static_cast<uint32_t>(crank) * static_cast<uint32_t>(steps) / static_cast<uint32_t>(csize));
+  const int c1 = static_cast<int>((static_cast<uint32_t>(crank) + 1u) * static_cast<uint32_t>(steps) / static_cast<uint32_t>(csize));
+  const int nchunks = c1 - c0;   // steps of this slice
   const uint32_t b_bytes = static_cast<uint32_t>(ntok) * (GT_BK * 2);
-  const uint32_t stage_bytes = A_BYTES * H + b_bytes;
+  const uint32_t a_all = A_BYTES * H * static_cast<uint32_t>(katoms);      // all A atoms of a stage, then all B atoms
+  const uint32_t stage_bytes = a_all + b_bytes * static_cast<uint32_t>(katoms);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the 128-byte swizzle repeats every 1024 bytes
 
   uint64_t pol_w = 0, pol_x = 0;
@@ -110,9 +122,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const uint32_t full = smem_u32(&bar_full[s]);
     const uint32_t a = smem_base + static_cast<uint32_t>(s) * stage_bytes;
     mbar_expect_tx(full, stage_bytes);
-    tma_load_2d(a, &tm_w, (c0 + i) * GT_BK, tile_n * ROWS, full, pol_w);
-    if (PAIR) tma_load_2d(a + A_BYTES, &tm_w, (c0 + i) * GT_BK, tile_n * ROWS + GT_ROWS, full, pol_w);
-    tma_load_2d(a + A_BYTES * H, &tm_x, (c0 + i) * GT_BK, tile_m * ntok, full, pol_x);
+    for (int t = 0; t < katoms; ++t) {
+      const int kcol = ((c0 + i) * katoms + t) * GT_BK;
+      tma_load_2d(a + static_cast<uint32_t>(t) * A_BYTES * H, &tm_w, kcol, tile_n * own_rows, full, pol_w);
+      if (PAIR) tma_load_2d(a + static_cast<uint32_t>(t) * A_BYTES * H + A_BYTES, &tm_w, kcol, tile_n * own_rows + GT_ROWS, full, pol_w);
+    }
+    for (int t = 0; t < katoms; ++t)
+      tma_load_2d(a + a_all + static_cast<uint32_t>(t) * b_bytes, &tm_x, ((c0 + i) * katoms + t) * GT_BK, tile_m * ntok, full, pol_x);
     ++issued;
   };
 
@@ -186,15 +202,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tc_fence_after_sync();
         if (i == 0) GT_STAMP(2);
         const uint32_t a = smem_base + static_cast<uint32_t>(s) * stage_bytes;
-        const uint64_t a0_desc = umma_desc_k_sw128(a);
-        const uint64_t a1_desc = umma_desc_k_sw128(a + A_BYTES);
-        const uint64_t b_desc = umma_desc_k_sw128(a + A_BYTES * H);
+#pragma unroll 1
+        for (int t = 0; t < katoms; ++t) {
+          const uint64_t a0_desc = umma_desc_k_sw128(a + static_cast<uint32_t>(t) * A_BYTES * H);
+          const uint64_t a1_desc = umma_desc_k_sw128(a + static_cast<uint32_t>(t) * A_BYTES * H + A_BYTES);
+          const uint64_t b_desc = umma_desc_k_sw128(a + a_all + static_cast<uint32_t>(t) * b_bytes);
 #pragma unroll
-        for (int k = 0; k < GT_BK / 16; ++k) {
-          // 16 BF16 = 32 bytes further along K inside the swizzle span: +2 in 16-byte units.
-          const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
-          umma_bf16(tmem_acc, a0_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
-          if (PAIR) umma_bf16(tmem_acc + acc_stride, a1_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+          for (int k = 0; k < GT_BK / 16; ++k) {
+            // 16 BF16 = 32 bytes further along K inside the swizzle span: +2 in 16-byte units.
+            const uint32_t accumulate = (i > 0 || t > 0 || k > 0) ? 1u : 0u;
+            umma_bf16(tmem_acc, a0_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+            if (PAIR) umma_bf16(tmem_acc + acc_stride, a1_desc + 2 * k, b_desc + 2 * k, idesc, accumulate);
+          }
         }
         umma_commit(smem_u32(&bar_empty[s]));
         if (++s == stages) {
@@ -377,8 +396,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       for (int it = r; it < GT_SUB * VPT; it += 128) {
         const int j = it / VPT, g8 = it % VPT;
         const int tok = my_first + sub + j;
-        const int n0 = tile_n * ROWS + g8 * 8;
-        if (tok >= mvalid || n0 >= n) continue;
+        const int n0 = tile_n * own_rows + g8 * 8;
+        if (tok >= mvalid || n0 >= n || g8 * 8 >= own_rows) continue;
         const float4 lo = *reinterpret_cast<const float4*>(stage + j * ROWS + g8 * 8);
         const float4 hi = *reinterpret_cast<const float4*>(stage + j * ROWS + g8 * 8 + 4);
         const size_t o = static_cast<size_t>(tok0 + tok) * ld_out + col0 + n0;
@@ -440,19 +459,22 @@ static int gt_tmem_cols(int ntok, int pair) {
   return cols;   // 32 .. 512, a power of two
 }
 
-int gemm_tc_stage_bytes(int ntok, int pair) { return GT_ROWS * GT_BK * 2 * (pair ? 2 : 1) + ntok * GT_BK * 2; }
+int gemm_tc_stage_bytes(int ntok, int pair, int tile_rows, int katoms) {
+  return katoms * ((pair ? 2 * GT_ROWS : tile_rows) * GT_BK * 2 + ntok * GT_BK * 2);
+}
 
 // Dynamic shared memory of a launch: the ring, or the receive slots plus the store staging (one area per warpgroup)
 // that replace it after the main loop, whichever is larger, plus alignment slack.
 // (`cluster` = K slices that meet in distributed shared memory; slices that meet in the global workspace need none.)
-int gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups) {
+int gemm_tc_smem_bytes(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int katoms) {
   const int rows = GT_ROWS * (pair ? 2 : 1);
   const int mvalid = m < ntok ? m : ntok;
   const int mpad = (mvalid + GT_SUB - 1) / GT_SUB * GT_SUB;
   const int T = cluster > 1 ? gt_owner_block(mpad, cluster) : mpad;
   const int rx = cluster > 1 ? (cluster - 1) * rows * T * 4 : 0;
   const int after = rx + warpgroups * GT_SUB * rows * 4;
-  const int ring = stages * gemm_tc_stage_bytes(ntok, pair);
+  // (a short tile's MMA reads 128 rows from where its tile starts: keep the last stage's over-read inside)
+  const int ring = stages * gemm_tc_stage_bytes(ntok, pair, tile_rows, katoms) + (pair ? 0 : (GT_ROWS - tile_rows) * GT_BK * 2);
   const int need = (ring > after ? ring : after) + 1024;
   // Never less than half an SM's shared memory: two of these CTAs must not share an SM, because together
   // they could ask for more tensor memory than the SM has, and tcgen05.alloc waits without a limit.
@@ -483,8 +505,8 @@ static cudaError_t gt_configure(int dev, int* room_out) {
 }
 
 static void gt_fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int m, int n, int ntok, int pair, int cluster,
-                           int split, int warpgroups, size_t smem, cudaStream_t stream) {
-  const int rows = GT_ROWS * (pair ? 2 : 1);
+                           int split, int warpgroups, int tile_rows, size_t smem, cudaStream_t stream) {
+  const int rows = pair ? 2 * GT_ROWS : tile_rows;
   *cfg = cudaLaunchConfig_t{};
   cfg->gridDim = dim3((n + rows - 1) / rows, cluster * split, (m + ntok - 1) / ntok);
   cfg->blockDim = dim3(128 * warpgroups, 1, 1);
@@ -500,35 +522,36 @@ static void gt_fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, i
 
 template <bool PAIR, bool PEERS>
 static cudaError_t gt_launch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m,
-                             int n, int chunks, int ntok, int cluster, int split, int stages, int warpgroups, int ld_out,
-                             const PeerSync& ps, cudaStream_t stream) {
+                             int n, int chunks, int ntok, int cluster, int split, int stages, int warpgroups, int tile_rows,
+                             int katoms, int ld_out, const PeerSync& ps, cudaStream_t stream) {
   int dev = 0, room = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if ((e = gt_configure<PAIR, PEERS>(dev, &room)) != cudaSuccess) return e;
-  const size_t smem = static_cast<size_t>(gemm_tc_smem_bytes(ntok, PAIR, stages, cluster, m, warpgroups));
+  const size_t smem = static_cast<size_t>(gemm_tc_smem_bytes(ntok, PAIR, stages, cluster, m, warpgroups, tile_rows, katoms));
   if (smem > static_cast<size_t>(room)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
-  gt_fill_config(&cfg, attr, m, n, ntok, PAIR, cluster, split, warpgroups, smem, stream);
+  gt_fill_config(&cfg, attr, m, n, ntok, PAIR, cluster, split, warpgroups, tile_rows, smem, stream);
   return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<PAIR, PEERS>, *tw, *tx, reinterpret_cast<__nv_bfloat16*>(out), ws, cnt, status,
-                            m, n, chunks, ntok, stages, gt_tmem_cols(ntok, PAIR), ld_out, ps);
+                            m, n, chunks, ntok, stages, gt_tmem_cols(ntok, PAIR), ld_out, tile_rows, katoms, ps);
 }
 
 // How many clusters of this launch shape the device holds at once (0: the shape cannot launch; negative: bad argument).
-int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups) {
+int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int warpgroups, int tile_rows, int katoms) {
   if (cluster < 1 || cluster > GT_MAX_CLUSTER || stages < 1 || stages > GT_MAX_STAGES || m < 1 || ntok < 16 || ntok > 256 ||
-      ntok % 16 || warpgroups < 1 || warpgroups > GT_MAX_THREADS / 128)
+      ntok % 16 || warpgroups < 1 || warpgroups > GT_MAX_THREADS / 128 || tile_rows < 8 || tile_rows > GT_ROWS || tile_rows % 8 || katoms < 1 || katoms > GT_MAX_KATOMS)
     return -1;
   int dev = 0, room = 0, num = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
   const cudaError_t e = pair ? gt_configure<true, false>(dev, &room) : gt_configure<false, false>(dev, &room);
   if (e != cudaSuccess) return -1;
-  const size_t smem = static_cast<size_t>(gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, warpgroups));
+  const size_t smem = static_cast<size_t>(gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, warpgroups, tile_rows, katoms));
   if (smem > static_cast<size_t>(room)) return 0;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
-  gt_fill_config(&cfg, attr, m < ntok ? m : ntok, GT_ROWS * (pair ? 2 : 1), ntok, pair, cluster, 1, warpgroups, smem, nullptr);
+  gt_fill_config(&cfg, attr, m < ntok ? m : ntok, pair ? 2 * GT_ROWS : tile_rows, ntok, pair, cluster, 1, warpgroups, tile_rows, smem,
+                 nullptr);
   const cudaError_t q = pair ? cudaOccupancyMaxActiveClusters(&num, gemm_tc_kernel<true, false>, &cfg)
                              : cudaOccupancyMaxActiveClusters(&num, gemm_tc_kernel<false, false>, &cfg);
   if (q != cudaSuccess) {
@@ -539,24 +562,25 @@ int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int
 }
 
 // Workspace floats and counters a launch with `split` K slices meeting in global memory needs (0 when split == 1).
-long long gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split) {
+long long gemm_tc_ws_floats(int m, int n, int ntok, int pair, int split, int tile_rows) {
   if (split <= 1) return 0;
-  const int rows = GT_ROWS * (pair ? 2 : 1);
-  const long long units = static_cast<long long>((n + rows - 1) / rows) * ((m + ntok - 1) / ntok);
+  const int rows = GT_ROWS * (pair ? 2 : 1);   // slots are sized for whole 128-row tiles, whatever the tile height
+  const int own = pair ? rows : tile_rows;
+  const long long units = static_cast<long long>((n + own - 1) / own) * ((m + ntok - 1) / ntok);
   const int mvalid = m < ntok ? m : ntok;
   const int T = gt_owner_block((mvalid + GT_SUB - 1) / GT_SUB * GT_SUB, split);
   return units * split * (split - 1) * rows * T;
 }
-int gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split) {
+int gemm_tc_cnt_ints(int m, int n, int ntok, int pair, int split, int tile_rows) {
   if (split <= 1) return 0;
-  const int rows = GT_ROWS * (pair ? 2 : 1);
-  return 2 * ((n + rows - 1) / rows) * ((m + ntok - 1) / ntok);
+  const int own = pair ? 2 * GT_ROWS : tile_rows;
+  return 2 * ((n + own - 1) / own) * ((m + ntok - 1) / ntok);
 }
 
 // Negative = argument error, positive = cudaError_t, 0 = launched.
 int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m, int n,
-                     int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups,
-                     const PeerSync* peers, cudaStream_t stream) {
+                     int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups, int tile_rows,
+                     int katoms, const PeerSync* peers, cudaStream_t stream) {
   PeerSync ps = {};
   if (peers && peers->world > 1) {
     ps = *peers;
@@ -569,27 +593,29 @@ int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, fl
   if (k % 8 != 0) return -2;
   const int chunks = (k + GT_BK - 1) / GT_BK;
   if (cluster < 1 || cluster > GT_MAX_CLUSTER || split < 1 || split > 64 || (cluster > 1 && split > 1)) return -3;
-  if (cluster * split > chunks || chunks > 65535) return -3;
+  if (katoms < 1 || katoms > GT_MAX_KATOMS) return -12;
+  if (cluster * split > (chunks + katoms - 1) / katoms || chunks > 65535) return -3;
   if (split > 1) {
     if (!ws || !cnt || (reinterpret_cast<uintptr_t>(ws) & 15)) return -4;
     // Slices wait for one another: every CTA of the grid has to be resident at once, one per SM.
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       return -1;
-    const int rows = GT_ROWS * (pair ? 2 : 1);
+    const int rows = pair ? 2 * GT_ROWS : tile_rows;
     if (static_cast<long long>((n + rows - 1) / rows) * split * ((m + ntok - 1) / ntok) > sms) return -10;
   }
+  if (tile_rows < 8 || tile_rows > GT_ROWS || tile_rows % 8 || (pair && tile_rows != GT_ROWS)) return -11;
   if (stages < 1 || stages > GT_MAX_STAGES) return -5;
   if (ld_out < n + ps.col0) return -6;
   if (ntok < 16 || ntok > 256 || ntok % 16) return -7;
   if (warpgroups < 1 || warpgroups > GT_MAX_THREADS / 128) return -9;
   cudaError_t e;
   if (ps.world > 1)
-    e = pair ? gt_launch<true, true>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, ld_out, ps, stream)
-             : gt_launch<false, true>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, ld_out, ps, stream);
+    e = pair ? gt_launch<true, true>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, tile_rows, katoms, ld_out, ps, stream)
+             : gt_launch<false, true>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, tile_rows, katoms, ld_out, ps, stream);
   else
-    e = pair ? gt_launch<true, false>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, ld_out, ps, stream)
-             : gt_launch<false, false>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, ld_out, ps, stream);
+    e = pair ? gt_launch<true, false>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, tile_rows, katoms, ld_out, ps, stream)
+             : gt_launch<false, false>(tw, tx, out, ws, cnt, status, m, n, chunks, ntok, cluster, split, stages, warpgroups, tile_rows, katoms, ld_out, ps, stream);
   return static_cast<int>(e);
 }
 

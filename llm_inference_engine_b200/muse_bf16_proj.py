@@ -139,16 +139,16 @@ def check_status(state) -> None:
         raise _capi.MuseError(f"a kernel reported a timed-out wait: status bits {word:#x} (see MUSE_ST_* in muse_proj.h)")
 
 
-def _weight_maps(state, layer: str, n: int):
-    """TMA maps of W[:n] (hi and lo for FP32 layers), encoded once per (layer, n)."""
-    key = (layer, n)
+def _weight_maps(state, layer: str, n: int, box_rows: int = 128):
+    """TMA maps of W[:n] (hi and lo for FP32 layers) delivering boxes of `box_rows` rows, encoded once per key."""
+    key = (layer, n, box_rows)
     maps = state["_tmaps"].get(key)
     if maps is None:
         if layer in FP32_LAYERS:
             srcs = (state[f"_{layer}_hi"], state[f"_{layer}_lo"])
         else:
             srcs = (state[layer],)
-        maps = tuple(_capi.TensorMap.for_matrix(t.data_ptr(), n, t.shape[1], t.stride(0) * 2, 128) for t in srcs)
+        maps = tuple(_capi.TensorMap.for_matrix(t.data_ptr(), n, t.shape[1], t.stride(0) * 2, box_rows) for t in srcs)
         state["_tmaps"][key] = maps
     return maps
 
@@ -171,9 +171,14 @@ def plan_for(state, layer: str, m: int, n: int, k: int, fused: bool = False) -> 
     elif ov is None and m <= FEWTOK_BUCKETS[-1]:
         few = fewtok_plan(m, n, k, f32, dev)
     gemm = None
-    if few is None and not f32 and (ov is None or "pair" in ov) and (m >= GEMM_MIN_TOKENS or ov):
+    from .plan import GEMM_BUCKETS, TUNED_GEMM   # fewer tokens take this kernel only where the table has measured it
+
+    tabled = m < GEMM_MIN_TOKENS and any((n, k, b) in TUNED_GEMM for b in GEMM_BUCKETS if -(-m // 16) * 16 <= b < GEMM_MIN_TOKENS)
+    if few is None and not f32 and (ov is None or "pair" in ov) and (m >= GEMM_MIN_TOKENS or ov or tabled):
         lib = _capi.load()
-        fit = lambda ntok, pair, stages, cluster, m_, wgs: lib.muse_gemm_tc_max_clusters(ntok, int(pair), stages, cluster, m_, wgs)
+        fit = lambda ntok, pair, stages, cluster, m_, wgs: lib.muse_gemm_tc_max_clusters(ntok, int(pair), stages, cluster, m_, wgs, 128, 1)
+        if fused and tabled:
+            tabled = False   # the table holds whole-weight shapes; a rank's slice is planned by the rules
         gemm = gemm_plan(m, n, k, dev, max_clusters=fit, ws_floats_cap=state["_ws_floats"], cnt_cap=CNT_INTS, **(ov or {}))
     if few is not None:
         plan = few
@@ -275,15 +280,15 @@ def _launch(state, layer: str, plan, m: int, n: int, k: int, x_ptr: int, ld_x: i
         _capi.check(lib.muse_gemv1(w.data_ptr(), x_ptr, out_ptr, n, k, int(f32), plan.wpr, plan.unroll,
                                    int(plan.persistent), status, _peer_ptr(peers), stream), f"muse_gemv1({layer}, n={n}, k={k})")
         return
-    maps = _weight_maps(state, layer, n)
+    maps = _weight_maps(state, layer, n, plan.tile_rows if isinstance(plan, GemmPlan) and not plan.pair else 128)
     if isinstance(plan, GemmPlan):
         ws_ptr = cnt_ptr = None
         if plan.split > 1:
             ws, cnt = _stream_workspace(state, device)
             ws_ptr, cnt_ptr = ws.data_ptr(), cnt.data_ptr()
         _capi.check(lib.muse_gemm_tc(maps[0].ptr, x_ptr, out_ptr, ws_ptr, cnt_ptr, status, m, n, k, ld_x, ld_out, plan.ntok,
-                                     int(plan.pair), plan.cluster, plan.split, plan.stages, plan.warpgroups, _peer_ptr(peers),
-                                     stream),
+                                     int(plan.pair), plan.cluster, plan.split, plan.stages, plan.warpgroups, plan.tile_rows,
+                                     plan.k_atoms, _peer_ptr(peers), stream),
                     f"muse_gemm_tc({layer}, m={m}, n={n}, k={k}, {plan})")
         return
     ws_ptr = cnt_ptr = None

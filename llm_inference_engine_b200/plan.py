@@ -69,26 +69,29 @@ class GemmPlan:
     split: int      # K slices as independent CTAs, reduced through the global workspace (one of the two is 1)
     stages: int     # shared-memory pipeline depth
     warpgroups: int = 4   # CTA size / 128 threads; all of them work in the epilogue
+    tile_rows: int = 128  # weight rows per CTA without `pair`: a multiple of 8; short tiles fill the SMs without a K split
+    k_atoms: int = 1      # 64-wide pieces of K per pipeline stage
 
     @property
     def slices(self) -> int:
         return self.cluster * self.split
 
 
-GEMM_MAX_STAGES = 8
+GEMM_MAX_STAGES = 12
 GEMM_MAX_SPLIT = 64
 GEMM_SUB = 16                 # owner blocks of the K-slice reduction are multiples of this many tokens
 GEMM_MIN_SMEM = 116 * 1024    # one CTA per SM (mirrors the C side)
 GEMM_MIN_TOKENS = 33          # below: the register-MMA walk and muse_skinny_tc
 GEMM_WARPGROUPS = 4
-GEMM_BUCKETS = (48, 64, 128, 256)
+GEMM_BUCKETS = (32, 48, 64, 128, 256)
 
 
 def _gemm_owner_block(mpad: int, slices: int) -> int:
     return -(-(-(-mpad // slices)) // GEMM_SUB) * GEMM_SUB
 
 
-def gemm_smem_bytes(ntok: int, pair: bool, stages: int, cluster: int, m: int, warpgroups: int = GEMM_WARPGROUPS) -> int:
+def gemm_smem_bytes(ntok: int, pair: bool, stages: int, cluster: int, m: int, warpgroups: int = GEMM_WARPGROUPS,
+                    tile_rows: int = TILE_ROWS, k_atoms: int = 1) -> int:
     """Dynamic shared memory of a muse_gemm_tc launch (mirrors muse_gemm_tc_smem_bytes); `cluster` = the slices
     that meet in distributed shared memory (slices that meet in the global workspace need no receive area)."""
     rows = TILE_ROWS * (2 if pair else 1)
@@ -96,16 +99,17 @@ def gemm_smem_bytes(ntok: int, pair: bool, stages: int, cluster: int, m: int, wa
     t = _gemm_owner_block(mpad, cluster) if cluster > 1 else mpad
     rx = (cluster - 1) * rows * t * 4 if cluster > 1 else 0
     after = rx + warpgroups * GEMM_SUB * rows * 4
-    ring = stages * (TILE_ROWS * BK * 2 * (2 if pair else 1) + ntok * BK * 2)
+    own = 2 * TILE_ROWS if pair else tile_rows
+    ring = stages * k_atoms * (own * BK * 2 + ntok * BK * 2) + (0 if pair else (TILE_ROWS - tile_rows) * BK * 2)
     return max(max(ring, after) + 1024, GEMM_MIN_SMEM)
 
 
-def gemm_ws_floats(m: int, n: int, ntok: int, pair: bool, split: int) -> int:
+def gemm_ws_floats(m: int, n: int, ntok: int, pair: bool, split: int, tile_rows: int = TILE_ROWS) -> int:
     """Workspace floats of a launch whose `split` slices meet in global memory (mirrors muse_gemm_tc_ws_floats)."""
     if split <= 1:
         return 0
     rows = TILE_ROWS * (2 if pair else 1)
-    units = -(-n // rows) * -(-m // ntok)
+    units = -(-n // (rows if pair else tile_rows)) * -(-m // ntok)
     mpad = -(-min(m, ntok) // GEMM_SUB) * GEMM_SUB
     return units * split * (split - 1) * rows * _gemm_owner_block(mpad, split)
 
@@ -118,7 +122,8 @@ def gemm_ntok(m: int) -> int:
 
 def gemm_plan(m: int, n: int, k: int, dev: DeviceFacts = DeviceFacts(), max_clusters=None, ws_floats_cap: int = 0,
               cnt_cap: int = 0, ntok: int | None = None, pair: bool | None = None, cluster: int | None = None,
-              split: int | None = None, stages: int | None = None) -> GemmPlan | None:
+              split: int | None = None, stages: int | None = None, tile_rows: int | None = None,
+              k_atoms: int | None = None) -> GemmPlan | None:
     """(Row units x K slices x token tiles) CTAs filling the SMs in one wave, one CTA per SM.
 
     Shapes that were swept on a B200 take their measured best (TUNED_GEMM). Otherwise one weight tile per CTA
@@ -129,7 +134,8 @@ def gemm_plan(m: int, n: int, k: int, dev: DeviceFacts = DeviceFacts(), max_clus
     cluster / split / stages override (tuning sweeps). None: the shape cannot run here."""
     if k % 8 != 0 or m < 1:
         return None
-    forced = ntok is not None or pair is not None or cluster is not None or split is not None
+    forced = (ntok is not None or pair is not None or cluster is not None or split is not None or tile_rows is not None
+              or k_atoms is not None)
     if ntok is None:
         ntok = gemm_ntok(m)
     if ntok % 16 or not 16 <= ntok <= 256:
@@ -143,28 +149,39 @@ def gemm_plan(m: int, n: int, k: int, dev: DeviceFacts = DeviceFacts(), max_clus
             if tok_tiles == 1 else None
         if tuned:
             pair, cluster, split = tuned[0], tuned[1], tuned[2]
+            tile_rows, k_atoms = (tuned[4], tuned[5]) if len(tuned) > 4 else (TILE_ROWS, 1)
             if stages is None:
                 stages = tuned[3]
-            units = -(-n // (TILE_ROWS * (2 if pair else 1)))
-            if split > 1 and (units * split > dev.sms or gemm_ws_floats(m, n, ntok, pair, split) > ws_floats_cap
+            units = -(-n // (2 * TILE_ROWS if pair else tile_rows))
+            if split > 1 and (units * split > dev.sms or gemm_ws_floats(m, n, ntok, pair, split, tile_rows) > ws_floats_cap
                               or 2 * units > cnt_cap):
-                pair = cluster = split = None   # the workspace route is closed here: plan a cluster instead
+                pair = cluster = split = tile_rows = k_atoms = None   # the workspace route is closed here: plan a cluster instead
             elif cluster > 1 and (units * cluster > dev.sms or (
                     max_clusters is not None and max_clusters(ntok, pair, stages, cluster, m, GEMM_WARPGROUPS) < units)):
-                pair = cluster = split = None   # this device does not hold the measured launch in one wave
+                pair = cluster = split = tile_rows = k_atoms = None   # this device does not hold the measured launch in one wave
+            elif units > dev.sms and tile_rows != TILE_ROWS:
+                tile_rows = k_atoms = None   # short tiles are sized for one wave on the device they were measured on
+
+    if tile_rows is None:
+        tile_rows = TILE_ROWS
+    if k_atoms is None:
+        k_atoms = 1
+    if tile_rows % 8 or not 8 <= tile_rows <= TILE_ROWS or not 1 <= k_atoms <= 8:
+        raise ValueError(f"tile_rows={tile_rows} (a multiple of 8 up to 128), k_atoms={k_atoms} (1..8)")
+    steps = -(-chunks // k_atoms)   # K slices are whole pipeline steps
 
     def deepest(pr: bool, cl: int) -> int:
         best = 0
         for st in range(1, GEMM_MAX_STAGES + 1):
-            if gemm_smem_bytes(ntok, pr, st, cl, m) <= limit:
+            if gemm_smem_bytes(ntok, pr, st, cl, m, GEMM_WARPGROUPS, TILE_ROWS if pr else tile_rows, k_atoms) <= limit:
                 best = st
         return best
 
     def cluster_for(pr: bool) -> int:
         """About a hundred CTAs (measured on the per-GPU shard shapes: beyond that the wider reduction costs more
         than the idle SMs), at least four chunks of K per slice, and no more clusters than the device holds."""
-        units = -(-n // (TILE_ROWS * (2 if pr else 1))) * tok_tiles
-        cl = max(1, min(100 // units, 12, chunks // 4, dev.sms // units))
+        units = -(-n // (TILE_ROWS * 2 if pr else tile_rows)) * tok_tiles
+        cl = max(1, min(100 // max(units, 1), 12, steps // 4, dev.sms // max(units, 1)))
         while cl > 1 and (deepest(pr, cl) < 2 or (max_clusters is not None and
                                                   max_clusters(ntok, pr, min(deepest(pr, cl), 4), cl, m, GEMM_WARPGROUPS) < units)):
             cl -= 1
@@ -177,40 +194,44 @@ def gemm_plan(m: int, n: int, k: int, dev: DeviceFacts = DeviceFacts(), max_clus
         if cluster is None and ntok > 128 and tok_tiles == 1:
             # Wide token tiles: the slices of a tile meet in the workspace (no GPC packing, so every SM can
             # take one), as long as the workspace holds them.
-            units = -(-n // (TILE_ROWS * (2 if pair else 1)))
-            want = min(dev.sms // units, chunks // 6 if chunks >= 48 else chunks // 4)
-            while want > 1 and (gemm_ws_floats(m, n, ntok, pair, want) > ws_floats_cap or 2 * units > cnt_cap):
+            units = -(-n // (TILE_ROWS * 2 if pair else tile_rows))
+            want = min(dev.sms // units, steps // 6 if steps >= 48 else steps // 4)
+            while want > 1 and (gemm_ws_floats(m, n, ntok, pair, want, tile_rows) > ws_floats_cap or 2 * units > cnt_cap):
                 want -= 1
             split = max(1, want)
     if cluster is None:
         cluster = 1 if split > 1 else cluster_for(pair)
-    cluster = max(1, min(cluster, MAX_CLUSTER, chunks))
-    split = max(1, min(split, GEMM_MAX_SPLIT, chunks))
+    if pair:
+        tile_rows = TILE_ROWS
+    cluster = max(1, min(cluster, MAX_CLUSTER, steps))
+    split = max(1, min(split, GEMM_MAX_SPLIT, steps))
     if cluster > 1 and split > 1:
         raise ValueError("muse_gemm_tc reduces its K slices either in a cluster or through the workspace, not both")
     most = deepest(pair, cluster)
     if most < 1:
         return None
-    longest = -(-chunks // (cluster * split))
+    longest = -(-steps // (cluster * split))
     stages = max(1, min(stages if stages is not None else 6, most, longest))
-    return GemmPlan(ntok=ntok, pair=bool(pair), cluster=cluster, split=split, stages=stages)
+    return GemmPlan(ntok=ntok, pair=bool(pair), cluster=cluster, split=split, stages=stages, tile_rows=tile_rows, k_atoms=k_atoms)
 
 
-# Measured on B200 (CUDA-graph replay, cold L2, in-stream): (n, k, token bucket) -> (pair, cluster, split, stages).
-# The figure after the slash is what the shape took before this kernel (muse_skinny_tc, or the register-MMA walk).
-TUNED_GEMM: dict[tuple[int, int, int], tuple[bool, int, int, int]] = {
-    (12288, 4096, 48): (True, 2, 1, 4),     # qkv_gate 23.7 us
-    (12288, 4096, 64): (True, 2, 1, 4),     # 23.9 / 26.5
-    (12288, 4096, 128): (True, 2, 1, 4),    # 25.4 / 25.6
+# Measured on B200 (CUDA-graph replay, cold L2, in-stream): (n, k, token bucket) -> (pair, cluster, split, stages[,
+# tile_rows, k_atoms]). The figure after the slash is what the shape took before this kernel (muse_skinny_tc, or the
+# register-MMA walk).
+TUNED_GEMM: dict[tuple[int, int, int], tuple] = {
+    (12288, 4096, 32): (False, 1, 1, 3, 88, 4),   # qkv_gate 21.7 us / 22.4: 140 short tiles, no K split
+    (12288, 4096, 48): (False, 1, 1, 4, 128, 2),  # 23.0
+    (12288, 4096, 64): (False, 1, 1, 4, 128, 2),  # 23.0 / 26.5
+    (12288, 4096, 128): (False, 1, 1, 3, 128, 2),  # 24.5 / 25.6 (pairs in clusters of two: 25.4)
     (12288, 4096, 256): (False, 1, 1, 4),   # 30.4 / 31.1
-    (4096, 4096, 48): (False, 4, 1, 6),     # o 12.2
-    (4096, 4096, 64): (False, 4, 1, 6),     # 12.3 / 15.5
+    (4096, 4096, 48): (False, 4, 1, 4, 128, 2),     # o 12.0
+    (4096, 4096, 64): (False, 4, 1, 4, 128, 2),     # 12.0 / 15.5
     (4096, 4096, 128): (False, 4, 1, 6),    # 13.9 / 18.5
     (4096, 4096, 256): (False, 1, 4, 4),    # 16.5 / 23.9
-    (1024, 4096, 128): (False, 8, 1, 4),    # pooler 10.2 / 11.4
+    (1024, 4096, 128): (False, 8, 1, 3, 128, 2),    # pooler 10.0 / 11.4
     (1024, 4096, 256): (False, 1, 16, 4),   # 12.6 / 17.3
-    (4096, 1024, 64): (False, 4, 1, 4),     # unpooler 8.0 / 9.1
-    (4096, 1024, 128): (False, 3, 1, 4),    # 8.95 / 9.35
+    (4096, 1024, 64): (False, 4, 1, 2, 128, 2),     # unpooler 7.8 / 9.1
+    (4096, 1024, 128): (False, 2, 1, 3, 128, 2),    # 8.7 / 9.35
     (4096, 1024, 256): (False, 2, 1, 4),    # 11.0 / 10.6
 }
 

@@ -55,12 +55,16 @@ def test_pure_host_entry_points_without_a_gpu():
     assert lib.muse_skinny_tiles(0, 1, 16) < 0
     for m, k, warps in ((2, 4096, 16), (8, 1024, 32), (9, 4096, 32), (16, 2048, 16)):
         assert lib.muse_fewtok_smem_bytes(m, k, warps) == plan.fewtok_smem_bytes(m, k, warps)
-    for ntok, pair, stages, cluster, m, wgs in ((16, 0, 1, 1, 5, 1), (64, 1, 3, 4, 64, 4), (256, 1, 3, 2, 256, 4), (112, 0, 4, 9, 100, 2),
-                                                (256, 0, 4, 16, 1000, 4), (160, 1, 8, 3, 300, 3)):
-        assert lib.muse_gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, wgs) == plan.gemm_smem_bytes(ntok, bool(pair), stages, cluster, m, wgs)
-    for m, n, ntok, pair, split in ((256, 12288, 256, 1, 3), (100, 1000, 112, 1, 3), (256, 1024, 256, 0, 16), (40, 700, 48, 0, 20),
-                                    (64, 512, 64, 0, 1), (1000, 4096, 256, 1, 2)):
-        assert lib.muse_gemm_tc_ws_floats(m, n, ntok, pair, split) == plan.gemm_ws_floats(m, n, ntok, bool(pair), split)
+    for ntok, pair, stages, cluster, m, wgs, rows, atoms in ((16, 0, 1, 1, 5, 1, 128, 1), (64, 1, 3, 4, 64, 4, 128, 1), (256, 1, 3, 2, 256, 4, 128, 1),
+                                                             (112, 0, 4, 9, 100, 2, 128, 1), (256, 0, 4, 16, 1000, 4, 128, 1),
+                                                             (160, 1, 8, 3, 300, 3, 128, 1), (32, 0, 12, 1, 32, 4, 88, 1), (16, 0, 10, 1, 9, 2, 8, 1),
+                                                             (64, 0, 8, 2, 64, 4, 56, 1), (32, 0, 3, 1, 32, 4, 88, 4), (128, 0, 3, 4, 128, 4, 128, 2)):
+        assert (lib.muse_gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, wgs, rows, atoms)
+                == plan.gemm_smem_bytes(ntok, bool(pair), stages, cluster, m, wgs, rows, atoms))
+    for m, n, ntok, pair, split, rows in ((256, 12288, 256, 1, 3, 128), (100, 1000, 112, 1, 3, 128), (256, 1024, 256, 0, 16, 128),
+                                          (40, 700, 48, 0, 20, 128), (64, 512, 64, 0, 1, 128), (1000, 4096, 256, 1, 2, 128),
+                                          (48, 2304, 48, 0, 2, 40)):
+        assert lib.muse_gemm_tc_ws_floats(m, n, ntok, pair, split, rows) == plan.gemm_ws_floats(m, n, ntok, bool(pair), split, rows)
     for ntok in plan.NTOK_CHOICES:
         for hilo in (False, True):
             assert lib.muse_skinny_stage_bytes(ntok, int(hilo)) == plan.stage_bytes(ntok, hilo)

@@ -234,13 +234,19 @@ def test_rejects_what_it_cannot_run(proj, dev, target_setup):
         proj.kernel_fn({"x": torch.zeros((1, 4096), dtype=torch.bfloat16, device=dev), "config": dict(cfg, n=2048)}, state)
 
 
-GEMM_CASES = [  # (m, n, k, ntok, pair, cluster, split, stages, warpgroups)
+GEMM_CASES = [  # (m, n, k, ntok, pair, cluster, split, stages, warpgroups[, tile_rows[, k_atoms]])
     (16, 128, 64, 16, False, 1, 1, 1, 1), (16, 256, 128, 16, True, 1, 1, 2, 4), (64, 512, 1024, 64, True, 4, 1, 2, 4),
     (100, 1000, 2048, 112, True, 3, 1, 3, 2), (256, 1024, 4096, 256, False, 4, 1, 4, 4), (128, 12288, 4096, 128, True, 2, 1, 4, 4),
     (256, 12288, 4096, 256, False, 1, 1, 4, 4), (128, 4096, 4096, 128, False, 4, 1, 6, 4), (300, 4096, 1024, 160, True, 4, 1, 3, 4),
     (33, 1030, 4096, 48, False, 8, 1, 4, 3), (1000, 777, 512, 256, True, 2, 1, 2, 4),
     (64, 512, 1024, 64, True, 1, 4, 2, 4), (100, 1000, 2048, 112, True, 1, 3, 3, 1), (256, 12288, 4096, 256, True, 1, 3, 3, 4),
     (256, 4096, 4096, 256, False, 1, 4, 4, 4), (256, 1024, 4096, 256, False, 1, 16, 4, 4), (40, 700, 4096, 48, False, 1, 20, 3, 2),
+    # short tiles: every SM takes a slab of rows, no K split
+    (32, 12288, 4096, 32, False, 1, 1, 12, 4, 88), (16, 4096, 4096, 16, False, 1, 1, 10, 2, 32), (5, 1001, 1024, 16, False, 1, 1, 6, 4, 8),
+    (64, 4096, 4096, 64, False, 2, 1, 8, 4, 56), (48, 2304, 8192, 48, False, 1, 2, 6, 4, 40),
+    # several 64-wide K atoms per stage (K = 2080 is 32.5 atoms: the last step is partly past the end of K)
+    (32, 12288, 4096, 32, False, 1, 1, 3, 4, 88, 4), (128, 4096, 4096, 128, False, 4, 1, 3, 4, 128, 2), (100, 1000, 2080, 112, True, 3, 1, 2, 2, 128, 2),
+    (16, 4096, 4096, 16, False, 1, 1, 2, 1, 32, 8), (256, 2048, 4096, 256, False, 1, 3, 2, 4, 128, 2),
 ]
 
 
@@ -253,23 +259,25 @@ def test_gemm_entry_point_matches_oracle_and_is_bit_stable(dev, case):
     from llm_inference_engine_b200 import _capi
     from llm_inference_engine_b200._capi import TensorMap
 
-    m, n, k, ntok, pair, cluster, split, stages, wgs = case
+    m, n, k, ntok, pair, cluster, split, stages, wgs = case[:9]
+    tile_rows = case[9] if len(case) > 9 else 128
+    k_atoms = case[10] if len(case) > 10 else 1
     lib = _capi.load()
     g = torch.Generator(device=dev).manual_seed(m * 13 + n)
     w = (torch.randn((n, k), generator=g, device=dev) * 0.02).to(torch.bfloat16)
     x = torch.randn((m, k + 24), generator=g, device=dev).to(torch.bfloat16)[:, :k]
     ref = x.double() @ w.double().T
-    tm = TensorMap.for_matrix(w.data_ptr(), n, k, k * 2, 128)
-    ws = torch.full((max(1, lib.muse_gemm_tc_ws_floats(m, n, ntok, int(pair), split)),), float("nan"), device=dev)
-    cnt = torch.zeros(max(1, lib.muse_gemm_tc_cnt_ints(m, n, ntok, int(pair), split)), device=dev, dtype=torch.int32)
+    tm = TensorMap.for_matrix(w.data_ptr(), n, k, k * 2, tile_rows)
+    ws = torch.full((max(1, lib.muse_gemm_tc_ws_floats(m, n, ntok, int(pair), split, tile_rows)),), float("nan"), device=dev)
+    cnt = torch.zeros(max(1, lib.muse_gemm_tc_cnt_ints(m, n, ntok, int(pair), split, tile_rows)), device=dev, dtype=torch.int32)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
-    if cluster > 1 and lib.muse_gemm_tc_max_clusters(ntok, int(pair), stages, cluster, m, wgs) < 1:
+    if cluster > 1 and lib.muse_gemm_tc_max_clusters(ntok, int(pair), stages, cluster, m, wgs, tile_rows, k_atoms) < 1:
         pytest.skip("this cluster shape does not fit the device")
     outs = []
     for _ in range(3):
         out = torch.full((m, n + 8), 3.0, device=dev, dtype=torch.bfloat16)
         _capi.check(lib.muse_gemm_tc(tm.ptr, x.data_ptr(), out.data_ptr(), ws.data_ptr(), cnt.data_ptr(), status.data_ptr(), m, n, k,
-                                     x.stride(0), out.stride(0), ntok, int(pair), cluster, split, stages, wgs, None,
+                                     x.stride(0), out.stride(0), ntok, int(pair), cluster, split, stages, wgs, tile_rows, k_atoms, None,
                                      torch.cuda.current_stream(dev).cuda_stream), "muse_gemm_tc")
         torch.cuda.synchronize(dev)
         outs.append(out)
@@ -294,15 +302,17 @@ def test_gemm_rejections(dev):
     cnt = torch.zeros(64, device=dev, dtype=torch.int32)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
     tm = TensorMap.for_matrix(w.data_ptr(), 4096, 1024, 2048, 128)
-    call = lambda ntok=64, pair=0, cluster=1, split=1, stages=2, wgs=4, ws_=ws: lib.muse_gemm_tc(
+    call = lambda ntok=64, pair=0, cluster=1, split=1, stages=2, wgs=4, ws_=ws, rows=128, atoms=1: lib.muse_gemm_tc(
         tm.ptr, x.data_ptr(), out.data_ptr(), None if ws_ is None else ws_.data_ptr(), cnt.data_ptr(), status.data_ptr(), 64, 4096,
-        1024, 1024, 4096, ntok, pair, cluster, split, stages, wgs, None, None)
+        1024, 1024, 4096, ntok, pair, cluster, split, stages, wgs, rows, atoms, None, None)
     assert call(ntok=40) == -7                      # tokens per tile: multiples of 16
     assert call(cluster=2, split=2) == -3           # slices meet in a cluster or in the workspace, not both
     assert call(cluster=17) == -3 and call(split=17) == -3   # more slices than 64-wide chunks of K
     assert call(split=4, ws_=None) == -4            # a workspace split needs the workspace
     assert call(split=8) == -10                     # 32 units x 8 slices cannot all be resident at once
-    assert call(stages=9) == -5 and call(wgs=5) == -9
+    assert call(stages=13) == -5 and call(wgs=5) == -9
+    assert call(atoms=0) == -12 and call(atoms=9) == -12 and call(cluster=5, atoms=4) == -3   # 16 atoms of K in steps of 4: four slices at most
+    assert call(rows=100) == -11 and call(rows=136) == -11 and call(pair=1, rows=64) == -11   # multiples of 8 up to 128; pairs are whole tiles
     torch.cuda.synchronize(dev)
     assert int(status.item()) == 0 and float(out.abs().max()) == 0.0
 

@@ -93,14 +93,15 @@ def test_gemm_plan_respects_every_kernel_limit(name, m):
     p = plan.gemm_plan(m, n, k, dev, ws_floats_cap=3 * 12288 * 256, cnt_cap=4096)
     chunks = -(-k // plan.BK)
     assert p.ntok % 16 == 0 and 16 <= p.ntok <= 256 and -(-m // p.ntok) == -(-m // 256)   # as few token tiles as possible
+    chunks = -(-chunks // p.k_atoms)   # K slices are whole pipeline steps
     assert (p.cluster == 1 or p.split == 1) and 1 <= p.cluster <= plan.MAX_CLUSTER and 1 <= p.slices <= chunks
     assert 1 <= p.stages <= plan.GEMM_MAX_STAGES and 1 <= p.warpgroups <= 4
-    assert plan.gemm_smem_bytes(p.ntok, p.pair, p.stages, p.cluster, m, p.warpgroups) + 512 <= plan.SMEM_PER_CTA_MAX
-    units = -(-n // (256 if p.pair else 128)) * -(-m // p.ntok)
+    assert plan.gemm_smem_bytes(p.ntok, p.pair, p.stages, p.cluster, m, p.warpgroups, p.tile_rows, p.k_atoms) + 512 <= plan.SMEM_PER_CTA_MAX
+    units = -(-n // (256 if p.pair else p.tile_rows)) * -(-m // p.ntok)
     if p.slices > 1:   # one wave, one CTA per SM: K slices wait for one another
         assert units * p.slices <= dev.sms
     if p.split > 1:
-        assert plan.gemm_ws_floats(m, n, p.ntok, p.pair, p.split) <= 3 * 12288 * 256 and 2 * units <= 4096
+        assert plan.gemm_ws_floats(m, n, p.ntok, p.pair, p.split, p.tile_rows) <= 3 * 12288 * 256 and 2 * units <= 4096
     bounds = [s * chunks // p.slices for s in range(p.slices + 1)]
     assert all(b > a for a, b in zip(bounds, bounds[1:]))
 
@@ -121,12 +122,16 @@ def test_gemm_plan_falls_back_to_a_cluster_without_workspace_room():
 
 
 def test_gemm_tuned_entries_are_launchable():
-    for (n, k, bucket), (pair, cluster, split, stages) in plan.TUNED_GEMM.items():
-        assert bucket in plan.GEMM_BUCKETS and (cluster == 1 or split == 1)
+    for (n, k, bucket), tuned in plan.TUNED_GEMM.items():
+        pair, cluster, split, stages = tuned[:4]
+        tile_rows, k_atoms = tuned[4:] if len(tuned) > 4 else (128, 1)
+        assert bucket in plan.GEMM_BUCKETS and (cluster == 1 or split == 1) and tile_rows % 8 == 0 and (not pair or tile_rows == 128)
         p = plan.gemm_plan(bucket, n, k, ws_floats_cap=3 * 12288 * 256, cnt_cap=4096)
-        longest = -(-(-(-k // plan.BK)) // (cluster * split))
-        assert (p.pair, p.cluster, p.split, p.stages) == (pair, cluster, split, min(stages, longest))
-        assert -(-n // (256 if pair else 128)) * cluster * split <= 148
+        steps = -(-(-(-k // plan.BK)) // k_atoms)
+        longest = -(-steps // (cluster * split))
+        assert (p.pair, p.cluster, p.split, p.stages, p.tile_rows, p.k_atoms) == (pair, cluster, split, min(stages, longest), tile_rows, k_atoms)
+        assert -(-n // (256 if pair else tile_rows)) * cluster * split <= 148
+        assert plan.gemm_smem_bytes(p.ntok, pair, p.stages, cluster, bucket, p.warpgroups, tile_rows, k_atoms) + 512 <= plan.SMEM_PER_CTA_MAX
 
 
 def test_fewtok_f32_table_is_consistent():
