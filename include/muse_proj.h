@@ -7,7 +7,10 @@
  * value for an argument it rejects (nothing was launched) or a positive cudaError_t / CUresult.
  * Nothing here allocates device memory or synchronises; launches go to `stream` and can be
  * captured in a CUDA graph. Thread-compatible: concurrent calls are fine as long as they do not
- * share a workspace (ws / cnt), which belongs to one stream at a time.
+ * share a workspace (ws / cnt), which belongs to one stream at a time. The first launch of a kernel
+ * variant on a device sets that variant's function attributes (shared-memory opt-in, cluster size) and
+ * caches a few device facts without locking: make the first call of each shape from one thread (a
+ * warm-up pass, as prepare() of the Python host does) before calling from several.
  *
  * The reference for this path is a Python submission (best_submissions/muse_bf16_proj.py) whose
  * native boundary is a pybind function around gemv1_launch (bf16_proj/gemv1.cu:122-125) plus Triton

@@ -40,7 +40,6 @@ int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int
 cudaError_t skinny_trace_set(unsigned long long* p);
 cudaError_t fewtok_trace_set(unsigned long long* p);
 cudaError_t gemm_trace_set(unsigned long long* p);
-cudaError_t gemm_trace_set_knob(int v);
 #endif
 long long skinny_static_ws_floats();
 int skinny_static_cnt_ints();
@@ -104,7 +103,6 @@ int muse_trace_set(void* device_buffer) {
   if (e == cudaSuccess) e = muse::gemm_trace_set(static_cast<unsigned long long*>(device_buffer));
   return static_cast<int>(e);
 }
-int muse_trace_knob(int v) { return static_cast<int>(muse::gemm_trace_set_knob(v)); }
 #endif
 
 int muse_query(int what) {

@@ -27,15 +27,11 @@ constexpr unsigned long long WAIT_LIMIT_NS = 500ull * 1000ull * 1000ull;  // 0.5
 // pointer (set through muse_trace_set, which only such builds export) to a buffer of 16 unsigned 64-bit
 // slots per CTA; in an ordinary build the base is a compile-time null and every stamp site folds away.
 #ifdef MUSE_TRACE
-static __device__ int g_trace_knob = 0;   // diagnostic builds: timing experiments that give wrong results on purpose
-#define MUSE_TRACE_KNOB() (g_trace_knob)
 static __device__ unsigned long long* g_trace_dev = nullptr;
 #define MUSE_TRACE_BASE() (g_trace_dev)
 #define MUSE_TRACE_SETTER(name) \
-  cudaError_t name(unsigned long long* p) { return cudaMemcpyToSymbol(g_trace_dev, &p, sizeof(p)); } \
-  cudaError_t name##_knob(int v) { return cudaMemcpyToSymbol(g_trace_knob, &v, sizeof(v)); }
+  cudaError_t name(unsigned long long* p) { return cudaMemcpyToSymbol(g_trace_dev, &p, sizeof(p)); }
 #else
-#define MUSE_TRACE_KNOB() (0)
 #define MUSE_TRACE_BASE() (static_cast<unsigned long long*>(nullptr))
 #define MUSE_TRACE_SETTER(name)
 #endif

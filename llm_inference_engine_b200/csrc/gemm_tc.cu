@@ -1,29 +1,32 @@
 // out[m, n] = x[m, K] . W[n, K]^T (BF16 in, FP32 accumulate, BF16 out) for many tokens: the m > 32 GEMM
-// of the path, which the reference hands to cuBLAS (best_submissions/muse_bf16_proj.py:390).
-//
-// At 64..256 tokens these products sit at or below the ridge of a B200 (m flop per weight byte against
-// ~220), and what limits a swap-AB kernel is not HBM or the tensor pipe but the traffic from L2 into
-// shared memory: every 128-row weight tile wants the whole x tile beside it, and x is as large as the
-// weight tile (256 tokens: twice as large). This kernel halves that traffic and keeps every SM busy:
-//   * a CTA owns a PAIR of 128-row weight tiles and brings each 64-wide chunk of x in once for both:
-//     two tcgen05.mma (M = 128, N = tokens, K = 16) per K step into two FP32 accumulators that share
-//     the SM's tensor memory (2 x 256 columns at 256 tokens);
-//   * the token tile is as wide as the call (N = m rounded up to 16, one tile up to 256 tokens), so W
-//     leaves HBM once and is never re-read through L2;
-//   * K is split across a thread-block cluster sized so that (row pairs x cluster) fills the 148 SMs in
-//     one wave with one CTA per SM; the partial tiles meet inside the cluster: tokens are dealt to the
-//     cluster's CTAs in blocks, every CTA pushes the blocks it does not own straight from tensor memory
-//     into the owner's shared memory (16-byte st.shared::cluster, a warp writing 512 contiguous bytes),
-//     the owner adds its own block and the received ones in a fixed order (bit-reproducible) and stores
-//     16-byte vectors. The receive area overlays the shared-memory ring, so a deep ring and a wide
-//     reduction both fit; one cluster barrier after the main loop says that the rings are idle, a
-//     second one that the pushes have landed.
-// One warp-specialised CTA of 128 threads: thread 0 = TMA producer (cp.async.bulk.tensor.2d, weights
-// with an evict-first L2 policy, x evict-last; no cluster multicast), warp 1 lane 0 = MMA issuer, all
-// four warps = epilogue (thread = weight row = TMEM lane). Without PAIR the CTA owns one tile: small
-// weights want more CTAs rather than less x traffic. Every wait is bounded and reports through the
-// status word. Column-parallel (PEERS) the output goes to every rank's gathered buffer with the flag
-// exchange of common.cuh.
+// of the path, which the reference hands to cuBLAS (best_submissions/muse_bf16_proj.py:390). Swap-AB like
+// muse_skinny_tc (the weight tile is the MMA's M = 128, the tokens its N), TMA -> shared-memory ring ->
+// tcgen05.mma -> tensor memory, but shaped for what bounds these sizes:
+//   * the token tile is as wide as the call (N = m rounded up to 16, a run-time value; one tile up to 256 tokens),
+//     so W leaves HBM once and is never re-read through L2;
+//   * traffic from L2 into shared memory, not HBM or the tensor pipe, limits a swap-AB kernel at 64..256
+//     tokens (every 128-row weight tile wants the whole x tile beside it). With PAIR a CTA owns two 128-row
+//     tiles and brings each x chunk in once for both: two MMAs per K step into two FP32 accumulators that share
+//     the SM's tensor memory (2 x 256 columns at 256 tokens). Without PAIR it owns one tile (small weights want
+//     more CTAs rather than less x traffic), which may be SHORT (tile_rows < 128: a weight of any height then
+//     fills the SMs in one wave without any K split; used at few tokens, where the tensor pipe has time to spare);
+//   * a pipeline stage holds k_atoms 64-wide pieces of K (each its own swizzled box), so that one step asks DRAM
+//     for k_atoms x 128 contiguous bytes of every weight row;
+//   * K slices fill the SMs in one wave, one CTA per SM, and meet in one of two ways, both with a fixed
+//     summation order (bit-reproducible). Cluster: tokens are dealt to the cluster's CTAs in blocks of 16, every
+//     CTA pushes the blocks it does not own from tensor memory into the owner's shared memory (16-byte
+//     st.shared::cluster, a warp writing 512 contiguous bytes); the receive area overlays the idle ring: one
+//     cluster barrier after the main loop says the rings are idle, a second one that the pushes have landed.
+//     Workspace: no cluster; every slice writes the blocks it does not own to its slot of a global workspace
+//     (plain 16-byte stores that stay in L2), counts itself in on the tile's counter, waits (bounded) for the
+//     others, reads its own block's slots back, and the last slice to finish reading zeroes the counters;
+//   * 128 .. 512 threads: thread 0 = TMA producer (cp.async.bulk.tensor.2d, weights with an evict-first L2
+//     policy, x evict-last; no cluster multicast), warp 1 lane 0 = MMA issuer, everybody else parked on a CTA
+//     barrier during the main loop; then every warpgroup reads accumulators out (warp w touches TMEM lanes
+//     32 (w % 4) ..), 16 tokens per warpgroup and step: TMEM (+ received slots) -> shared-memory transpose ->
+//     16-byte global stores.
+// Every wait is bounded and reports through the status word. Column-parallel (PEERS) the output goes to every
+// rank's gathered buffer with the flag exchange of common.cuh.
 #include "common.cuh"
 
 namespace muse {

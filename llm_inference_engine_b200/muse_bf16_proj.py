@@ -387,6 +387,7 @@ FETCH_X_BY_KERNEL = True
 STORE_OUT_BY_KERNEL = True   # the copy-out of the larger calls by the same small kernel (786 KB: 5 us less than the copy engine)
 FETCH_MAX_TOKENS = 32       # x up to 256 KB: the fetch kernel beats the copy engine at every size measured
 DIRECT_OUT_MAX_TOKENS = 8   # beyond: 16-byte PCIe writes cost more than the copy-out they replace
+DIRECT_OUT_GEMM_MAX_TOKENS = 32   # the many-token GEMM writes 176 contiguous bytes per token and CTA: measured 56 vs 59.5 us at m = 32, no gain at 64
 HOST_GRAPH_SLOTS = 64   # recorded round trips kept per state (oldest dropped first)
 _EMPTY: dict = {}
 
@@ -444,6 +445,10 @@ def kernel_fn_host(data: Inputs, state, out: torch.Tensor | None = None, record:
         # writes the caller's buffer itself while it streams the weights, and the copy-out disappears.
         direct = (isinstance(plan, FewTokPlan) and not f32 and n % 8 == 0 and out.data_ptr() % 16 == 0
                   and m <= DIRECT_OUT_MAX_TOKENS)
+        # The many-token GEMM stores a token's rows of one CTA as neighbouring 16-byte vectors (176 contiguous bytes
+        # per token with 88-row tiles), which the PCIe link takes as large writes.
+        direct = direct or (isinstance(plan, GemmPlan) and n % 8 == 0 and out.data_ptr() % 16 == 0
+                            and m <= DIRECT_OUT_GEMM_MAX_TOKENS)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             rec = torch.cuda.current_stream(w.device).cuda_stream
