@@ -65,8 +65,10 @@ PARITY_CASES = (("qkv_gate", 1), ("qkv_gate", 8), ("qkv_gate", 16), ("qkv_gate",
 # figure the line carries for comparison with `bytes_per_launch`, not something measured in this run.
 NCU_TRAFFIC = {
     "fewtok_xreg<32,4,false> qkv_gate m=8": 104474368,
-    "skinny_tc qkv_gate m=32": 104364800,
-    "skinny_tc qkv_gate m=256": 106700000,
+    "fewtok_xreg<16,8,true> qkv_gate m=16": 104567808,
+    "gemm_tc qkv_gate m=32": 104101632,
+    "gemm_tc qkv_gate m=128": 105473280,
+    "gemm_tc qkv_gate m=256": 109367808,
     "gemv1_rows o m=1": 33578496,
     "skinny_tc router m=128": 5302016,
     "fewtok_xreg_f32<16,8> router m=32": 4471040,
@@ -463,7 +465,8 @@ def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
     feeding the pooler and, up to 8 tokens in FP32, the router. Per token count, one graph per variant over
     rotating cold weight copies: the boundary as a kernel of its own in front of the two projections, and the
     boundary fused into both as their prologue; each with the router after the pooler on one stream and with
-    the router forked to a side stream as the reference's layer does."""
+    the router forked to a side stream as the reference's layer does; and all three as one launch
+    (muse_boundary_pooler_router)."""
     proj = h.proj
     layers = ("pooler", "router")
     copies = 80
@@ -508,6 +511,13 @@ def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
                             torch.cuda.current_stream(h.device).wait_stream(side)
 
                 row[("fused" if fused else "separate") + ("_fork_us" if fork else "_us")] = 1e3 * h.time_graph(fn, steps, warmup) / copies
+
+        def one(keep=[]):
+            keep.clear()
+            for st in states:
+                keep.append(proj.boundary_pooler_router({"stream": stream_in, "attn_out": attn_out}, st, stream1=s1))
+
+        row["one_launch_us"] = 1e3 * h.time_graph(one, steps, warmup) / copies
         rows.append(row)
     for st in states:
         proj.check_status(st)

@@ -218,16 +218,18 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
   if (my_groups > 0) load(w, 0);
   if constexpr (BND) {
     // The first weight loads are in flight; every CTA now rebuilds h for all tokens and takes its fragments from it.
-    extern __shared__ __align__(16) float bnd_s1[];
+    extern __shared__ __align__(16) float bnd_base[];
     __shared__ float bnd_red[NW][BND_TOKENS];
     __shared__ float bnd_inv1[BND_TOKENS], bnd_inv2[BND_TOKENS];
-    boundary_prologue<NW * 32>(bd, m, K, bnd_s1, bnd_red, bnd_inv1, bnd_inv2);
+    __shared__ __align__(8) uint64_t bnd_bar;
+    const BoundarySmem bs = boundary_smem_carve(bnd_base, K, m);
+    if (!boundary_prologue<NW * 32>(bd, m, K, bs, &bnd_bar, bnd_red, bnd_inv1, bnd_inv2, status)) return;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       xr[u] = make_uint4(0u, 0u, 0u, 0u);
       if (g < m && first + u < kblocks) {
         float h[8];
-        boundary_h8(bd, bnd_s1, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
+        boundary_h8(bs, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
         xr[u] = make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
       }
     }
@@ -391,7 +393,7 @@ template <int NW, int U, bool XF32, bool BND = false>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* __restrict__ W, const void* __restrict__ xv,
                                                                   float* __restrict__ out, int m, int N, int K, int ld_x,
                                                                   int ld_out, int tok_split,
-                                                                  const __grid_constant__ BoundaryArgs bd) {
+                                                                  const __grid_constant__ BoundaryArgs bd, int* __restrict__ status) {
   static_assert(!BND || XF32, "the boundary hands the router FP32 activations");
   constexpr int OUTS = 64, TOKS = 8;
   constexpr int SUBS = XF32 && U > 1 ? 2 : 1, PS = U / SUBS;   // weight sub-batches of a group, pieces in each
@@ -431,16 +433,18 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
     lo = *reinterpret_cast<const uint32_t*>(&l);
   };
   if constexpr (BND) {
-    extern __shared__ __align__(16) float bnd_s1[];
+    extern __shared__ __align__(16) float bnd_base[];
     __shared__ float bnd_red[NW][BND_TOKENS];
     __shared__ float bnd_inv1[BND_TOKENS], bnd_inv2[BND_TOKENS];
-    boundary_prologue<NW * 32>(bd, m, K, bnd_s1, bnd_red, bnd_inv1, bnd_inv2);
+    __shared__ __align__(8) uint64_t bnd_bar;
+    const BoundarySmem bs = boundary_smem_carve(bnd_base, K, m);
+    if (!boundary_prologue<NW * 32>(bd, m, K, bs, &bnd_bar, bnd_red, bnd_inv1, bnd_inv2, status)) return;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       xr[u] = xl[XF32 ? u : 0] = make_uint4(0u, 0u, 0u, 0u);
       if (g < m && first + u < kblocks) {
         float h[8];
-        boundary_h8(bd, bnd_s1, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
+        boundary_h8(bs, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
         split(__float_as_uint(h[0]), __float_as_uint(h[1]), xr[u].x, xl[XF32 ? u : 0].x);
         split(__float_as_uint(h[2]), __float_as_uint(h[3]), xr[u].y, xl[XF32 ? u : 0].y);
         split(__float_as_uint(h[4]), __float_as_uint(h[5]), xr[u].z, xl[XF32 ? u : 0].z);
@@ -647,7 +651,7 @@ static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int 
   if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), x, reinterpret_cast<float*>(out), m, N, K,
-                                               ld_x, ld_out, tok_split, BoundaryArgs{});
+                                               ld_x, ld_out, tok_split, BoundaryArgs{}, nullptr);
   return cudaGetLastError();
 }
 
@@ -755,6 +759,140 @@ __global__ void __launch_bounds__(256) attn_boundary_kernel(const __grid_constan
   }
 }
 
+// ---------------------------------------------------------------- boundary + pooler + router in one launch
+//
+// The three kernels the decode layer runs between the `o` projection and the experts (boundary, pooler, and the
+// router on a side stream: best_submissions/muse_decode_layer.py:855-869) as ONE launch for up to 8 tokens: every
+// CTA first issues the weight loads of its first row group, then every CTA rebuilds h (boundary_prologue: bulk
+// copies of the inputs into shared memory, two CTA-wide reductions), and then the first `pooler_ctas` CTAs walk the pooler's BF16 rows with BF16-rounded h while the others walk the
+// router's FP32 rows with FP32 h split to hi + lo (three MMAs per weight half-pair, as the FP32-input mode).
+// One launch and one prologue instead of three launches (or two launches with a prologue each).
+__device__ __forceinline__ void split_hi_lo_pair(uint32_t a_bits, uint32_t b_bits, uint32_t& hi, uint32_t& lo) {
+  const float a = __uint_as_float(a_bits), b = __uint_as_float(b_bits);
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  const float ra = a - __uint_as_float(hi << 16), rb = b - __uint_as_float(hi & 0xffff0000u);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(ra, rb);
+  lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+constexpr int FB_NW = 16, FB_U = 8, FB_NT = FB_NW * 32;   // 512 threads: 16 warps x 8 pieces of 32 elements = K up to 4096
+
+__global__ void __launch_bounds__(FB_NT, 1)
+fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restrict__ Wr, const __grid_constant__ BoundaryArgs bd,
+                      __nv_bfloat16* __restrict__ outp, float* __restrict__ outr, int m, int Np, int Nr, int K, int ld_outp,
+                      int ld_outr, int pooler_ctas, int* __restrict__ status) {
+  extern __shared__ __align__(16) float fb_smem[];
+  __shared__ __align__(16) float red[2][FB_NW][64];
+  __shared__ float bnd_red[FB_NW][BND_TOKENS];
+  __shared__ float inv1[BND_TOKENS], inv2[BND_TOKENS];
+  __shared__ __align__(8) uint64_t bnd_bar;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+  const bool router = static_cast<int>(blockIdx.x) >= pooler_ctas;
+  const int C = router ? static_cast<int>(gridDim.x) - pooler_ctas : pooler_ctas;
+  const int c = router ? static_cast<int>(blockIdx.x) - pooler_ctas : static_cast<int>(blockIdx.x);
+  const int N = router ? Nr : Np;
+  const int kblocks = K >> 5, groups = (N + 7) >> 3;
+  const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
+  const int first = warp * FB_U;
+
+  // ---- first weight loads (BF16: 8 pieces of 16 bytes; FP32: the first 4 of 8 pieces, 32 bytes each)
+  uint4 w[FB_U];
+  auto load_p = [&](int i) {
+    int r = (c + i * C) * 8 + g;
+    r = r < N ? r : N - 1;
+    const uint4* p = reinterpret_cast<const uint4*>(Wp + static_cast<size_t>(r) * K) + q;
+#pragma unroll
+    for (int u = 0; u < FB_U; ++u) w[u] = first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+  };
+  auto load_r = [&](int i, int h) {
+    int r = (c + i * C) * 8 + g;
+    r = r < N ? r : N - 1;
+    const uint4* p = reinterpret_cast<const uint4*>(Wr + static_cast<size_t>(r) * K) + 2 * q;
+#pragma unroll
+    for (int u = 0; u < FB_U / 2; ++u) {
+      const int piece = first + h * (FB_U / 2) + u;
+      const bool ok = piece < kblocks;
+      w[2 * u] = ok ? ldg_stream16(p + piece * 8) : make_uint4(0u, 0u, 0u, 0u);
+      w[2 * u + 1] = ok ? ldg_stream16(p + piece * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  if (my_groups > 0) {
+    if (router) load_r(0, 0);
+    else load_p(0);
+  }
+
+  // ---- the boundary, once, while those loads are in flight
+  const BoundarySmem bs = boundary_smem_carve(fb_smem, K, m);
+  if (!boundary_prologue<FB_NT>(bd, m, K, bs, &bnd_bar, bnd_red, inv1, inv2, status)) return;
+
+  // ---- x fragments from shared memory: BF16 h for the pooler, FP32 h -> hi + lo for the router
+  uint4 xr[FB_U], xl[FB_U];
+#pragma unroll
+  for (int u = 0; u < FB_U; ++u) {
+    xr[u] = xl[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (g < m && first + u < kblocks) {
+      float h[8];
+      boundary_h8(bs, inv2, K, g, (first + u) * 32 + q * 8, h);
+      if (router) {
+        split_hi_lo_pair(__float_as_uint(h[0]), __float_as_uint(h[1]), xr[u].x, xl[u].x);
+        split_hi_lo_pair(__float_as_uint(h[2]), __float_as_uint(h[3]), xr[u].y, xl[u].y);
+        split_hi_lo_pair(__float_as_uint(h[4]), __float_as_uint(h[5]), xr[u].z, xl[u].z);
+        split_hi_lo_pair(__float_as_uint(h[6]), __float_as_uint(h[7]), xr[u].w, xl[u].w);
+      } else {
+        xr[u] = make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+      }
+    }
+  }
+
+  // ---- the walks (fewtok_xreg_kernel / fewtok_xreg_f32_kernel<.., XF32> with their x already in registers)
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = 0; i < my_groups; ++i) {
+    if (!router) {
+#pragma unroll
+      for (int u = 0; u < FB_U; ++u) {
+        mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, w[u].x, w[u].y);
+        mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, w[u].z, w[u].w);
+      }
+      if (i + 1 < my_groups) load_p(i + 1);
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int u = 0; u < FB_U / 2; ++u) {
+          uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+          split_hi_lo_pair(w[2 * u].x, w[2 * u].y, h0, l0);
+          split_hi_lo_pair(w[2 * u].z, w[2 * u].w, h1, l1);
+          split_hi_lo_pair(w[2 * u + 1].x, w[2 * u + 1].y, h2, l2);
+          split_hi_lo_pair(w[2 * u + 1].z, w[2 * u + 1].w, h3, l3);
+          const uint4 xa = xr[h * (FB_U / 2) + u], xb = xl[h * (FB_U / 2) + u];
+          mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, h0, h1);
+          mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, h2, h3);
+          mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, l0, l1);
+          mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, l2, l3);
+          mma_bf16_16816(acc, xb.x, 0u, xb.y, 0u, h0, h1);
+          mma_bf16_16816(acc, xb.z, 0u, xb.w, 0u, h2, h3);
+        }
+        if (h == 0) load_r(i, 1);
+        else if (i + 1 < my_groups) load_r(i + 1, 0);
+      }
+    }
+    *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+    __syncthreads();   // the buffer written two groups ago is free again once every warp passed this
+    if (threadIdx.x < 64) {
+      float sum = 0.f;
+#pragma unroll 8
+      for (int wv = 0; wv < FB_NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
+      const int t = threadIdx.x >> 3, r = (c + i * C) * 8 + (threadIdx.x & 7);
+      if (t < m && r < N) {
+        if (router) outr[static_cast<size_t>(t) * ld_outr + r] = sum;
+        else outp[static_cast<size_t>(t) * ld_outp + r] = __float2bfloat16_rn(sum);
+      }
+    }
+  }
+}
+
 static int boundary_args_ok(const BoundaryArgs& bd, int m, int D) {
   if (!bd.stream || !bd.attn || !bd.alpha || !bd.beta || !bd.norm_w || m < 1 || D < 8 || D % 8) return -1;
   const uintptr_t all = reinterpret_cast<uintptr_t>(bd.stream) | reinterpret_cast<uintptr_t>(bd.attn) |
@@ -783,18 +921,18 @@ static cudaError_t launch_boundary(const void* W, void* out, int m, int N, int K
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  const size_t smem = boundary_smem_bytes(K);
+  const size_t smem = boundary_smem_bytes(K, m);
   if (!sms[dev]) {
     int v = 0;
     if ((e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
     if constexpr (F32W) {
       if ((e = cudaFuncSetAttribute(fewtok_xreg_f32_kernel<16, 8, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
+                                    static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) != cudaSuccess) return e;
     } else {
       if ((e = cudaFuncSetAttribute(fewtok_xreg_kernel<16, 8, false, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
+                                    static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) != cudaSuccess) return e;
       if ((e = cudaFuncSetAttribute(fewtok_xreg_kernel<16, 8, false, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
+                                    static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) != cudaSuccess) return e;
     }
     sms[dev] = v;
   }
@@ -803,7 +941,7 @@ static cudaError_t launch_boundary(const void* W, void* out, int m, int N, int K
   if (walkers > groups) walkers = groups;
   if constexpr (F32W) {
     fewtok_xreg_f32_kernel<16, 8, true, true><<<walkers, 512, smem, s>>>(reinterpret_cast<const float*>(W), nullptr,
-                                                                         reinterpret_cast<float*>(out), m, N, K, K, ld_out, 1, bd);
+                                                                         reinterpret_cast<float*>(out), m, N, K, K, ld_out, 1, bd, status);
   } else {
     const bool vec = N % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | (static_cast<uintptr_t>(ld_out) * 2)) & 15) == 0;
     if (vec)
@@ -881,6 +1019,43 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
 #undef MUSE_FEWTOK
   if (e == cudaErrorInvalidConfiguration) return -5;
   return static_cast<int>(e);
+}
+
+// One launch for boundary -> pooler + router (up to 8 tokens, K <= 4096 in whole 32-element pieces, at least 8 m
+// pooler rows so that CTA t exists for every token t).
+int fused_boundary_dispatch(const void* Wp, const void* Wr, const BoundaryArgs& bd, void* outp, void* outr, int m, int Np, int Nr,
+                            int K, int ld_outp, int ld_outr, int* status, cudaStream_t stream) {
+  if (!Wp || !Wr || !outp || !outr || !status || Np <= 0 || Nr <= 0) return -1;
+  const int bad = boundary_args_ok(bd, m, K);
+  if (bad) return bad;
+  if (m > BND_TOKENS) return -9;
+  if (K % 32 != 0 || K / 32 > FB_NW * FB_U || ld_outp < Np || ld_outr < Nr) return -2;
+  if ((reinterpret_cast<uintptr_t>(Wp) | reinterpret_cast<uintptr_t>(Wr)) & 15) return -2;
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return static_cast<int>(cudaErrorInvalidDevice);
+  const size_t smem = boundary_smem_bytes(K, m);
+  if (!sms[dev]) {
+    int v = 0;
+    if ((e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaFuncSetAttribute(fused_boundary_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) !=
+        cudaSuccess)
+      return static_cast<int>(e);
+    sms[dev] = v;
+  }
+  // The router's groups are twice the bytes of the pooler's: give each router group a CTA of its own (up to a
+  // quarter of the SMs), the pooler the rest.
+  const int gp = (Np + 7) / 8, gr = (Nr + 7) / 8;
+  int rc = gr < sms[dev] / 4 ? gr : sms[dev] / 4;
+  int pc = sms[dev] - rc < gp ? sms[dev] - rc : gp;
+  if (pc < m) return -9;   // CTA t publishes token t
+  fused_boundary_kernel<<<pc + rc, FB_NT, smem, stream>>>(reinterpret_cast<const __nv_bfloat16*>(Wp), reinterpret_cast<const float*>(Wr), bd,
+                                                           reinterpret_cast<__nv_bfloat16*>(outp), reinterpret_cast<float*>(outr), m, Np, Nr,
+                                                           K, ld_outp, ld_outr, pc, status);
+  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace muse

@@ -383,6 +383,30 @@ def kernel_fn_boundary(data, state, stream1: torch.Tensor | None = None, h: torc
     return out
 
 
+def boundary_pooler_router(data, state, stream1: torch.Tensor | None = None, h: torch.Tensor | None = None,
+                           h_f32: torch.Tensor | None = None):
+    """The boundary, the pooler and the router as one launch (three launches on two streams in the reference:
+    best_submissions/muse_decode_layer.py:855-869): data = {"stream": FP32 [m, K], "attn_out": BF16 [m, K]} with
+    m <= 8 and K <= 4096; returns (pooler output BF16 [m, n_pooler], router logits FP32 [m, n_router]), the same
+    values as kernel_fn_boundary gives for each layer. `stream1`, `h`, `h_f32` as there."""
+    wp, wr = state["pooler"], state["router"]
+    stream_in, attn_out = data["stream"], data["attn_out"]
+    m, k = stream_in.shape
+    if k != wp.shape[1] or k != wr.shape[1]:
+        raise ValueError(f"stream {tuple(stream_in.shape)} does not fit the pooler {tuple(wp.shape)} / router {tuple(wr.shape)}")
+    if m > BOUNDARY_FUSED_MAX_TOKENS or k > 4096 or k % 32 or -(-wp.shape[0] // 8) < m:
+        raise ValueError(f"the fused boundary serves m <= {BOUNDARY_FUSED_MAX_TOKENS}, K <= 4096 in whole 32-element pieces "
+                         f"and n >= 8 m; got m={m}, K={k}")
+    out_p = torch.empty((m, wp.shape[0]), device=stream_in.device, dtype=torch.bfloat16)
+    out_r = torch.empty((m, wr.shape[0]), device=stream_in.device, dtype=torch.float32)
+    bd = _boundary_args(state, stream_in, attn_out, stream1, h, h_f32)
+    _capi.check(_capi.load().muse_boundary_pooler_router(wp.data_ptr(), wr.data_ptr(), ctypes.addressof(bd), out_p.data_ptr(),
+                                                         out_r.data_ptr(), m, wp.shape[0], wr.shape[0], k, wp.shape[0], wr.shape[0],
+                                                         state["_status"].data_ptr(), torch.cuda.current_stream(stream_in.device).cuda_stream),
+                f"muse_boundary_pooler_router(m={m}, k={k})")
+    return out_p, out_r
+
+
 FETCH_X_BY_KERNEL = True
 STORE_OUT_BY_KERNEL = True   # the copy-out of the larger calls by the same small kernel (786 KB: 5 us less than the copy engine)
 FETCH_MAX_TOKENS = 32       # x up to 256 KB: the fetch kernel beats the copy engine at every size measured

@@ -86,6 +86,40 @@ def test_fused_boundary_projection_matches_the_oracle(oracle, proj, layer, m):
     assert torch.equal(again, outs[0])
 
 
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+def test_one_launch_boundary_pooler_router(oracle, proj, m):
+    """muse_boundary_pooler_router: both outputs, stream1, h and the FP32 h against the oracle, and bit for bit
+    against the per-layer fused entry (same walk, same summation order), over repeated calls."""
+    layers = {name: oracle.TARGET_LAYERS[name] for name in ("pooler", "router")}
+    k = layers["pooler"][1]
+    state, w_cpu, gate, norm_w = _state(oracle, proj, k, 41, layers)
+    stream, attn_out, _, _ = oracle.boundary_inputs(m, k, 41)
+    stream, attn_out = stream[:m].contiguous(), attn_out[:m].contiguous()
+    want_s1, want_h = oracle.attn_boundary(stream, attn_out, gate, norm_w)
+    s1 = torch.full((m, k), float("nan"), device=DEV)
+    h = torch.full((m, k), float("nan"), device=DEV, dtype=torch.bfloat16)
+    hf = torch.full((m, k), float("nan"), device=DEV)
+    data = {"stream": stream.to(DEV), "attn_out": attn_out.to(DEV)}
+    outs = [proj.boundary_pooler_router(data, state, stream1=s1, h=h, h_f32=hf) for _ in range(3)]
+    torch.cuda.synchronize(DEV)
+    assert all(torch.equal(outs[0][0], o[0]) and torch.equal(outs[0][1], o[1]) for o in outs[1:])
+    pooled, logits = outs[0]
+    assert pooled.dtype == torch.bfloat16 and tuple(pooled.shape) == (m, layers["pooler"][0])
+    assert logits.dtype == torch.float32 and tuple(logits.shape) == (m, layers["router"][0])
+    assert rel(s1.cpu(), want_s1) < 2e-6 and rel(hf.cpu(), want_h) < 2e-6 and rel(h.cpu().float(), want_h) < 4e-3
+    assert rel(logits.cpu(), want_h.double() @ w_cpu["router"].double().T) < 2e-5
+    assert rel(pooled.cpu(), want_h.to(torch.bfloat16).double() @ w_cpu["pooler"].double().T) < 6e-3
+    for layer, got in (("pooler", pooled), ("router", logits)):
+        cfg = {"layer": layer, "m": m, "n": layers[layer][0], "k": k}
+        one = proj.kernel_fn_boundary(dict(data, config=cfg), state)
+        assert rel(got.cpu(), one.cpu()) < (2e-3 if layer == "pooler" else 2e-6)
+    again = proj.boundary_pooler_router(data, state)                     # without the optional outputs
+    assert torch.equal(again[0], pooled) and torch.equal(again[1], logits)
+    with pytest.raises(ValueError):
+        big = {"stream": torch.zeros((9, k), device=DEV), "attn_out": torch.zeros((9, k), device=DEV, dtype=torch.bfloat16)}
+        proj.boundary_pooler_router(big, state)
+
+
 def test_fused_boundary_rejections(oracle, proj):
     layers = {"pooler": oracle.TARGET_LAYERS["pooler"]}
     state, _, _, _ = _state(oracle, proj, 4096, 5, layers)
