@@ -157,15 +157,16 @@ int muse_attn_boundary(const muse_boundary_t* bd, int m, int d, void* stream);
 int muse_fewtok_boundary(const void* W, int w_is_f32, const muse_boundary_t* bd, void* out, int m, int N, int K, int ld_out,
                          int* status, void* stream);
 /* The whole stretch between the `o` projection and the experts as ONE launch (the boundary, the pooler and the
- * router of best_submissions/muse_decode_layer.py:855-869, three launches on two streams there): every CTA
- * rebuilds h once (one pass over stream and attn_out), then most CTAs walk the pooler's BF16 rows with h rounded
- * to BF16 and the others the router's FP32 rows with h in FP32 (hi + lo), each exactly as muse_fewtok_boundary
- * would. out_pooler: BF16 [m, n_pooler]; out_router: FP32 [m, n_router]; m <= 8, K = d <= 4096, K % 32 == 0,
- * n_pooler >= 8 m; CTA t also writes token t's stream1 / h / h_f32 where given. `status` as for muse_fewtok_mma
- * (the one bounded wait is for the CTA's own bulk copies of its input). */
+ * router of best_submissions/muse_decode_layer.py:855-869, three launches on two streams there): CTA t computes
+ * token t's boundary once and publishes stream1 / h / h_f32 (h and h_f32 are REQUIRED here: the other CTAs read
+ * them), every CTA waits for the m tokens with a bounded wait, then most CTAs walk the pooler's BF16 rows with the
+ * BF16 h and the others the router's FP32 rows with the FP32 h (hi + lo), each as muse_fewtok_mma /
+ * muse_fewtok_f32 would. out_pooler: BF16 [m, n_pooler]; out_router: FP32 [m, n_router]; m <= 8, K = d <= 4096,
+ * K % 32 == 0, n_pooler >= 8 m. cnt: 9 ints in device memory, zero before the first call and left zero by every
+ * call (calls that may overlap on the GPU need one each). `status`: ST_X_TIMEOUT if a token never arrived. */
 int muse_boundary_pooler_router(const void* W_pooler, const void* W_router, const muse_boundary_t* bd, void* out_pooler,
                                 void* out_router, int m, int n_pooler, int n_router, int K, int ld_out_pooler,
-                                int ld_out_router, int* status, void* stream);
+                                int ld_out_router, int* cnt, int* status, void* stream);
 
 /* Staging for callers whose activations live in HOST memory (page-locked for the copies to be
  * asynchronous): x goes host -> device on `stream` before the projection is launched there, and

@@ -60,58 +60,12 @@ __device__ __forceinline__ void bnd_reduce8(float (&ss)[BND_TOKENS], float (*red
   __syncthreads();
 }
 
-// Shared memory of the prologue for m tokens of width D: s1 rows (FP32, padded), the attention rows (BF16) and
-// 1 + w (FP32).
-struct BoundarySmem {
-  float* s1;            // [m][D + BND_PAD]
-  __nv_bfloat16* a;     // [m][D]
-  float* onew;          // [D]
-};
-__host__ __device__ inline size_t boundary_smem_bytes(int D, int m) {
-  return static_cast<size_t>(m) * (D + BND_PAD) * sizeof(float) + static_cast<size_t>(m) * D * 2 + static_cast<size_t>(D) * sizeof(float);
-}
-__device__ __forceinline__ BoundarySmem boundary_smem_carve(float* base, int D, int m) {
-  BoundarySmem b;
-  b.s1 = base;
-  b.a = reinterpret_cast<__nv_bfloat16*>(base + static_cast<size_t>(m) * (D + BND_PAD));
-  b.onew = reinterpret_cast<float*>(b.a + static_cast<size_t>(m) * D);
-  return b;
-}
-
-// The prologue. One thread starts a bulk copy of every token's stream row (into its s1 row, rewritten in place)
-// and attention row, so that all of a CTA's input is in flight at once without holding registers (loads behind
-// a per-token branch would be waited for one token at a time); the threads meanwhile fetch alpha, beta and the
-// norm weight for their own 8-element chunks. On return (true) b.s1[t * (D + BND_PAD) + d] holds s1 for t < m,
-// b.onew[d] = 1 + w[d] and inv2[t] the second norm's factor, so that h[t][d] = s1 * inv2[t] * onew[d]; CTA t
-// has written token t's stream1 / h / h_f32 where those pointers are given. False (every thread alike): the
-// copies did not arrive within the wait limit, ST_X_TIMEOUT has been raised in *status where given, and the
-// caller returns. `bar` is a shared-memory mbarrier not used otherwise. D % 8 == 0; 1 <= m <= BND_TOKENS.
+// The prologue. On return s1buf[t * (D + BND_PAD) + d] holds s1 (FP32) for t < m and inv2[t] the second norm's
+// factor, so that h[t][d] = s1 * inv2[t] * (1 + w[d]). D % 8 == 0; m <= BND_TOKENS.
 template <int NT>
-__device__ __forceinline__ bool boundary_prologue(const BoundaryArgs& bd, int m, int D, const BoundarySmem& b, uint64_t* bar,
-                                                  float (*red)[BND_TOKENS], float* inv1, float* inv2, int* status) {
+__device__ __forceinline__ void boundary_prologue(const BoundaryArgs& bd, int m, int D, float* s1buf,
+                                                  float (*red)[BND_TOKENS], float* inv1, float* inv2) {
   const int cpt = D >> 3, row = D + BND_PAD;
-  if (threadIdx.x == 0) {
-    mbar_init(smem_u32(bar), 1);
-    fence_mbar_init();
-    mbar_expect_tx(smem_u32(bar), static_cast<uint32_t>(m) * static_cast<uint32_t>(D) * 6u);
-    for (int t = 0; t < m; ++t) {
-      bulk_load_1d(smem_u32(b.s1 + t * row), bd.stream + static_cast<size_t>(t) * D, static_cast<uint32_t>(D) * 4u, smem_u32(bar));
-      bulk_load_1d(smem_u32(b.a + static_cast<size_t>(t) * D), bd.attn + static_cast<size_t>(t) * D, static_cast<uint32_t>(D) * 2u,
-                   smem_u32(bar));
-    }
-  }
-  for (int c = threadIdx.x; c < cpt; c += NT) {
-    float w[8];
-    bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.norm_w) + c), w);
-    float4* ow = reinterpret_cast<float4*>(b.onew + c * 8);
-    ow[0] = make_float4(1.f + w[0], 1.f + w[1], 1.f + w[2], 1.f + w[3]);
-    ow[1] = make_float4(1.f + w[4], 1.f + w[5], 1.f + w[6], 1.f + w[7]);
-  }
-  __syncthreads();   // the barrier's initialisation is visible to every waiter
-  if (!__syncthreads_and(mbar_wait(smem_u32(bar), 0) ? 1 : 0)) {
-    if (threadIdx.x == 0 && status) atomicOr(status, ST_X_TIMEOUT);
-    return false;
-  }
   float ss[BND_TOKENS];
 #pragma unroll
   for (int t = 0; t < BND_TOKENS; ++t) ss[t] = 0.f;
@@ -121,13 +75,14 @@ __device__ __forceinline__ bool boundary_prologue(const BoundaryArgs& bd, int m,
     for (int t = 0; t < BND_TOKENS; ++t) {
       if (t < m) {
         float a[8];
-        bf16x8_to_f32(reinterpret_cast<const uint4*>(b.a + static_cast<size_t>(t) * D)[c], a);
+        bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a);
+        const float4 s0 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c);
+        const float4 s1 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c + 1);
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss[t] = fmaf(a[i], a[i], ss[t]);
-        float4* p = reinterpret_cast<float4*>(b.s1 + t * row + c * 8);
-        const float4 s0 = p[0], s1 = p[1];
-        p[0] = make_float4(a0.x * s0.x, a0.y * s0.y, a0.z * s0.z, a0.w * s0.w);
-        p[1] = make_float4(a1.x * s1.x, a1.y * s1.y, a1.z * s1.z, a1.w * s1.w);
+        float4* dst = reinterpret_cast<float4*>(s1buf + t * row + c * 8);
+        dst[0] = make_float4(a0.x * s0.x, a0.y * s0.y, a0.z * s0.z, a0.w * s0.w);
+        dst[1] = make_float4(a1.x * s1.x, a1.y * s1.y, a1.z * s1.z, a1.w * s1.w);
       }
     }
   }
@@ -140,8 +95,8 @@ __device__ __forceinline__ bool boundary_prologue(const BoundaryArgs& bd, int m,
     for (int t = 0; t < BND_TOKENS; ++t) {
       if (t < m) {
         float a[8];
-        bf16x8_to_f32(reinterpret_cast<const uint4*>(b.a + static_cast<size_t>(t) * D)[c], a);
-        float4* p = reinterpret_cast<float4*>(b.s1 + t * row + c * 8);
+        bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a);
+        float4* p = reinterpret_cast<float4*>(s1buf + t * row + c * 8);
         const float r = inv1[t];
         float4 v0 = p[0], v1 = p[1];
         v0.x = fmaf(b0.x * a[0], r, v0.x); v0.y = fmaf(b0.y * a[1], r, v0.y); v0.z = fmaf(b0.z * a[2], r, v0.z); v0.w = fmaf(b0.w * a[3], r, v0.w);
@@ -162,11 +117,12 @@ __device__ __forceinline__ bool boundary_prologue(const BoundaryArgs& bd, int m,
   if (t < m && (bd.h || bd.h_f32)) {
     const float r = inv2[t];
     for (int c = threadIdx.x; c < cpt; c += NT) {
-      const float4* p = reinterpret_cast<const float4*>(b.s1 + t * row + c * 8);
-      const float4* ow = reinterpret_cast<const float4*>(b.onew + c * 8);
-      const float4 v0 = p[0], v1 = p[1], o0 = ow[0], o1 = ow[1];
-      const float h[8] = {v0.x * r * o0.x, v0.y * r * o0.y, v0.z * r * o0.z, v0.w * r * o0.w,
-                          v1.x * r * o1.x, v1.y * r * o1.y, v1.z * r * o1.z, v1.w * r * o1.w};
+      float w[8];
+      bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.norm_w) + c), w);
+      const float4* p = reinterpret_cast<const float4*>(s1buf + t * row + c * 8);
+      const float4 v0 = p[0], v1 = p[1];
+      const float h[8] = {v0.x * r * (1.f + w[0]), v0.y * r * (1.f + w[1]), v0.z * r * (1.f + w[2]), v0.w * r * (1.f + w[3]),
+                          v1.x * r * (1.f + w[4]), v1.y * r * (1.f + w[5]), v1.z * r * (1.f + w[6]), v1.w * r * (1.f + w[7])};
       if (bd.h)
         reinterpret_cast<uint4*>(bd.h + static_cast<size_t>(t) * D)[c] =
             make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
@@ -177,17 +133,20 @@ __device__ __forceinline__ bool boundary_prologue(const BoundaryArgs& bd, int m,
       }
     }
   }
-  return true;
 }
 
 // Eight consecutive values of h for token g starting at element k0 (a multiple of 8), from the prologue's buffers.
-__device__ __forceinline__ void boundary_h8(const BoundarySmem& b, const float* inv2, int D, int g, int k0, float (&h)[8]) {
-  const float4* p = reinterpret_cast<const float4*>(b.s1 + g * (D + BND_PAD) + k0);
-  const float4* ow = reinterpret_cast<const float4*>(b.onew + k0);
-  const float4 v0 = p[0], v1 = p[1], o0 = ow[0], o1 = ow[1];
+__device__ __forceinline__ void boundary_h8(const BoundaryArgs& bd, const float* s1buf, const float* inv2, int D, int g, int k0,
+                                            float (&h)[8]) {
+  float w[8];
+  bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.norm_w + k0)), w);
+  const float4* p = reinterpret_cast<const float4*>(s1buf + g * (D + BND_PAD) + k0);
+  const float4 v0 = p[0], v1 = p[1];
   const float r = inv2[g];
-  h[0] = v0.x * r * o0.x; h[1] = v0.y * r * o0.y; h[2] = v0.z * r * o0.z; h[3] = v0.w * r * o0.w;
-  h[4] = v1.x * r * o1.x; h[5] = v1.y * r * o1.y; h[6] = v1.z * r * o1.z; h[7] = v1.w * r * o1.w;
+  h[0] = v0.x * r * (1.f + w[0]); h[1] = v0.y * r * (1.f + w[1]); h[2] = v0.z * r * (1.f + w[2]); h[3] = v0.w * r * (1.f + w[3]);
+  h[4] = v1.x * r * (1.f + w[4]); h[5] = v1.y * r * (1.f + w[5]); h[6] = v1.z * r * (1.f + w[6]); h[7] = v1.w * r * (1.f + w[7]);
 }
+
+inline size_t boundary_smem_bytes(int D) { return static_cast<size_t>(BND_TOKENS) * (D + BND_PAD) * sizeof(float); }
 
 }  // namespace muse

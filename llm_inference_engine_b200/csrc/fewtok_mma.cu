@@ -218,18 +218,16 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
   if (my_groups > 0) load(w, 0);
   if constexpr (BND) {
     // The first weight loads are in flight; every CTA now rebuilds h for all tokens and takes its fragments from it.
-    extern __shared__ __align__(16) float bnd_base[];
+    extern __shared__ __align__(16) float bnd_s1[];
     __shared__ float bnd_red[NW][BND_TOKENS];
     __shared__ float bnd_inv1[BND_TOKENS], bnd_inv2[BND_TOKENS];
-    __shared__ __align__(8) uint64_t bnd_bar;
-    const BoundarySmem bs = boundary_smem_carve(bnd_base, K, m);
-    if (!boundary_prologue<NW * 32>(bd, m, K, bs, &bnd_bar, bnd_red, bnd_inv1, bnd_inv2, status)) return;
+    boundary_prologue<NW * 32>(bd, m, K, bnd_s1, bnd_red, bnd_inv1, bnd_inv2);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       xr[u] = make_uint4(0u, 0u, 0u, 0u);
       if (g < m && first + u < kblocks) {
         float h[8];
-        boundary_h8(bs, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
+        boundary_h8(bd, bnd_s1, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
         xr[u] = make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
       }
     }
@@ -393,7 +391,7 @@ template <int NW, int U, bool XF32, bool BND = false>
 __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* __restrict__ W, const void* __restrict__ xv,
                                                                   float* __restrict__ out, int m, int N, int K, int ld_x,
                                                                   int ld_out, int tok_split,
-                                                                  const __grid_constant__ BoundaryArgs bd, int* __restrict__ status) {
+                                                                  const __grid_constant__ BoundaryArgs bd) {
   static_assert(!BND || XF32, "the boundary hands the router FP32 activations");
   constexpr int OUTS = 64, TOKS = 8;
   constexpr int SUBS = XF32 && U > 1 ? 2 : 1, PS = U / SUBS;   // weight sub-batches of a group, pieces in each
@@ -433,18 +431,16 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
     lo = *reinterpret_cast<const uint32_t*>(&l);
   };
   if constexpr (BND) {
-    extern __shared__ __align__(16) float bnd_base[];
+    extern __shared__ __align__(16) float bnd_s1[];
     __shared__ float bnd_red[NW][BND_TOKENS];
     __shared__ float bnd_inv1[BND_TOKENS], bnd_inv2[BND_TOKENS];
-    __shared__ __align__(8) uint64_t bnd_bar;
-    const BoundarySmem bs = boundary_smem_carve(bnd_base, K, m);
-    if (!boundary_prologue<NW * 32>(bd, m, K, bs, &bnd_bar, bnd_red, bnd_inv1, bnd_inv2, status)) return;
+    boundary_prologue<NW * 32>(bd, m, K, bnd_s1, bnd_red, bnd_inv1, bnd_inv2);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       xr[u] = xl[XF32 ? u : 0] = make_uint4(0u, 0u, 0u, 0u);
       if (g < m && first + u < kblocks) {
         float h[8];
-        boundary_h8(bs, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
+        boundary_h8(bd, bnd_s1, bnd_inv2, K, g, (first + u) * 32 + q * 8, h);
         split(__float_as_uint(h[0]), __float_as_uint(h[1]), xr[u].x, xl[XF32 ? u : 0].x);
         split(__float_as_uint(h[2]), __float_as_uint(h[3]), xr[u].y, xl[XF32 ? u : 0].y);
         split(__float_as_uint(h[4]), __float_as_uint(h[5]), xr[u].z, xl[XF32 ? u : 0].z);
@@ -651,7 +647,7 @@ static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int 
   if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
   kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), x, reinterpret_cast<float*>(out), m, N, K,
-                                               ld_x, ld_out, tok_split, BoundaryArgs{}, nullptr);
+                                               ld_x, ld_out, tok_split, BoundaryArgs{});
   return cudaGetLastError();
 }
 
@@ -762,11 +758,17 @@ __global__ void __launch_bounds__(256) attn_boundary_kernel(const __grid_constan
 // ---------------------------------------------------------------- boundary + pooler + router in one launch
 //
 // The three kernels the decode layer runs between the `o` projection and the experts (boundary, pooler, and the
-// router on a side stream: best_submissions/muse_decode_layer.py:855-869) as ONE launch for up to 8 tokens: every
-// CTA first issues the weight loads of its first row group, then every CTA rebuilds h (boundary_prologue: bulk
-// copies of the inputs into shared memory, two CTA-wide reductions), and then the first `pooler_ctas` CTAs walk the pooler's BF16 rows with BF16-rounded h while the others walk the
-// router's FP32 rows with FP32 h split to hi + lo (three MMAs per weight half-pair, as the FP32-input mode).
-// One launch and one prologue instead of three launches (or two launches with a prologue each).
+// router on a side stream: best_submissions/muse_decode_layer.py:855-869) as ONE launch for up to 8 tokens.
+// Every CTA first issues the weight loads of its first row group. One CTA per token then computes its boundary
+// (one 8-element chunk per thread, values in registers between the two CTA-wide reductions), writes stream1, the
+// BF16 h and the FP32 h to global memory and releases flag t. Every CTA waits (bounded) for the m flags and takes
+// its x from those rows: the first `pooler_ctas` CTAs walk the pooler's BF16 rows with BF16 fragments held in
+// registers (as fewtok_xreg_kernel), the others the router's FP32 rows with the FP32 h copied to shared memory
+// and split to hi + lo as it is read (three MMAs per weight half-pair), which leaves their registers for a whole
+// 8-row group of FP32 weight in flight at once. Rebuilding h in every CTA instead costs about a
+// microsecond per token of shared-memory traffic on every SM; here it is computed once and read from L2.
+// The producers wait for nobody, so nothing can wait in a circle; the grid is at most one CTA per SM. The last
+// CTA to have read its fragments (a counter) puts the flags and the counter back to zero for the next call.
 __device__ __forceinline__ void split_hi_lo_pair(uint32_t a_bits, uint32_t b_bits, uint32_t& hi, uint32_t& lo) {
   const float a = __uint_as_float(a_bits), b = __uint_as_float(b_bits);
   const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -775,122 +777,253 @@ __device__ __forceinline__ void split_hi_lo_pair(uint32_t a_bits, uint32_t b_bit
   const __nv_bfloat162 l = __floats2bfloat162_rn(ra, rb);
   lo = *reinterpret_cast<const uint32_t*>(&l);
 }
+__device__ __forceinline__ uint4 ld_cg16(const void* p) {   // L2 load of data another CTA of this launch wrote
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 
 constexpr int FB_NW = 16, FB_U = 8, FB_NT = FB_NW * 32;   // 512 threads: 16 warps x 8 pieces of 32 elements = K up to 4096
+constexpr int FB_DONE = BND_TOKENS;                        // cnt[0..7]: token ready flags; cnt[8]: CTAs that have read them
+
+// Sum over the CTA; every thread gets the total. red: [FB_NW] floats.
+__device__ __forceinline__ float fb_block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();   // red is free again
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = (threadIdx.x & 31) < FB_NW ? red[threadIdx.x & 31] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+// Every thread of the CTA: wait (bounded) until the m tokens are published, thread t on flag t. CTA-uniform result.
+__device__ __forceinline__ bool fb_wait_tokens(const int* cnt, int m) {
+  bool ready = true;
+  if (threadIdx.x < m) {
+    const unsigned long long t0 = global_ns();
+    while (ld_acquire_gpu(cnt + threadIdx.x) == 0) {
+      if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        ready = false;
+        break;
+      }
+    }
+  }
+  return __syncthreads_and(ready ? 1 : 0) != 0;
+}
+
+// One row group's 64 partial sums per warp -> out[t][8 rows]: every warp has written red[warp][64] and the CTA has
+// synchronised; threads 0..63 add the warps up.
+template <typename OutT>
+__device__ __forceinline__ void fb_store_group(const float (*red)[64], OutT* out, int ld_out, int m, int N, int row0) {
+  if (threadIdx.x < 64) {
+    float sum = 0.f;
+#pragma unroll 8
+    for (int wv = 0; wv < FB_NW; ++wv) sum += red[wv][threadIdx.x];
+    const int t = threadIdx.x >> 3, r = row0 + (threadIdx.x & 7);
+    if (t < m && r < N) {
+      if constexpr (sizeof(OutT) == 4) out[static_cast<size_t>(t) * ld_out + r] = sum;
+      else out[static_cast<size_t>(t) * ld_out + r] = __float2bfloat16_rn(sum);
+    }
+  }
+}
 
 __global__ void __launch_bounds__(FB_NT, 1)
 fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restrict__ Wr, const __grid_constant__ BoundaryArgs bd,
                       __nv_bfloat16* __restrict__ outp, float* __restrict__ outr, int m, int Np, int Nr, int K, int ld_outp,
-                      int ld_outr, int pooler_ctas, int* __restrict__ status) {
-  extern __shared__ __align__(16) float fb_smem[];
+                      int ld_outr, int pooler_ctas, int* __restrict__ cnt, int* __restrict__ status) {
+  extern __shared__ __align__(16) float fb_x[];          // router CTAs: the FP32 h rows, [m][K + BND_PAD]
   __shared__ __align__(16) float red[2][FB_NW][64];
-  __shared__ float bnd_red[FB_NW][BND_TOKENS];
-  __shared__ float inv1[BND_TOKENS], inv2[BND_TOKENS];
-  __shared__ __align__(8) uint64_t bnd_bar;
+  __shared__ float bsum[FB_NW];
+  __shared__ __align__(8) uint64_t xbar;
+  // Diagnostic builds: thread 0 of every CTA stamps the global nanosecond timer into its 16 slots (0 entry, 1 first
+  // loads issued, 2 token published (producers), 3 all tokens seen, 4 fragments ready, 5 first group multiplied,
+  // 6 exit).
+  unsigned long long* const trace = MUSE_TRACE_BASE();
+  unsigned long long* const tr = trace && threadIdx.x == 0 ? trace + 16ull * blockIdx.x : nullptr;
+#define FB_STAMP(slot) do { if (tr) tr[slot] = global_ns(); } while (0)
+  FB_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
-  const bool router = static_cast<int>(blockIdx.x) >= pooler_ctas;
-  const int C = router ? static_cast<int>(gridDim.x) - pooler_ctas : pooler_ctas;
-  const int c = router ? static_cast<int>(blockIdx.x) - pooler_ctas : static_cast<int>(blockIdx.x);
-  const int N = router ? Nr : Np;
-  const int kblocks = K >> 5, groups = (N + 7) >> 3;
-  const int my_groups = c < groups ? (groups - c + C - 1) / C : 0;
-  const int first = warp * FB_U;
+  const int kblocks = K >> 5, first = warp * FB_U;
+  bool ok;
 
-  // ---- first weight loads (BF16: 8 pieces of 16 bytes; FP32: the first 4 of 8 pieces, 32 bytes each)
-  uint4 w[FB_U];
-  auto load_p = [&](int i) {
-    int r = (c + i * C) * 8 + g;
-    r = r < N ? r : N - 1;
-    const uint4* p = reinterpret_cast<const uint4*>(Wp + static_cast<size_t>(r) * K) + q;
-#pragma unroll
-    for (int u = 0; u < FB_U; ++u) w[u] = first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
-  };
-  auto load_r = [&](int i, int h) {
-    int r = (c + i * C) * 8 + g;
-    r = r < N ? r : N - 1;
-    const uint4* p = reinterpret_cast<const uint4*>(Wr + static_cast<size_t>(r) * K) + 2 * q;
-#pragma unroll
-    for (int u = 0; u < FB_U / 2; ++u) {
-      const int piece = first + h * (FB_U / 2) + u;
-      const bool ok = piece < kblocks;
-      w[2 * u] = ok ? ldg_stream16(p + piece * 8) : make_uint4(0u, 0u, 0u, 0u);
-      w[2 * u + 1] = ok ? ldg_stream16(p + piece * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
+  if (static_cast<int>(blockIdx.x) >= pooler_ctas) {
+    // ================================================================ router CTAs
+    const int C = static_cast<int>(gridDim.x) - pooler_ctas, c = static_cast<int>(blockIdx.x) - pooler_ctas;
+    const int groups = (Nr + 7) >> 3, my_groups = c < groups ? (groups - c + C - 1) / C : 0;
+    const int xrow = K + BND_PAD;
+    if (threadIdx.x == 0) {
+      mbar_init(smem_u32(&xbar), 1);
+      fence_mbar_init();
     }
-  };
-  if (my_groups > 0) {
-    if (router) load_r(0, 0);
-    else load_p(0);
-  }
-
-  // ---- the boundary, once, while those loads are in flight
-  const BoundarySmem bs = boundary_smem_carve(fb_smem, K, m);
-  if (!boundary_prologue<FB_NT>(bd, m, K, bs, &bnd_bar, bnd_red, inv1, inv2, status)) return;
-
-  // ---- x fragments from shared memory: BF16 h for the pooler, FP32 h -> hi + lo for the router
-  uint4 xr[FB_U], xl[FB_U];
+    // A WHOLE group in flight: 8 pieces of 32 bytes (x stays in shared memory, which leaves the registers for it).
+    uint4 w[2 * FB_U];
+    auto load = [&](int i) {
+      int r = (c + i * C) * 8 + g;
+      r = r < Nr ? r : Nr - 1;
+      const uint4* p = reinterpret_cast<const uint4*>(Wr + static_cast<size_t>(r) * K) + 2 * q;
 #pragma unroll
-  for (int u = 0; u < FB_U; ++u) {
-    xr[u] = xl[u] = make_uint4(0u, 0u, 0u, 0u);
-    if (g < m && first + u < kblocks) {
-      float h[8];
-      boundary_h8(bs, inv2, K, g, (first + u) * 32 + q * 8, h);
-      if (router) {
-        split_hi_lo_pair(__float_as_uint(h[0]), __float_as_uint(h[1]), xr[u].x, xl[u].x);
-        split_hi_lo_pair(__float_as_uint(h[2]), __float_as_uint(h[3]), xr[u].y, xl[u].y);
-        split_hi_lo_pair(__float_as_uint(h[4]), __float_as_uint(h[5]), xr[u].z, xl[u].z);
-        split_hi_lo_pair(__float_as_uint(h[6]), __float_as_uint(h[7]), xr[u].w, xl[u].w);
-      } else {
-        xr[u] = make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+      for (int u = 0; u < FB_U; ++u) {
+        const bool in = first + u < kblocks;
+        w[2 * u] = in ? ldg_stream16(p + (first + u) * 8) : make_uint4(0u, 0u, 0u, 0u);
+        w[2 * u + 1] = in ? ldg_stream16(p + (first + u) * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
       }
+    };
+    if (my_groups > 0) load(0);
+    FB_STAMP(1);
+    ok = fb_wait_tokens(cnt, m);
+    FB_STAMP(3);
+    // The FP32 rows into shared memory by one thread's bulk copies (they were written through the generic proxy,
+    // hence the proxy fence).
+    if (ok && threadIdx.x == 0) {
+      asm volatile("fence.proxy.async;" ::: "memory");
+      mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(m) * static_cast<uint32_t>(K) * 4u);
+      for (int t = 0; t < m; ++t)
+        bulk_load_1d(smem_u32(fb_x + t * xrow), bd.h_f32 + static_cast<size_t>(t) * K, static_cast<uint32_t>(K) * 4u, smem_u32(&xbar));
     }
-  }
-
-  // ---- the walks (fewtok_xreg_kernel / fewtok_xreg_f32_kernel<.., XF32> with their x already in registers)
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int i = 0; i < my_groups; ++i) {
-    if (!router) {
+    if (ok) ok = __syncthreads_and(mbar_wait(smem_u32(&xbar), 0) ? 1 : 0) != 0;
+    FB_STAMP(4);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < (ok ? my_groups : 0); ++i) {
+#pragma unroll
+      for (int u = 0; u < FB_U; ++u) {
+        uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
+        if (g < m && first + u < kblocks) {
+          const uint4* px = reinterpret_cast<const uint4*>(fb_x + g * xrow + (first + u) * 32 + q * 8);
+          const uint4 f0 = px[0], f1 = px[1];
+          split_hi_lo_pair(f0.x, f0.y, xa.x, xb.x);
+          split_hi_lo_pair(f0.z, f0.w, xa.y, xb.y);
+          split_hi_lo_pair(f1.x, f1.y, xa.z, xb.z);
+          split_hi_lo_pair(f1.z, f1.w, xa.w, xb.w);
+        }
+        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+        split_hi_lo_pair(w[2 * u].x, w[2 * u].y, h0, l0);
+        split_hi_lo_pair(w[2 * u].z, w[2 * u].w, h1, l1);
+        split_hi_lo_pair(w[2 * u + 1].x, w[2 * u + 1].y, h2, l2);
+        split_hi_lo_pair(w[2 * u + 1].z, w[2 * u + 1].w, h3, l3);
+        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, h0, h1);
+        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, h2, h3);
+        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, l0, l1);
+        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, l2, l3);
+        mma_bf16_16816(acc, xb.x, 0u, xb.y, 0u, h0, h1);
+        mma_bf16_16816(acc, xb.z, 0u, xb.w, 0u, h2, h3);
+      }
+      if (i + 1 < my_groups) load(i + 1);
+      *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      __syncthreads();   // the buffer written two groups ago is free again once every warp passed this
+      if (i == 0) FB_STAMP(5);
+      fb_store_group(red[i & 1], outr, ld_outr, m, Nr, (c + i * C) * 8);
+    }
+  } else {
+    // ================================================================ pooler CTAs (the last m of them produce h)
+    const int C = pooler_ctas, c = static_cast<int>(blockIdx.x);
+    const int groups = (Np + 7) >> 3, my_groups = c < groups ? (groups - c + C - 1) / C : 0;
+    // The producer of token t is pooler CTA pooler_ctas - 1 - t (the last CTAs walk the fewest groups). Its own
+    // input loads go out ahead of its weight loads: everybody waits for it.
+    const int tok = pooler_ctas - 1 - c;
+    const bool producer = tok < m;
+    const int ch = threadIdx.x;
+    const bool live = producer && ch < (K >> 3);
+    uint4 av = make_uint4(0u, 0u, 0u, 0u), nw = av;
+    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = s0, a0 = s0, a1 = s0, b0 = s0, b1 = s0;
+    if (live) {
+      av = __ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(tok) * K) + ch);
+      s0 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(tok) * K) + 2 * ch);
+      s4 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(tok) * K) + 2 * ch + 1);
+      a0 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * ch);
+      a1 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * ch + 1);
+      b0 = __ldg(reinterpret_cast<const float4*>(bd.beta) + 2 * ch);
+      b1 = __ldg(reinterpret_cast<const float4*>(bd.beta) + 2 * ch + 1);
+      nw = __ldg(reinterpret_cast<const uint4*>(bd.norm_w) + ch);
+    }
+    uint4 w[FB_U];
+    auto load = [&](int i) {
+      int r = (c + i * C) * 8 + g;
+      r = r < Np ? r : Np - 1;
+      const uint4* p = reinterpret_cast<const uint4*>(Wp + static_cast<size_t>(r) * K) + q;
+#pragma unroll
+      for (int u = 0; u < FB_U; ++u) w[u] = first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    };
+    if (my_groups > 0) load(0);
+    FB_STAMP(1);
+    if (producer) {   // token `tok`'s boundary, one chunk of 8 elements per thread (K / 8 <= 512)
+      float a[8], s1[8], ow[8];
+      const float be[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      bf16x8_to_f32(av, a);
+      bf16x8_to_f32(nw, ow);
+      s1[0] = a0.x * s0.x; s1[1] = a0.y * s0.y; s1[2] = a0.z * s0.z; s1[3] = a0.w * s0.w;
+      s1[4] = a1.x * s4.x; s1[5] = a1.y * s4.y; s1[6] = a1.z * s4.z; s1[7] = a1.w * s4.w;
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(a[i], a[i], ss);
+      const float r1 = rsqrtf(fb_block_sum(ss, bsum) / static_cast<float>(K) + BND_POST_EPS);
+      FB_STAMP(7);
+      ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s1[i] = fmaf(be[i] * a[i], r1, s1[i]);
+        ss = fmaf(s1[i], s1[i], ss);
+      }
+      const float r2 = rsqrtf(fb_block_sum(ss, bsum) / static_cast<float>(K) + BND_RMS_EPS);
+      if (live) {
+        float h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = s1[i] * r2 * (1.f + ow[i]);
+        float4* hf = reinterpret_cast<float4*>(bd.h_f32 + static_cast<size_t>(tok) * K) + 2 * ch;
+        hf[0] = make_float4(h[0], h[1], h[2], h[3]);
+        hf[1] = make_float4(h[4], h[5], h[6], h[7]);
+        reinterpret_cast<uint4*>(bd.h + static_cast<size_t>(tok) * K)[ch] =
+            make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+        if (bd.stream1) {
+          float4* gp = reinterpret_cast<float4*>(bd.stream1 + static_cast<size_t>(tok) * K) + 2 * ch;
+          gp[0] = make_float4(s1[0], s1[1], s1[2], s1[3]);
+          gp[1] = make_float4(s1[4], s1[5], s1[6], s1[7]);
+        }
+      }
+      __syncthreads();   // every thread's stores precede thread 0's release (cumulative at GPU scope)
+      FB_STAMP(8);
+      if (threadIdx.x == 0) st_release_gpu(cnt + tok, 1);
+      FB_STAMP(2);
+    }
+    ok = fb_wait_tokens(cnt, m);
+    FB_STAMP(3);
+    uint4 xr[FB_U];   // the BF16 fragments, straight from L2
+#pragma unroll
+    for (int u = 0; u < FB_U; ++u)
+      xr[u] = (ok && g < m && first + u < kblocks) ? ld_cg16(bd.h + static_cast<size_t>(g) * K + (first + u) * 32 + q * 8)
+                                                   : make_uint4(0u, 0u, 0u, 0u);
+    FB_STAMP(4);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < (ok ? my_groups : 0); ++i) {
 #pragma unroll
       for (int u = 0; u < FB_U; ++u) {
         mma_bf16_16816(acc, xr[u].x, 0u, xr[u].y, 0u, w[u].x, w[u].y);
         mma_bf16_16816(acc, xr[u].z, 0u, xr[u].w, 0u, w[u].z, w[u].w);
       }
-      if (i + 1 < my_groups) load_p(i + 1);
-    } else {
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-#pragma unroll
-        for (int u = 0; u < FB_U / 2; ++u) {
-          uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-          split_hi_lo_pair(w[2 * u].x, w[2 * u].y, h0, l0);
-          split_hi_lo_pair(w[2 * u].z, w[2 * u].w, h1, l1);
-          split_hi_lo_pair(w[2 * u + 1].x, w[2 * u + 1].y, h2, l2);
-          split_hi_lo_pair(w[2 * u + 1].z, w[2 * u + 1].w, h3, l3);
-          const uint4 xa = xr[h * (FB_U / 2) + u], xb = xl[h * (FB_U / 2) + u];
-          mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, h0, h1);
-          mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, h2, h3);
-          mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, l0, l1);
-          mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, l2, l3);
-          mma_bf16_16816(acc, xb.x, 0u, xb.y, 0u, h0, h1);
-          mma_bf16_16816(acc, xb.z, 0u, xb.w, 0u, h2, h3);
-        }
-        if (h == 0) load_r(i, 1);
-        else if (i + 1 < my_groups) load_r(i + 1, 0);
-      }
-    }
-    *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
-    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-    __syncthreads();   // the buffer written two groups ago is free again once every warp passed this
-    if (threadIdx.x < 64) {
-      float sum = 0.f;
-#pragma unroll 8
-      for (int wv = 0; wv < FB_NW; ++wv) sum += red[i & 1][wv][threadIdx.x];
-      const int t = threadIdx.x >> 3, r = (c + i * C) * 8 + (threadIdx.x & 7);
-      if (t < m && r < N) {
-        if (router) outr[static_cast<size_t>(t) * ld_outr + r] = sum;
-        else outp[static_cast<size_t>(t) * ld_outp + r] = __float2bfloat16_rn(sum);
-      }
+      if (i + 1 < my_groups) load(i + 1);
+      *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      __syncthreads();
+      if (i == 0) FB_STAMP(5);
+      fb_store_group(red[i & 1], outp, ld_outp, m, Np, (c + i * C) * 8);
     }
   }
+  if (!ok && threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
+  // The fragments were consumed above. The last CTA to get here re-arms the flags for the next call.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(cnt + FB_DONE, 1) == static_cast<int>(gridDim.x) - 1) {
+      for (int t = 0; t < BND_TOKENS; ++t) cnt[t] = 0;
+      __threadfence();
+      cnt[FB_DONE] = 0;
+    }
+  }
+  FB_STAMP(6);
+#undef FB_STAMP
 }
 
 static int boundary_args_ok(const BoundaryArgs& bd, int m, int D) {
@@ -921,18 +1054,18 @@ static cudaError_t launch_boundary(const void* W, void* out, int m, int N, int K
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  const size_t smem = boundary_smem_bytes(K, m);
+  const size_t smem = boundary_smem_bytes(K);
   if (!sms[dev]) {
     int v = 0;
     if ((e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
     if constexpr (F32W) {
       if ((e = cudaFuncSetAttribute(fewtok_xreg_f32_kernel<16, 8, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) != cudaSuccess) return e;
+                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
     } else {
       if ((e = cudaFuncSetAttribute(fewtok_xreg_kernel<16, 8, false, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) != cudaSuccess) return e;
+                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
       if ((e = cudaFuncSetAttribute(fewtok_xreg_kernel<16, 8, false, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) != cudaSuccess) return e;
+                                    static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess) return e;
     }
     sms[dev] = v;
   }
@@ -941,7 +1074,7 @@ static cudaError_t launch_boundary(const void* W, void* out, int m, int N, int K
   if (walkers > groups) walkers = groups;
   if constexpr (F32W) {
     fewtok_xreg_f32_kernel<16, 8, true, true><<<walkers, 512, smem, s>>>(reinterpret_cast<const float*>(W), nullptr,
-                                                                         reinterpret_cast<float*>(out), m, N, K, K, ld_out, 1, bd, status);
+                                                                         reinterpret_cast<float*>(out), m, N, K, K, ld_out, 1, bd);
   } else {
     const bool vec = N % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | (static_cast<uintptr_t>(ld_out) * 2)) & 15) == 0;
     if (vec)
@@ -1022,10 +1155,11 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
 }
 
 // One launch for boundary -> pooler + router (up to 8 tokens, K <= 4096 in whole 32-element pieces, at least 8 m
-// pooler rows so that CTA t exists for every token t).
+// pooler rows so that CTA t exists for every token t). At most one CTA per SM: the consumers of a token's h
+// spin while its producer runs. cnt: 9 ints, zero before the first call and again after every call.
 int fused_boundary_dispatch(const void* Wp, const void* Wr, const BoundaryArgs& bd, void* outp, void* outr, int m, int Np, int Nr,
-                            int K, int ld_outp, int ld_outr, int* status, cudaStream_t stream) {
-  if (!Wp || !Wr || !outp || !outr || !status || Np <= 0 || Nr <= 0) return -1;
+                            int K, int ld_outp, int ld_outr, int* cnt, int* status, cudaStream_t stream) {
+  if (!Wp || !Wr || !outp || !outr || !cnt || !status || Np <= 0 || Nr <= 0 || !bd.h || !bd.h_f32) return -1;
   const int bad = boundary_args_ok(bd, m, K);
   if (bad) return bad;
   if (m > BND_TOKENS) return -9;
@@ -1036,25 +1170,24 @@ int fused_boundary_dispatch(const void* Wp, const void* Wr, const BoundaryArgs& 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= 64) return static_cast<int>(cudaErrorInvalidDevice);
-  const size_t smem = boundary_smem_bytes(K, m);
   if (!sms[dev]) {
     int v = 0;
     if ((e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return static_cast<int>(e);
     if ((e = cudaFuncSetAttribute(fused_boundary_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(boundary_smem_bytes(4096, BND_TOKENS)))) !=
-        cudaSuccess)
+                                  static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess)
       return static_cast<int>(e);
     sms[dev] = v;
   }
+  const size_t smem = static_cast<size_t>(m) * (K + BND_PAD) * sizeof(float);   // the router CTAs' copy of the FP32 h
   // The router's groups are twice the bytes of the pooler's: give each router group a CTA of its own (up to a
   // quarter of the SMs), the pooler the rest.
   const int gp = (Np + 7) / 8, gr = (Nr + 7) / 8;
   int rc = gr < sms[dev] / 4 ? gr : sms[dev] / 4;
   int pc = sms[dev] - rc < gp ? sms[dev] - rc : gp;
-  if (pc < m) return -9;   // CTA t publishes token t
+  if (pc < m) return -9;   // one pooler CTA per token publishes it
   fused_boundary_kernel<<<pc + rc, FB_NT, smem, stream>>>(reinterpret_cast<const __nv_bfloat16*>(Wp), reinterpret_cast<const float*>(Wr), bd,
                                                            reinterpret_cast<__nv_bfloat16*>(outp), reinterpret_cast<float*>(outr), m, Np, Nr,
-                                                           K, ld_outp, ld_outr, pc, status);
+                                                           K, ld_outp, ld_outr, pc, cnt, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -388,7 +388,7 @@ def boundary_pooler_router(data, state, stream1: torch.Tensor | None = None, h: 
     """The boundary, the pooler and the router as one launch (three launches on two streams in the reference:
     best_submissions/muse_decode_layer.py:855-869): data = {"stream": FP32 [m, K], "attn_out": BF16 [m, K]} with
     m <= 8 and K <= 4096; returns (pooler output BF16 [m, n_pooler], router logits FP32 [m, n_router]), the same
-    values as kernel_fn_boundary gives for each layer. `stream1`, `h`, `h_f32` as there."""
+    values as attn_boundary() followed by kernel_fn() gives for each layer. `stream1`, `h`, `h_f32` as there."""
     wp, wr = state["pooler"], state["router"]
     stream_in, attn_out = data["stream"], data["attn_out"]
     m, k = stream_in.shape
@@ -397,12 +397,19 @@ def boundary_pooler_router(data, state, stream1: torch.Tensor | None = None, h: 
     if m > BOUNDARY_FUSED_MAX_TOKENS or k > 4096 or k % 32 or -(-wp.shape[0] // 8) < m:
         raise ValueError(f"the fused boundary serves m <= {BOUNDARY_FUSED_MAX_TOKENS}, K <= 4096 in whole 32-element pieces "
                          f"and n >= 8 m; got m={m}, K={k}")
-    out_p = torch.empty((m, wp.shape[0]), device=stream_in.device, dtype=torch.bfloat16)
-    out_r = torch.empty((m, wr.shape[0]), device=stream_in.device, dtype=torch.float32)
+    dev = stream_in.device
+    out_p = torch.empty((m, wp.shape[0]), device=dev, dtype=torch.bfloat16)
+    out_r = torch.empty((m, wr.shape[0]), device=dev, dtype=torch.float32)
+    if h is None:            # the kernel's CTAs hand h to one another through these rows
+        h = torch.empty((m, k), device=dev, dtype=torch.bfloat16)
+    if h_f32 is None:
+        h_f32 = torch.empty((m, k), device=dev, dtype=torch.float32)
     bd = _boundary_args(state, stream_in, attn_out, stream1, h, h_f32)
+    _, cnt = _stream_workspace(state, dev)
     _capi.check(_capi.load().muse_boundary_pooler_router(wp.data_ptr(), wr.data_ptr(), ctypes.addressof(bd), out_p.data_ptr(),
                                                          out_r.data_ptr(), m, wp.shape[0], wr.shape[0], k, wp.shape[0], wr.shape[0],
-                                                         state["_status"].data_ptr(), torch.cuda.current_stream(stream_in.device).cuda_stream),
+                                                         cnt.data_ptr(), state["_status"].data_ptr(),
+                                                         torch.cuda.current_stream(dev).cuda_stream),
                 f"muse_boundary_pooler_router(m={m}, k={k})")
     return out_p, out_r
 
