@@ -732,7 +732,7 @@ def run_ours(args) -> None:
     if boundary_rows:
         line["boundary_pooler_router"] = {
             "what": "us per (post-attention boundary -> pooler + router) of the decode layer, cold weights: boundary as its own "
-                    "kernel (separate) or as the prologue of both projections (fused); _fork = router on a side stream",
+                    "kernel (separate), as the prologue of both projections (fused), or all three as one launch (one_launch: muse_boundary_pooler_router); _fork = router on a side stream",
             "rows": [{k2: (round(v, 3) if isinstance(v, float) else v) for k2, v in r.items()} for r in boundary_rows]}
     if rowpar is not None:
         line["row_parallel_o"] = rowpar

@@ -157,16 +157,19 @@ int muse_attn_boundary(const muse_boundary_t* bd, int m, int d, void* stream);
 int muse_fewtok_boundary(const void* W, int w_is_f32, const muse_boundary_t* bd, void* out, int m, int N, int K, int ld_out,
                          int* status, void* stream);
 /* The whole stretch between the `o` projection and the experts as ONE launch (the boundary, the pooler and the
- * router of best_submissions/muse_decode_layer.py:855-869, three launches on two streams there): CTA t computes
- * token t's boundary once and publishes stream1 / h / h_f32 (h and h_f32 are REQUIRED here: the other CTAs read
- * them), every CTA waits for the m tokens with a bounded wait, then most CTAs walk the pooler's BF16 rows with the
- * BF16 h and the others the router's FP32 rows with the FP32 h (hi + lo), each as muse_fewtok_mma /
- * muse_fewtok_f32 would. out_pooler: BF16 [m, n_pooler]; out_router: FP32 [m, n_router]; m <= 8, K = d <= 4096,
- * K % 32 == 0, n_pooler >= 8 m. cnt: 9 ints in device memory, zero before the first call and left zero by every
- * call (calls that may overlap on the GPU need one each). `status`: ST_X_TIMEOUT if a token never arrived. */
-int muse_boundary_pooler_router(const void* W_pooler, const void* W_router, const muse_boundary_t* bd, void* out_pooler,
-                                void* out_router, int m, int n_pooler, int n_router, int K, int ld_out_pooler,
-                                int ld_out_router, int* cnt, int* status, void* stream);
+ * router of best_submissions/muse_decode_layer.py:855-869, three launches on two streams there): one CTA per
+ * token computes its boundary once and publishes stream1 (where given), h (REQUIRED: the BF16 h, which is also
+ * the high half of the FP32 h), h_lo (REQUIRED scratch, BF16 [m, K]: bf16(h_fp32 - h)) and h_f32 (where given);
+ * every CTA waits for the m tokens with a bounded wait, then most CTAs walk the pooler's BF16 rows with h and the
+ * others the router's rows with h + h_lo against the router weight's BF16 hi + lo halves (W_router_hi / _lo:
+ * hi = bf16(W), lo = bf16(W - hi), as muse_skinny_tc takes them): x_hi W_hi + x_hi W_lo + x_lo W_hi, the sums
+ * muse_fewtok_f32 forms in its FP32-input mode. out_pooler: BF16 [m, n_pooler]; out_router: FP32 [m, n_router];
+ * m <= 8, K = d <= 4096, K % 32 == 0, n_pooler >= 8 m. cnt: 9 ints in device memory, zero before the first call
+ * and left zero by every call (calls that may overlap on the GPU need one each, and an h_lo each). `status`:
+ * ST_X_TIMEOUT if a token never arrived. */
+int muse_boundary_pooler_router(const void* W_pooler, const void* W_router_hi, const void* W_router_lo, const muse_boundary_t* bd,
+                                void* h_lo, void* out_pooler, void* out_router, int m, int n_pooler, int n_router, int K,
+                                int ld_out_pooler, int ld_out_router, int* cnt, int* status, void* stream);
 
 /* Staging for callers whose activations live in HOST memory (page-locked for the copies to be
  * asynchronous): x goes host -> device on `stream` before the projection is launched there, and

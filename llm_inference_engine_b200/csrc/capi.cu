@@ -29,8 +29,9 @@ int fewtok_rowpar_dispatch(const void* W, const void* x, void* out, int m, int N
 int attn_boundary_dispatch(const BoundaryArgs& bd, int m, int D, cudaStream_t stream);
 int fewtok_boundary_dispatch(const void* W, int w_is_f32, const BoundaryArgs& bd, void* out, int m, int N, int K, int ld_out,
                              int* status, cudaStream_t stream);
-int fused_boundary_dispatch(const void* Wp, const void* Wr, const BoundaryArgs& bd, void* outp, void* outr, int m, int Np, int Nr,
-                            int K, int ld_outp, int ld_outr, int* cnt, int* status, cudaStream_t stream);
+int fused_boundary_dispatch(const void* Wp, const void* Wr_hi, const void* Wr_lo, const BoundaryArgs& bd, void* h_lo, void* outp,
+                            void* outr, int m, int Np, int Nr, int K, int ld_outp, int ld_outr, int* cnt, int* status,
+                            cudaStream_t stream);
 int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m, int n,
                      int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups, int tile_rows,
                      int katoms, const PeerSync* peers, cudaStream_t stream);
@@ -142,12 +143,13 @@ int muse_fewtok_boundary(const void* W, int w_is_f32, const muse_boundary_t* bd,
                                         static_cast<cudaStream_t>(stream));
 }
 
-int muse_boundary_pooler_router(const void* W_pooler, const void* W_router, const muse_boundary_t* bd, void* out_pooler,
-                                void* out_router, int m, int n_pooler, int n_router, int K, int ld_out_pooler,
-                                int ld_out_router, int* cnt, int* status, void* stream) {
+int muse_boundary_pooler_router(const void* W_pooler, const void* W_router_hi, const void* W_router_lo, const muse_boundary_t* bd,
+                                void* h_lo, void* out_pooler, void* out_router, int m, int n_pooler, int n_router, int K,
+                                int ld_out_pooler, int ld_out_router, int* cnt, int* status, void* stream) {
   if (!bd) return -1;
-  return muse::fused_boundary_dispatch(W_pooler, W_router, *reinterpret_cast<const muse::BoundaryArgs*>(bd), out_pooler, out_router, m,
-                                       n_pooler, n_router, K, ld_out_pooler, ld_out_router, cnt, status, static_cast<cudaStream_t>(stream));
+  return muse::fused_boundary_dispatch(W_pooler, W_router_hi, W_router_lo, *reinterpret_cast<const muse::BoundaryArgs*>(bd), h_lo,
+                                       out_pooler, out_router, m, n_pooler, n_router, K, ld_out_pooler, ld_out_router, cnt, status,
+                                       static_cast<cudaStream_t>(stream));
 }
 
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,

@@ -760,12 +760,13 @@ __global__ void __launch_bounds__(256) attn_boundary_kernel(const __grid_constan
 // The three kernels the decode layer runs between the `o` projection and the experts (boundary, pooler, and the
 // router on a side stream: best_submissions/muse_decode_layer.py:855-869) as ONE launch for up to 8 tokens.
 // Every CTA first issues the weight loads of its first row group. One CTA per token then computes its boundary
-// (one 8-element chunk per thread, values in registers between the two CTA-wide reductions), writes stream1, the
-// BF16 h and the FP32 h to global memory and releases flag t. Every CTA waits (bounded) for the m flags and takes
-// its x from those rows: the first `pooler_ctas` CTAs walk the pooler's BF16 rows with BF16 fragments held in
-// registers (as fewtok_xreg_kernel), the others the router's FP32 rows with the FP32 h copied to shared memory
-// and split to hi + lo as it is read (three MMAs per weight half-pair), which leaves their registers for a whole
-// 8-row group of FP32 weight in flight at once. Rebuilding h in every CTA instead costs about a
+// (one 8-element chunk per thread, values in registers between the two CTA-wide reductions), writes stream1, h as
+// BF16 hi (the layer's BF16 h) + BF16 lo (the remainder of the FP32 value) and, where asked, the FP32 h to global
+// memory and releases flag t. Every CTA waits (bounded) for the m flags and takes its x from those rows: the first
+// `pooler_ctas` CTAs walk the pooler's BF16 rows with the hi fragments held in registers (as fewtok_xreg_kernel),
+// the others the router's rows, given as the BF16 hi + lo halves of the FP32 weight, with the hi and lo rows of h
+// copied to shared memory: x_hi W_hi + x_hi W_lo + x_lo W_hi, the three MMAs of the FP32-input mode with both
+// splits made once instead of per use, which leaves the registers for a whole 8-row group (hi and lo) in flight. Rebuilding h in every CTA instead costs about a
 // microsecond per token of shared-memory traffic on every SM; here it is computed once and read from L2.
 // The producers wait for nobody, so nothing can wait in a circle; the grid is at most one CTA per SM. The last
 // CTA to have read its fragments (a counter) puts the flags and the counter back to zero for the next call.
@@ -785,6 +786,10 @@ __device__ __forceinline__ uint4 ld_cg16(const void* p) {   // L2 load of data a
 
 constexpr int FB_NW = 16, FB_U = 8, FB_NT = FB_NW * 32;   // 512 threads: 16 warps x 8 pieces of 32 elements = K up to 4096
 constexpr int FB_DONE = BND_TOKENS;                        // cnt[0..7]: token ready flags; cnt[8]: CTAs that have read them
+// Every CTA but the producers sleeps this long before its first weight loads, so that the producers' 40 KB of
+// input is ahead of 12 MB of weight in the memory system's queues: measured on cold weights 8.0 / 8.7 / 10.0 us
+// per call at 1 / 4 / 8 tokens against 8.7 / 9.3 / 10.5 without (600 and 1000 ns: no better).
+constexpr int FB_STAGGER_NS = 300;
 
 // Sum over the CTA; every thread gets the total. red: [FB_NW] floats.
 __device__ __forceinline__ float fb_block_sum(float v, float* red) {
@@ -831,16 +836,18 @@ __device__ __forceinline__ void fb_store_group(const float (*red)[64], OutT* out
 }
 
 __global__ void __launch_bounds__(FB_NT, 1)
-fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restrict__ Wr, const __grid_constant__ BoundaryArgs bd,
-                      __nv_bfloat16* __restrict__ outp, float* __restrict__ outr, int m, int Np, int Nr, int K, int ld_outp,
-                      int ld_outr, int pooler_ctas, int* __restrict__ cnt, int* __restrict__ status) {
-  extern __shared__ __align__(16) float fb_x[];          // router CTAs: the FP32 h rows, [m][K + BND_PAD]
+fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const __nv_bfloat16* __restrict__ Wr_hi,
+                      const __nv_bfloat16* __restrict__ Wr_lo, const __grid_constant__ BoundaryArgs bd,
+                      __nv_bfloat16* __restrict__ h_lo, __nv_bfloat16* __restrict__ outp, float* __restrict__ outr, int m, int Np,
+                      int Nr, int K, int ld_outp, int ld_outr, int pooler_ctas, int stagger_ns, int* __restrict__ cnt,
+                      int* __restrict__ status) {
+  extern __shared__ __align__(16) uint8_t fb_x[];        // router CTAs: h hi rows then h lo rows, [2][m][2 K + pad]
   __shared__ __align__(16) float red[2][FB_NW][64];
   __shared__ float bsum[FB_NW];
   __shared__ __align__(8) uint64_t xbar;
   // Diagnostic builds: thread 0 of every CTA stamps the global nanosecond timer into its 16 slots (0 entry, 1 first
-  // loads issued, 2 token published (producers), 3 all tokens seen, 4 fragments ready, 5 first group multiplied,
-  // 6 exit).
+  // loads issued, 7 / 8 / 2 producers: input arrived / rows stored / token published, 3 all tokens seen,
+  // 4 fragments ready, 5 first group multiplied, 6 exit).
   unsigned long long* const trace = MUSE_TRACE_BASE();
   unsigned long long* const tr = trace && threadIdx.x == 0 ? trace + 16ull * blockIdx.x : nullptr;
 #define FB_STAMP(slot) do { if (tr) tr[slot] = global_ns(); } while (0)
@@ -848,67 +855,69 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int kblocks = K >> 5, first = warp * FB_U;
   bool ok;
+  int arrived = 0;   // thread 0: this CTA's number among those that have seen the tokens
 
   if (static_cast<int>(blockIdx.x) >= pooler_ctas) {
     // ================================================================ router CTAs
     const int C = static_cast<int>(gridDim.x) - pooler_ctas, c = static_cast<int>(blockIdx.x) - pooler_ctas;
     const int groups = (Nr + 7) >> 3, my_groups = c < groups ? (groups - c + C - 1) / C : 0;
-    const int xrow = K + BND_PAD;
+    const uint32_t xrow = static_cast<uint32_t>(K) * 2u + FEWTOK_X_PAD;
     if (threadIdx.x == 0) {
       mbar_init(smem_u32(&xbar), 1);
       fence_mbar_init();
     }
-    // A WHOLE group in flight: 8 pieces of 32 bytes (x stays in shared memory, which leaves the registers for it).
-    uint4 w[2 * FB_U];
+    if (stagger_ns > 0) __nanosleep(stagger_ns);   // the producers' input goes to the memory system first
+    // A WHOLE group in flight, hi and lo halves: 8 pieces of 16 bytes each (x stays in shared memory, which leaves
+    // the registers for it).
+    uint4 wh[FB_U], wl[FB_U];
     auto load = [&](int i) {
       int r = (c + i * C) * 8 + g;
       r = r < Nr ? r : Nr - 1;
-      const uint4* p = reinterpret_cast<const uint4*>(Wr + static_cast<size_t>(r) * K) + 2 * q;
+      const uint4* ph = reinterpret_cast<const uint4*>(Wr_hi + static_cast<size_t>(r) * K) + q;
+      const uint4* pl = reinterpret_cast<const uint4*>(Wr_lo + static_cast<size_t>(r) * K) + q;
 #pragma unroll
       for (int u = 0; u < FB_U; ++u) {
         const bool in = first + u < kblocks;
-        w[2 * u] = in ? ldg_stream16(p + (first + u) * 8) : make_uint4(0u, 0u, 0u, 0u);
-        w[2 * u + 1] = in ? ldg_stream16(p + (first + u) * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
+        wh[u] = in ? ldg_stream16(ph + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+        wl[u] = in ? ldg_stream16(pl + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
       }
     };
     if (my_groups > 0) load(0);
     FB_STAMP(1);
     ok = fb_wait_tokens(cnt, m);
+    if (threadIdx.x == 0) arrived = atomicAdd(cnt + FB_DONE, 1);   // consumed at the end: the round trip overlaps the walk
     FB_STAMP(3);
-    // The FP32 rows into shared memory by one thread's bulk copies (they were written through the generic proxy,
-    // hence the proxy fence).
+    // The rows into shared memory by one thread's bulk copies (they were written through the generic proxy, hence
+    // the proxy fence).
     if (ok && threadIdx.x == 0) {
       asm volatile("fence.proxy.async;" ::: "memory");
       mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(m) * static_cast<uint32_t>(K) * 4u);
-      for (int t = 0; t < m; ++t)
-        bulk_load_1d(smem_u32(fb_x + t * xrow), bd.h_f32 + static_cast<size_t>(t) * K, static_cast<uint32_t>(K) * 4u, smem_u32(&xbar));
+      for (int t = 0; t < m; ++t) {
+        bulk_load_1d(smem_u32(fb_x) + static_cast<uint32_t>(t) * xrow, bd.h + static_cast<size_t>(t) * K, static_cast<uint32_t>(K) * 2u,
+                     smem_u32(&xbar));
+        bulk_load_1d(smem_u32(fb_x) + static_cast<uint32_t>(m + t) * xrow, h_lo + static_cast<size_t>(t) * K,
+                     static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
+      }
     }
     if (ok) ok = __syncthreads_and(mbar_wait(smem_u32(&xbar), 0) ? 1 : 0) != 0;
     FB_STAMP(4);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint8_t* const xh = fb_x + static_cast<uint32_t>(g < m ? g : 0) * xrow + q * 16;
+    const uint8_t* const xl = xh + static_cast<uint32_t>(m) * xrow;
     for (int i = 0; i < (ok ? my_groups : 0); ++i) {
 #pragma unroll
       for (int u = 0; u < FB_U; ++u) {
         uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
         if (g < m && first + u < kblocks) {
-          const uint4* px = reinterpret_cast<const uint4*>(fb_x + g * xrow + (first + u) * 32 + q * 8);
-          const uint4 f0 = px[0], f1 = px[1];
-          split_hi_lo_pair(f0.x, f0.y, xa.x, xb.x);
-          split_hi_lo_pair(f0.z, f0.w, xa.y, xb.y);
-          split_hi_lo_pair(f1.x, f1.y, xa.z, xb.z);
-          split_hi_lo_pair(f1.z, f1.w, xa.w, xb.w);
+          xa = *reinterpret_cast<const uint4*>(xh + (first + u) * 64);
+          xb = *reinterpret_cast<const uint4*>(xl + (first + u) * 64);
         }
-        uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-        split_hi_lo_pair(w[2 * u].x, w[2 * u].y, h0, l0);
-        split_hi_lo_pair(w[2 * u].z, w[2 * u].w, h1, l1);
-        split_hi_lo_pair(w[2 * u + 1].x, w[2 * u + 1].y, h2, l2);
-        split_hi_lo_pair(w[2 * u + 1].z, w[2 * u + 1].w, h3, l3);
-        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, h0, h1);
-        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, h2, h3);
-        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, l0, l1);
-        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, l2, l3);
-        mma_bf16_16816(acc, xb.x, 0u, xb.y, 0u, h0, h1);
-        mma_bf16_16816(acc, xb.z, 0u, xb.w, 0u, h2, h3);
+        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, wh[u].x, wh[u].y);   // x_hi W_hi, x_hi W_lo, x_lo W_hi
+        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, wh[u].z, wh[u].w);
+        mma_bf16_16816(acc, xa.x, 0u, xa.y, 0u, wl[u].x, wl[u].y);
+        mma_bf16_16816(acc, xa.z, 0u, xa.w, 0u, wl[u].z, wl[u].w);
+        mma_bf16_16816(acc, xb.x, 0u, xb.y, 0u, wh[u].x, wh[u].y);
+        mma_bf16_16816(acc, xb.z, 0u, xb.w, 0u, wh[u].z, wh[u].w);
       }
       if (i + 1 < my_groups) load(i + 1);
       *reinterpret_cast<float2*>(&red[i & 1][warp][g * 8 + 2 * q]) = make_float2(acc[0], acc[1]);
@@ -947,7 +956,11 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restr
 #pragma unroll
       for (int u = 0; u < FB_U; ++u) w[u] = first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
     };
-    if (my_groups > 0) load(0);
+    // A producer loads its first weights only after it has published (its release would wait for them).
+    if (!producer) {
+      if (stagger_ns > 0) __nanosleep(stagger_ns);   // the producers' input goes to the memory system first
+      if (my_groups > 0) load(0);
+    }
     FB_STAMP(1);
     if (producer) {   // token `tok`'s boundary, one chunk of 8 elements per thread (K / 8 <= 512)
       float a[8], s1[8], ow[8];
@@ -972,11 +985,18 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restr
         float h[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) h[i] = s1[i] * r2 * (1.f + ow[i]);
-        float4* hf = reinterpret_cast<float4*>(bd.h_f32 + static_cast<size_t>(tok) * K) + 2 * ch;
-        hf[0] = make_float4(h[0], h[1], h[2], h[3]);
-        hf[1] = make_float4(h[4], h[5], h[6], h[7]);
-        reinterpret_cast<uint4*>(bd.h + static_cast<size_t>(tok) * K)[ch] =
-            make_uint4(pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7]));
+        if (bd.h_f32) {
+          float4* hf = reinterpret_cast<float4*>(bd.h_f32 + static_cast<size_t>(tok) * K) + 2 * ch;
+          hf[0] = make_float4(h[0], h[1], h[2], h[3]);
+          hf[1] = make_float4(h[4], h[5], h[6], h[7]);
+        }
+        uint4 hi, lo;   // h = hi + lo in BF16: hi is the layer's BF16 h, lo the remainder the router adds back
+        split_hi_lo_pair(__float_as_uint(h[0]), __float_as_uint(h[1]), hi.x, lo.x);
+        split_hi_lo_pair(__float_as_uint(h[2]), __float_as_uint(h[3]), hi.y, lo.y);
+        split_hi_lo_pair(__float_as_uint(h[4]), __float_as_uint(h[5]), hi.z, lo.z);
+        split_hi_lo_pair(__float_as_uint(h[6]), __float_as_uint(h[7]), hi.w, lo.w);
+        reinterpret_cast<uint4*>(bd.h + static_cast<size_t>(tok) * K)[ch] = hi;
+        reinterpret_cast<uint4*>(h_lo + static_cast<size_t>(tok) * K)[ch] = lo;
         if (bd.stream1) {
           float4* gp = reinterpret_cast<float4*>(bd.stream1 + static_cast<size_t>(tok) * K) + 2 * ch;
           gp[0] = make_float4(s1[0], s1[1], s1[2], s1[3]);
@@ -987,8 +1007,10 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restr
       FB_STAMP(8);
       if (threadIdx.x == 0) st_release_gpu(cnt + tok, 1);
       FB_STAMP(2);
+      if (my_groups > 0) load(0);
     }
     ok = fb_wait_tokens(cnt, m);
+    if (threadIdx.x == 0) arrived = atomicAdd(cnt + FB_DONE, 1);   // consumed at the end: the round trip overlaps the walk
     FB_STAMP(3);
     uint4 xr[FB_U];   // the BF16 fragments, straight from L2
 #pragma unroll
@@ -1012,15 +1034,10 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const float* __restr
     }
   }
   if (!ok && threadIdx.x == 0) atomicOr(status, ST_X_TIMEOUT);
-  // The fragments were consumed above. The last CTA to get here re-arms the flags for the next call.
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(cnt + FB_DONE, 1) == static_cast<int>(gridDim.x) - 1) {
-      for (int t = 0; t < BND_TOKENS; ++t) cnt[t] = 0;
-      __threadfence();
-      cnt[FB_DONE] = 0;
-    }
+  // Every CTA counted itself once it had seen the flags; the last one to do so re-arms them for the next call.
+  if (threadIdx.x == 0 && arrived == static_cast<int>(gridDim.x) - 1) {
+    for (int t = 0; t < BND_TOKENS; ++t) cnt[t] = 0;
+    cnt[FB_DONE] = 0;
   }
   FB_STAMP(6);
 #undef FB_STAMP
@@ -1156,38 +1173,43 @@ int fewtok_mma_dispatch(const void* W, const void* x, void* out, int m, int N, i
 
 // One launch for boundary -> pooler + router (up to 8 tokens, K <= 4096 in whole 32-element pieces, at least 8 m
 // pooler rows so that CTA t exists for every token t). At most one CTA per SM: the consumers of a token's h
-// spin while its producer runs. cnt: 9 ints, zero before the first call and again after every call.
-int fused_boundary_dispatch(const void* Wp, const void* Wr, const BoundaryArgs& bd, void* outp, void* outr, int m, int Np, int Nr,
-                            int K, int ld_outp, int ld_outr, int* cnt, int* status, cudaStream_t stream) {
-  if (!Wp || !Wr || !outp || !outr || !cnt || !status || Np <= 0 || Nr <= 0 || !bd.h || !bd.h_f32) return -1;
+// spin while its producer runs. cnt: 9 ints, zero before the first call and again after every call. h_lo: [m, K]
+// BF16 scratch the CTAs hand the low half of h to one another through.
+int fused_boundary_dispatch(const void* Wp, const void* Wr_hi, const void* Wr_lo, const BoundaryArgs& bd, void* h_lo, void* outp,
+                            void* outr, int m, int Np, int Nr, int K, int ld_outp, int ld_outr, int* cnt, int* status,
+                            cudaStream_t stream) {
+  if (!Wp || !Wr_hi || !Wr_lo || !h_lo || !outp || !outr || !cnt || !status || Np <= 0 || Nr <= 0 || !bd.h) return -1;
   const int bad = boundary_args_ok(bd, m, K);
   if (bad) return bad;
   if (m > BND_TOKENS) return -9;
   if (K % 32 != 0 || K / 32 > FB_NW * FB_U || ld_outp < Np || ld_outr < Nr) return -2;
-  if ((reinterpret_cast<uintptr_t>(Wp) | reinterpret_cast<uintptr_t>(Wr)) & 15) return -2;
+  if ((reinterpret_cast<uintptr_t>(Wp) | reinterpret_cast<uintptr_t>(Wr_hi) | reinterpret_cast<uintptr_t>(Wr_lo) |
+       reinterpret_cast<uintptr_t>(h_lo)) & 15)
+    return -2;
   static int sms[64] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= 64) return static_cast<int>(cudaErrorInvalidDevice);
+  const auto x_bytes = [](int tokens, int k) { return static_cast<size_t>(2 * tokens) * (static_cast<size_t>(k) * 2 + FEWTOK_X_PAD); };
   if (!sms[dev]) {
     int v = 0;
     if ((e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return static_cast<int>(e);
     if ((e = cudaFuncSetAttribute(fused_boundary_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(boundary_smem_bytes(4096)))) != cudaSuccess)
+                                  static_cast<int>(x_bytes(BND_TOKENS, FB_NW * FB_U * 32)))) != cudaSuccess)
       return static_cast<int>(e);
     sms[dev] = v;
   }
-  const size_t smem = static_cast<size_t>(m) * (K + BND_PAD) * sizeof(float);   // the router CTAs' copy of the FP32 h
   // The router's groups are twice the bytes of the pooler's: give each router group a CTA of its own (up to a
   // quarter of the SMs), the pooler the rest.
   const int gp = (Np + 7) / 8, gr = (Nr + 7) / 8;
-  int rc = gr < sms[dev] / 4 ? gr : sms[dev] / 4;
-  int pc = sms[dev] - rc < gp ? sms[dev] - rc : gp;
+  const int rc = gr < sms[dev] / 4 ? gr : sms[dev] / 4;
+  const int pc = sms[dev] - rc < gp ? sms[dev] - rc : gp;
   if (pc < m) return -9;   // one pooler CTA per token publishes it
-  fused_boundary_kernel<<<pc + rc, FB_NT, smem, stream>>>(reinterpret_cast<const __nv_bfloat16*>(Wp), reinterpret_cast<const float*>(Wr), bd,
-                                                           reinterpret_cast<__nv_bfloat16*>(outp), reinterpret_cast<float*>(outr), m, Np, Nr,
-                                                           K, ld_outp, ld_outr, pc, cnt, status);
+  fused_boundary_kernel<<<pc + rc, FB_NT, x_bytes(m, K), stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(Wp), reinterpret_cast<const __nv_bfloat16*>(Wr_hi), reinterpret_cast<const __nv_bfloat16*>(Wr_lo),
+      bd, reinterpret_cast<__nv_bfloat16*>(h_lo), reinterpret_cast<__nv_bfloat16*>(outp), reinterpret_cast<float*>(outr), m, Np, Nr, K,
+      ld_outp, ld_outr, pc, FB_STAGGER_NS, cnt, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -400,16 +400,15 @@ def boundary_pooler_router(data, state, stream1: torch.Tensor | None = None, h: 
     dev = stream_in.device
     out_p = torch.empty((m, wp.shape[0]), device=dev, dtype=torch.bfloat16)
     out_r = torch.empty((m, wr.shape[0]), device=dev, dtype=torch.float32)
-    if h is None:            # the kernel's CTAs hand h to one another through these rows
+    if h is None:            # the kernel's CTAs hand h to one another through this and a scratch for its low half
         h = torch.empty((m, k), device=dev, dtype=torch.bfloat16)
-    if h_f32 is None:
-        h_f32 = torch.empty((m, k), device=dev, dtype=torch.float32)
+    h_lo = torch.empty((m, k), device=dev, dtype=torch.bfloat16)
     bd = _boundary_args(state, stream_in, attn_out, stream1, h, h_f32)
     _, cnt = _stream_workspace(state, dev)
-    _capi.check(_capi.load().muse_boundary_pooler_router(wp.data_ptr(), wr.data_ptr(), ctypes.addressof(bd), out_p.data_ptr(),
-                                                         out_r.data_ptr(), m, wp.shape[0], wr.shape[0], k, wp.shape[0], wr.shape[0],
-                                                         cnt.data_ptr(), state["_status"].data_ptr(),
-                                                         torch.cuda.current_stream(dev).cuda_stream),
+    _capi.check(_capi.load().muse_boundary_pooler_router(wp.data_ptr(), state["_router_hi"].data_ptr(), state["_router_lo"].data_ptr(),
+                                                         ctypes.addressof(bd), h_lo.data_ptr(), out_p.data_ptr(), out_r.data_ptr(), m,
+                                                         wp.shape[0], wr.shape[0], k, wp.shape[0], wr.shape[0], cnt.data_ptr(),
+                                                         state["_status"].data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
                 f"muse_boundary_pooler_router(m={m}, k={k})")
     return out_p, out_r
 

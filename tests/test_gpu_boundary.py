@@ -120,6 +120,45 @@ def test_one_launch_boundary_pooler_router(oracle, proj, m):
         proj.boundary_pooler_router(big, state)
 
 
+def test_one_launch_replays_leave_the_flags_clear(oracle, proj):
+    """The kernel's CTAs hand h over through ready flags that the last CTA re-arms: 600 replays of one captured
+    call, with the inputs changed between two batches, give the eager results bit for bit, the flag words end at
+    zero and no wait ran out."""
+    layers = {name: oracle.TARGET_LAYERS[name] for name in ("pooler", "router")}
+    k = layers["pooler"][1]
+    state, _, _, _ = _state(oracle, proj, k, 43, layers)
+    m = 8
+    stream, attn_out, _, _ = oracle.boundary_inputs(m, k, 43)
+    data = {"stream": stream[:m].contiguous().to(DEV), "attn_out": attn_out[:m].contiguous().to(DEV)}
+    want = [t.clone() for t in proj.boundary_pooler_router(data, state)]
+    side = torch.cuda.Stream(DEV)
+    side.wait_stream(torch.cuda.current_stream(DEV))
+    with torch.cuda.stream(side):
+        proj.boundary_pooler_router(data, state)                        # this stream's workspace exists before the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            got = proj.boundary_pooler_router(data, state)
+        for _ in range(300):
+            graph.replay()
+        side.synchronize()
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+        data["stream"].mul_(1.5)
+        data["attn_out"].mul_(0.5)
+        for _ in range(300):
+            graph.replay()
+        side.synchronize()
+        key = side.cuda_stream
+    torch.cuda.current_stream(DEV).wait_stream(side)
+    want2 = proj.boundary_pooler_router(data, state)
+    torch.cuda.synchronize(DEV)
+    assert torch.equal(got[0], want2[0]) and torch.equal(got[1], want2[1])
+    assert not torch.equal(want2[0], want[0])
+    for _, cnt in state["_ws_by_stream"].values():
+        assert int(cnt[:16].abs().max()) == 0
+    assert key in state["_ws_by_stream"]
+    proj.check_status(state)
+
+
 def test_fused_boundary_rejections(oracle, proj):
     layers = {"pooler": oracle.TARGET_LAYERS["pooler"]}
     state, _, _, _ = _state(oracle, proj, 4096, 5, layers)
