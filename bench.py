@@ -526,6 +526,41 @@ def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
     return rows
 
 
+def zip12_table(h: Harness, steps: int, warmup: int) -> list[dict]:
+    """The lossless 12-bit weight form beside the plain walk (one GPU): us per call over rotating cold copies of
+    qkv_gate and o at 1 and 8 tokens, and the bytes each reads."""
+    proj = h.proj
+    rows = []
+    for layer in ("qkv_gate", "o"):
+        n, k = LAYERS[layer]
+        copies = max(6, min(40, -(-(640 << 20) // (n * k * 2))))
+        states = []
+        for i in range(copies):
+            st = proj.prepare({layer: make_weight(layer, h.device, SEED + 17 * i)}, warmup=(i == 0))
+            proj.prepare_zip12(st)
+            states.append(st)
+        z = states[0]["_zip12"][layer]
+        for m in (1, 8):
+            data = {"x": make_x(layer, m, h.device, 300 + m), "config": {"m": m, "n": n, "k": k, "layer": layer}}
+            row = {"layer": layer, "m": m, "copies": copies, "plain_bytes": n * k * 2, "zip12_bytes": z.nbytes,
+                   "outside_window": z.exceptions / (n * k)}
+            for name, fn in (("plain_us", proj.kernel_fn), ("zip12_us", proj.kernel_fn_zip12)):
+                keep = []
+
+                def body(fn=fn, keep=keep):
+                    keep.clear()
+                    for st in states:
+                        keep.append(fn(data, st))
+
+                row[name] = 1e3 * h.time_graph(body, steps, warmup) / copies
+            rows.append(row)
+        for st in states:
+            proj.check_status(st)
+        del states
+        torch.cuda.empty_cache()
+    return rows
+
+
 def run_e2e(h: Harness, states, steps: int, warmup: int) -> dict:
     """The same six calls through the public API from HOST buffers: per call, x is copied from pinned
     host memory, the projection runs, and the result is copied back to pinned host memory and waited
@@ -663,12 +698,14 @@ def run_ours(args) -> None:
 
     rows = []
     boundary_rows = []
+    zip_rows = []
     rowpar = None
     if not args.no_table:
         with sampler:
             rows = case_table(h, list(CASES), max(5, min(args.steps, 20)), args.warmup, peak)
             if world == 1:
                 boundary_rows = boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
+                zip_rows = zip12_table(h, max(5, min(args.steps, 20)), args.warmup)
             elif h.fused is not None:
                 rowpar = rowpar_table(h, max(5, min(args.steps, 20)), args.warmup)
 
@@ -734,6 +771,10 @@ def run_ours(args) -> None:
             "what": "us per (post-attention boundary -> pooler + router) of the decode layer, cold weights: boundary as its own "
                     "kernel (separate), as the prologue of both projections (fused), or all three as one launch (one_launch: muse_boundary_pooler_router); _fork = router on a side stream",
             "rows": [{k2: (round(v, 3) if isinstance(v, float) else v) for k2, v in r.items()} for r in boundary_rows]}
+    if zip_rows:
+        line["zip12"] = {"what": "us per call, cold weights: the plain register-MMA walk and the same walk over the lossless 12-bit "
+                                 "weight form (muse_fewtok_zip; not selected by the planner)",
+                         "rows": [{k2: (round(v, 5) if isinstance(v, float) else v) for k2, v in r.items()} for r in zip_rows]}
     if rowpar is not None:
         line["row_parallel_o"] = rowpar
     if cpu is not None:

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 15
+#define MUSE_PROJ_ABI_VERSION 16
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -127,6 +127,18 @@ int muse_fewtok_rowpar(const void* W, const void* x, void* out, int m, int N, in
  * out = x_hi (hi + lo) + x_lo hi. ld_x counts elements of x's type, ld_x % 8 == 0. */
 int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                     int tok_split, int x_is_f32, void* stream);
+
+/* out[m, N] = x . W^T for 1..8 tokens with W in the LOSSLESS 12-bit form of the reference author's experiment
+ * (bf16_proj/probe18.py:332-362 `_zip`; 25 % fewer bytes): `low` uint8 [N, K] raw low bytes, `code` uint8 [N, K/2]
+ * 4-bit codes (sign, index of the high byte in the 8-value window starting at `base`), `table` int32
+ * [ceil(N/8), cap, 2] = {row in group << 16 | column, FP32 bits of the true weight} for the weights outside the
+ * window ({-1, 0} = unused, last; cap <= 64, NULL when cap == 0), in the lane-major layouts that
+ * llm_inference_engine_b200/zip12.py documents and builds. The register-MMA walk of muse_fewtok_mma with the
+ * decode in registers: the same MMAs on the same BF16 values, plus x * true - x * coded in FP32 for the listed
+ * weights. K % 128 == 0, K <= 32 * warps * unroll, (warps, unroll) in {(32, 4), (16, 8), (16, 4)}, reduce_every = 1 or
+ * 2 row groups per CTA-wide reduction. No waits (x is read with plain loads): no status word. */
+int muse_fewtok_zip(const void* low, const void* code, const void* table, int cap, int base, const void* x, void* out, int m, int N,
+                    int K, int ld_x, int ld_out, int warps, int unroll, int reduce_every, void* stream);
 
 /* The post-attention boundary of the reference's decode layer, the producer of the pooler's and the router's
  * input (_attn_boundary_kernel, best_submissions/muse_decode_layer.py:694-712; decode_layer/reference.py:452-454),

@@ -32,6 +32,8 @@ int fewtok_boundary_dispatch(const void* W, int w_is_f32, const BoundaryArgs& bd
 int fused_boundary_dispatch(const void* Wp, const void* Wr_hi, const void* Wr_lo, const BoundaryArgs& bd, void* h_lo, void* outp,
                             void* outr, int m, int Np, int Nr, int K, int ld_outp, int ld_outr, int* cnt, int* status,
                             cudaStream_t stream);
+int fewtok_zip_dispatch(const void* lo, const void* nib, const void* exc, int cap, int base, const void* x, void* out, int m, int N,
+                        int K, int ld_x, int ld_out, int warps, int unroll, int reduce_every, cudaStream_t stream);
 int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m, int n,
                      int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups, int tile_rows,
                      int katoms, const PeerSync* peers, cudaStream_t stream);
@@ -150,6 +152,12 @@ int muse_boundary_pooler_router(const void* W_pooler, const void* W_router_hi, c
   return muse::fused_boundary_dispatch(W_pooler, W_router_hi, W_router_lo, *reinterpret_cast<const muse::BoundaryArgs*>(bd), h_lo,
                                        out_pooler, out_router, m, n_pooler, n_router, K, ld_out_pooler, ld_out_router, cnt, status,
                                        static_cast<cudaStream_t>(stream));
+}
+
+int muse_fewtok_zip(const void* low, const void* code, const void* table, int cap, int base, const void* x, void* out, int m, int N,
+                    int K, int ld_x, int ld_out, int warps, int unroll, int reduce_every, void* stream) {
+  return muse::fewtok_zip_dispatch(low, code, table, cap, base, x, out, m, N, K, ld_x, ld_out, warps, unroll, reduce_every,
+                                   static_cast<cudaStream_t>(stream));
 }
 
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,

@@ -413,6 +413,52 @@ def boundary_pooler_router(data, state, stream1: torch.Tensor | None = None, h: 
     return out_p, out_r
 
 
+def prepare_zip12(state, layers=None) -> dict:
+    """The lossless 12-bit form (zip12.encode) of the BF16 weights named in `layers` (default: all of them), kept in
+    `state` beside the weights for kernel_fn_zip12(). Returns {layer: exceptions / weights}; a layer the form does
+    not cover (K not a multiple of 128, too many weights outside the window in one row group) is left out."""
+    from . import zip12
+
+    done = {}
+    for name in (layers if layers is not None else [k for k in state if not k.startswith("_") and k not in FP32_LAYERS]):
+        w = state[name]
+        if w.dtype != torch.bfloat16:
+            raise TypeError(f"{name}: the 12-bit form is for BF16 weights")
+        z = zip12.encode(w)
+        if z is not None:
+            state.setdefault("_zip12", {})[name] = z
+            done[name] = z.exceptions / w.numel()
+    return done
+
+
+ZIP12_PLANS = ((4096, 32, 4), (2048, 16, 4))      # K up to -> (warps, unroll)
+
+
+def kernel_fn_zip12(data, state) -> torch.Tensor:
+    """kernel_fn through the 12-bit form of the weight (1..8 tokens, the whole weight: n = N): the same values as
+    the plain register-MMA walk gives, from 25 % fewer bytes. Not what kernel_fn() selects: on B200 it is no
+    faster than the plain walk (18.1-18.4 us against 18.1-18.4 us on qkv_gate, 8.9 against 8.3 on o)."""
+    cfg = data["config"]
+    layer, n = cfg["layer"], int(cfg["n"])
+    z = state.get("_zip12", {}).get(layer)
+    if z is None:
+        raise KeyError(f"{layer}: prepare_zip12() has not made a 12-bit form of this layer")
+    x = data["x"]
+    _require_cuda(x, "x")
+    m, k = x.shape
+    if x.dtype != torch.bfloat16 or k != z.k or n != z.n or not 1 <= m <= 8 or x.stride(1) != 1:
+        raise ValueError(f"{layer}: the 12-bit path takes BF16 x [1..8, {z.k}] and n = {z.n}; got {tuple(x.shape)} {x.dtype}, n={n}")
+    plan = next(((w, u) for kmax, w, u in ZIP12_PLANS[::-1] if k <= kmax), None)
+    if plan is None:
+        raise ValueError(f"{layer}: K = {k} is wider than the 12-bit kernel's 4096")
+    out = torch.empty((m, n), device=x.device, dtype=torch.bfloat16)
+    _capi.check(_capi.load().muse_fewtok_zip(z.low.data_ptr(), z.code.data_ptr(), z.table.data_ptr() if z.cap else None, z.cap, z.base,
+                                             x.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), n, plan[0], plan[1], 1,
+                                             torch.cuda.current_stream(x.device).cuda_stream),
+                f"muse_fewtok_zip({layer}, m={m}, n={n}, k={k})")
+    return out
+
+
 FETCH_X_BY_KERNEL = True
 STORE_OUT_BY_KERNEL = True   # the copy-out of the larger calls by the same small kernel (786 KB: 5 us less than the copy engine)
 FETCH_MAX_TOKENS = 32       # x up to 256 KB: the fetch kernel beats the copy engine at every size measured

@@ -334,3 +334,31 @@ def target_check(data, output, weights) -> tuple[bool, str]:
     excess = (output.float() - ref).abs() - (TARGET_BF16_ATOL + TARGET_BF16_RTOL * ref.abs())
     worst = float(excess.max())
     return worst <= 0, f"worst |out-ref| - (atol + rtol|ref|) = {worst:.3e} (must be <= 0)"
+
+
+def zip12_decode(low: torch.Tensor, code: torch.Tensor, table: torch.Tensor, base: int) -> torch.Tensor:
+    """The BF16 matrix a 12-bit form stands for (the inverse of the reference's `_zip`,
+    bf16_proj/probe18.py:332-362, for the lane-major layouts the CUDA kernel reads): raw low byte, high byte =
+    sign << 7 | base + index from the 4-bit code, and the table's true values put back where the code could not
+    hold them. Plain index arithmetic, no shared code with the encoder's permutes."""
+    n, k = low.shape
+    low, code = low.cpu().to(torch.int32), code.cpu().to(torch.int32)
+    rows = torch.arange(n).view(n, 1).expand(n, k)
+    col = torch.arange(k).view(1, k).expand(n, k)
+    piece, within = col // 32, col % 32
+    q, j = within // 8, within % 8                                   # lane of the piece, weight of the lane
+    low_at = (piece // 2) * 64 + q * 16 + (piece % 2) * 8 + j
+    code_at = (piece // 4) * 64 + q * 16 + (piece % 4) * 4 + (j % 4)
+    lo = torch.gather(low, 1, low_at)
+    nb = torch.gather(code, 1, code_at)
+    c = torch.where(j < 4, nb & 15, nb >> 4)
+    hi = ((c & 8) << 4) | ((c & 7) + base)
+    bits = (hi << 8) | lo
+    out = (bits - ((bits >= 32768).to(torch.int32) << 16)).to(torch.int16).view(torch.bfloat16).clone()   # 16-bit pattern -> BF16
+    t = table.cpu()
+    if t.numel():
+        grp, slot = (t[:, :, 0] >= 0).nonzero(as_tuple=True)
+        rc = t[grp, slot, 0]
+        vals = t[grp, slot, 1].contiguous().view(torch.float32)
+        out[grp * 8 + (rc >> 16), rc & 0xFFFF] = vals.to(torch.bfloat16)
+    return out
