@@ -460,7 +460,7 @@ def rowpar_table(h: Harness, steps: int, warmup: int) -> dict:
                     "nccl_us = kernel + NCCL all-reduce of BF16 partials, kernel_us = local kernel alone"}
 
 
-def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
+def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = None) -> list[dict]:
     """The path's first caller beyond the five projections (one GPU): the decode layer's post-attention boundary
     feeding the pooler and, up to 8 tokens in FP32, the router. Per token count, one graph per variant over
     rotating cold weight copies: the boundary as a kernel of its own in front of the two projections, and the
@@ -480,6 +480,8 @@ def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
     side = torch.cuda.Stream(h.device)
     rows = []
     for m in (1, 4, 8):
+        if only_m is not None and m != only_m:   # one case, the one-launch form only: the command ncu wraps
+            continue
         k = LAYERS["pooler"][1]
         g = torch.Generator(device=h.device).manual_seed(50 + m)
         stream_in = torch.randn((m, k), device=h.device, generator=g)
@@ -489,6 +491,8 @@ def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
         row = {"m": m, "copies": copies}
         for fused in (False, True):
             for fork in (False, True):
+                if only_m is not None:
+                    continue
                 keep = []
 
                 def fn(fused=fused, fork=fork, keep=keep):
@@ -526,12 +530,14 @@ def boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
     return rows
 
 
-def zip12_table(h: Harness, steps: int, warmup: int) -> list[dict]:
+def zip12_table(h: Harness, steps: int, warmup: int, only=None) -> list[dict]:
     """The lossless 12-bit weight form beside the plain walk (one GPU): us per call over rotating cold copies of
     qkv_gate and o at 1 and 8 tokens, and the bytes each reads."""
     proj = h.proj
     rows = []
     for layer in ("qkv_gate", "o"):
+        if only and only[0] != layer:
+            continue
         n, k = LAYERS[layer]
         copies = max(6, min(40, -(-(640 << 20) // (n * k * 2))))
         states = []
@@ -541,6 +547,8 @@ def zip12_table(h: Harness, steps: int, warmup: int) -> list[dict]:
             states.append(st)
         z = states[0]["_zip12"][layer]
         for m in (1, 8):
+            if only and only[1] != m:
+                continue
             data = {"x": make_x(layer, m, h.device, 300 + m), "config": {"m": m, "n": n, "k": k, "layer": layer}}
             row = {"layer": layer, "m": m, "copies": copies, "plain_bytes": n * k * 2, "zip12_bytes": z.nbytes,
                    "outside_window": z.exceptions / (n * k)}
@@ -662,7 +670,12 @@ def run_ours(args) -> None:
     if args.case:  # single case, few launches: the command ncu wraps
         layer, m = args.case.split(":")
         with sampler:
-            rows = case_table(h, [layer], args.steps, args.warmup, peak, only=(layer, int(m)))
+            if layer == "boundary_pooler_router":        # the one-launch boundary + pooler + router at m tokens
+                rows = boundary_table(h, args.steps, args.warmup, only_m=int(m))
+            elif layer.startswith("zip12_"):             # zip12_qkv_gate:8, zip12_o:1: plain walk and 12-bit walk
+                rows = zip12_table(h, args.steps, args.warmup, only=(layer[6:], int(m)))
+            else:
+                rows = case_table(h, [layer], args.steps, args.warmup, peak, only=(layer, int(m)))
         if rank == 0:
             emit({"case": rows[0], "clocks": sampler.summary()})
         return
