@@ -530,6 +530,52 @@ def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = Non
     return rows
 
 
+def ffn_boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
+    """The other caller-side step (one GPU): the unpooler's 1024-row slice followed by the post-FFN boundary, as two
+    kernels (projection, boundary) and as one launch (muse_unpooler_ffn_boundary), per token count over rotating
+    cold weight copies."""
+    proj = h.proj
+    n, k = LAYERS["unpooler"]
+    nf = 1024                                   # this GPU's slice of the unpooler's rows up to 8 tokens
+    copies = 80
+    gen = lambda seed: torch.Generator(device=h.device).manual_seed(seed)  # noqa: E731
+    gate = torch.randn(n, device=h.device, generator=gen(5)) * 0.3
+    post_w = (torch.randn(n, device=h.device, generator=gen(6)) * 0.1).bfloat16()
+    next_w = (torch.randn(n, device=h.device, generator=gen(7)) * 0.1).bfloat16()
+    states = []
+    for i in range(copies):
+        st = proj.prepare({"unpooler": make_weight("unpooler", h.device, SEED + 13 * i)}, warmup=(i == 0))
+        proj.prepare_ffn_boundary(st, gate, post_w, next_w)
+        states.append(st)
+    rows = []
+    for m in (1, 4, 8):
+        x = make_x("unpooler", m, h.device, 400 + m)
+        stream1 = torch.randn((m, n), device=h.device, generator=gen(80 + m))
+        cfg = {"m": m, "n": nf, "k": k, "layer": "unpooler"}
+        row = {"m": m, "nf": nf, "copies": copies}
+        keep = []
+
+        def two(keep=keep):
+            keep.clear()
+            for st in states:
+                f = proj.kernel_fn({"x": x, "config": cfg}, st)
+                keep.append(proj.ffn_boundary(stream1, f, st))
+
+        def one(keep=keep):
+            keep.clear()
+            for st in states:
+                keep.append(proj.unpooler_ffn_boundary({"x": x, "stream1": stream1, "config": cfg}, st))
+
+        row["separate_us"] = 1e3 * h.time_graph(two, steps, warmup) / copies
+        row["one_launch_us"] = 1e3 * h.time_graph(one, steps, warmup) / copies
+        rows.append(row)
+    for st in states:
+        proj.check_status(st)
+    del states
+    torch.cuda.empty_cache()
+    return rows
+
+
 def zip12_table(h: Harness, steps: int, warmup: int, only=None) -> list[dict]:
     """The lossless 12-bit weight form beside the plain walk (one GPU): us per call over rotating cold copies of
     qkv_gate and o at 1 and 8 tokens, and the bytes each reads."""
@@ -663,8 +709,9 @@ def run_ours(args) -> None:
     if args.boundary_only:
         with sampler:
             table = boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
+            ffn = ffn_boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
         if rank == 0:
-            emit({"boundary_pooler_router": table, "clocks": sampler.summary()})
+            emit({"boundary_pooler_router": table, "unpooler_ffn_boundary": ffn, "clocks": sampler.summary()})
         return
 
     if args.case:  # single case, few launches: the command ncu wraps
@@ -712,12 +759,14 @@ def run_ours(args) -> None:
     rows = []
     boundary_rows = []
     zip_rows = []
+    ffn_rows = []
     rowpar = None
     if not args.no_table:
         with sampler:
             rows = case_table(h, list(CASES), max(5, min(args.steps, 20)), args.warmup, peak)
             if world == 1:
                 boundary_rows = boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
+                ffn_rows = ffn_boundary_table(h, max(5, min(args.steps, 20)), args.warmup)
                 zip_rows = zip12_table(h, max(5, min(args.steps, 20)), args.warmup)
             elif h.fused is not None:
                 rowpar = rowpar_table(h, max(5, min(args.steps, 20)), args.warmup)
@@ -784,6 +833,11 @@ def run_ours(args) -> None:
             "what": "us per (post-attention boundary -> pooler + router) of the decode layer, cold weights: boundary as its own "
                     "kernel (separate), as the prologue of both projections (fused), or all three as one launch (one_launch: muse_boundary_pooler_router); _fork = router on a side stream",
             "rows": [{k2: (round(v, 3) if isinstance(v, float) else v) for k2, v in r.items()} for r in boundary_rows]}
+    if ffn_rows:
+        line["unpooler_ffn_boundary"] = {
+            "what": "us per (unpooler slice of 1024 rows -> post-FFN boundary) of the decode layer, cold weights: projection and "
+                    "boundary as two kernels (separate) or as one launch (one_launch: muse_unpooler_ffn_boundary)",
+            "rows": [{k2: (round(v, 3) if isinstance(v, float) else v) for k2, v in r.items()} for r in ffn_rows]}
     if zip_rows:
         line["zip12"] = {"what": "us per call, cold weights: the plain register-MMA walk and the same walk over the lossless 12-bit "
                                  "weight form (muse_fewtok_zip; not selected by the planner)",

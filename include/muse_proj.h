@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 16
+#define MUSE_PROJ_ABI_VERSION 17
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -127,6 +127,35 @@ int muse_fewtok_rowpar(const void* W, const void* x, void* out, int m, int N, in
  * out = x_hi (hi + lo) + x_lo hi. ld_x counts elements of x's type, ld_x % 8 == 0. */
 int muse_fewtok_f32(const void* W, const void* x, void* out, int m, int N, int K, int ld_x, int ld_out, int unroll,
                     int tok_split, int x_is_f32, void* stream);
+
+/* The post-FFN boundary of the reference's decode layer, the consumer of the unpooler's output
+ * (_ffn_boundary_kernel, best_submissions/muse_decode_layer.py:715-730; decode_layer/reference.py:466-476), per
+ * token over the hidden width d, f being the unpooler's output of nf <= d columns (zero beyond: up to 8 tokens a
+ * GPU computes only its slice):
+ *     f'      = f * (1 + post_w)
+ *     stream2 = alpha * stream1 + beta * f' * rsqrt(mean(f'^2) + 1e-8)
+ *     hidden  = stream2 * rsqrt(mean(stream2^2) + 1e-5) * (1 + next_w)         (the next layer's attention input)
+ * stream1, stream2: FP32 [m, d]; hidden: BF16 [m, d]; alpha, beta: FP32 [d]; post_w, next_w: BF16 [d]. All
+ * contiguous, 16-byte aligned; d % 8 == 0, d <= 8192, nf % 8 == 0. */
+typedef struct muse_ffn_boundary {
+  const float* stream1;
+  const float* alpha;
+  const float* beta;
+  const void* post_w;
+  const void* next_w;
+  float* stream2;   /* output, may be NULL */
+  void* hidden;     /* output */
+} muse_ffn_boundary_t;
+/* Stand-alone: one CTA per token, f BF16 [m, nf] contiguous (the projection's output). */
+int muse_ffn_boundary(const muse_ffn_boundary_t* bd, const void* f, int m, int d, int nf, void* stream);
+/* The unpooler projection and the boundary as ONE launch (lines 869-877 of the reference's layer, two launches
+ * there): f = x . W[nf, K]^T by the register-MMA walk of muse_fewtok_mma, kept in FP32 in f_scratch [m, nf]; every
+ * CTA counts itself done and CTA t < m then computes token t after a bounded wait for the count. m <= 8,
+ * K <= 4096, K % 32 == 0, nf >= 8 m. cnt: 2 ints in device memory, zero before the first call and left zero by
+ * every call (one per stream that may run such calls at once, and a scratch each). `status`: ST_X_TIMEOUT if the
+ * count never completed. */
+int muse_unpooler_ffn_boundary(const void* W, const void* x, void* f_scratch, const muse_ffn_boundary_t* bd, int m, int nf, int K, int ld_x,
+                               int d, int* cnt, int* status, void* stream);
 
 /* out[m, N] = x . W^T for 1..8 tokens with W in the LOSSLESS 12-bit form of the reference author's experiment
  * (bf16_proj/probe18.py:332-362 `_zip`; 25 % fewer bytes): `low` uint8 [N, K] raw low bytes, `code` uint8 [N, K/2]

@@ -49,6 +49,9 @@ SIGNATURES = {
                                               C.c_void_p]),
     "muse_fewtok_zip": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "muse_ffn_boundary": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "muse_unpooler_ffn_boundary": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                             C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "muse_gemm_tc_smem_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_gemm_tc_max_clusters": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "muse_gemm_tc_ws_floats": (C.c_longlong, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
@@ -63,7 +66,7 @@ SIGNATURES = {
                                          C.c_void_p]),
 }
 
-ABI_VERSION = 16
+ABI_VERSION = 17
 
 
 class MuseError(RuntimeError):
@@ -118,6 +121,13 @@ class Boundary(C.Structure):
 
     _fields_ = [("stream", C.c_void_p), ("attn_out", C.c_void_p), ("alpha", C.c_void_p), ("beta", C.c_void_p),
                 ("norm_w", C.c_void_p), ("stream1", C.c_void_p), ("h", C.c_void_p), ("h_f32", C.c_void_p)]
+
+
+class FfnBoundary(C.Structure):
+    """muse_ffn_boundary_t: the operands of the post-FFN boundary (muse_proj.h)."""
+
+    _fields_ = [("stream1", C.c_void_p), ("alpha", C.c_void_p), ("beta", C.c_void_p), ("post_w", C.c_void_p),
+                ("next_w", C.c_void_p), ("stream2", C.c_void_p), ("hidden", C.c_void_p)]
 
 
 class TensorMap:

@@ -20,7 +20,7 @@ CSRC = PKG_DIR / "csrc"
 # stamp their phases; the ordinary library carries none of that code.
 TRACE = bool(os.environ.get("MUSE_TRACE"))
 LIB_PATH = PKG_DIR / ("libmuse_proj_trace.so" if TRACE else "libmuse_proj.so")
-SOURCES = ["gemv1.cu", "fewtok_mma.cu", "fewtok_zip.cu", "skinny_tc.cu", "gemm_tc.cu", "capi.cu"]
+SOURCES = ["gemv1.cu", "fewtok_mma.cu", "fewtok_zip.cu", "ffn_boundary.cu", "skinny_tc.cu", "gemm_tc.cu", "capi.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

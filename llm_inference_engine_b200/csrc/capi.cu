@@ -34,6 +34,10 @@ int fused_boundary_dispatch(const void* Wp, const void* Wr_hi, const void* Wr_lo
                             cudaStream_t stream);
 int fewtok_zip_dispatch(const void* lo, const void* nib, const void* exc, int cap, int base, const void* x, void* out, int m, int N,
                         int K, int ld_x, int ld_out, int warps, int unroll, int reduce_every, cudaStream_t stream);
+struct FfnBoundaryArgs;
+int ffn_boundary_dispatch(const FfnBoundaryArgs& a, const void* f, int m, int D, int nf, cudaStream_t stream);
+int unpooler_ffn_dispatch(const void* W, const void* x, void* f_scratch, const FfnBoundaryArgs& a, int m, int NF, int K, int ld_x, int D,
+                          int* cnt, int* status, cudaStream_t stream);
 int gemm_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* tx, void* out, float* ws, int* cnt, int* status, int m, int n,
                      int k, int ld_out, int ntok, int pair, int cluster, int split, int stages, int warpgroups, int tile_rows,
                      int katoms, const PeerSync* peers, cudaStream_t stream);
@@ -158,6 +162,18 @@ int muse_fewtok_zip(const void* low, const void* code, const void* table, int ca
                     int K, int ld_x, int ld_out, int warps, int unroll, int reduce_every, void* stream) {
   return muse::fewtok_zip_dispatch(low, code, table, cap, base, x, out, m, N, K, ld_x, ld_out, warps, unroll, reduce_every,
                                    static_cast<cudaStream_t>(stream));
+}
+
+int muse_ffn_boundary(const muse_ffn_boundary_t* bd, const void* f, int m, int d, int nf, void* stream) {
+  if (!bd) return -1;
+  return muse::ffn_boundary_dispatch(*reinterpret_cast<const muse::FfnBoundaryArgs*>(bd), f, m, d, nf, static_cast<cudaStream_t>(stream));
+}
+
+int muse_unpooler_ffn_boundary(const void* W, const void* x, void* f_scratch, const muse_ffn_boundary_t* bd, int m, int nf, int K, int ld_x,
+                               int d, int* cnt, int* status, void* stream) {
+  if (!bd) return -1;
+  return muse::unpooler_ffn_dispatch(W, x, f_scratch, *reinterpret_cast<const muse::FfnBoundaryArgs*>(bd), m, nf, K, ld_x, d, cnt, status,
+                                     static_cast<cudaStream_t>(stream));
 }
 
 int muse_gemv1(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll, int persistent,

@@ -413,6 +413,85 @@ def boundary_pooler_router(data, state, stream1: torch.Tensor | None = None, h: 
     return out_p, out_r
 
 
+def prepare_ffn_boundary(state, ffn_residual_gate: torch.Tensor, post_ffn_norm: torch.Tensor, next_pre_attn_norm: torch.Tensor) -> None:
+    """Once per layer: the residual coefficients of the FFN gate as FP32 vectors and the two BF16 norm weights
+    (decode_layer/reference.py:473-476), kept in `state` for ffn_boundary() and unpooler_ffn_boundary()."""
+    for name, t in (("ffn_residual_gate", ffn_residual_gate), ("post_ffn_norm", post_ffn_norm), ("next_pre_attn_norm", next_pre_attn_norm)):
+        _require_cuda(t, name)
+    w = ffn_residual_gate.float() / RESIDUAL_TEMPERATURE
+    beta = torch.sigmoid(w)
+    alpha = torch.sqrt(torch.clamp(torch.sigmoid(-w) * (1.0 + beta), min=RESIDUAL_GATE_EPS))
+    state["_ffn_boundary"] = (alpha.contiguous(), beta.contiguous(), post_ffn_norm.to(torch.bfloat16).contiguous(),
+                              next_pre_attn_norm.to(torch.bfloat16).contiguous())
+
+
+def _ffn_boundary_args(state, stream1: torch.Tensor, stream2, hidden: torch.Tensor) -> _capi.FfnBoundary:
+    if "_ffn_boundary" not in state:
+        raise RuntimeError("prepare_ffn_boundary(state, ffn_residual_gate, post_ffn_norm, next_pre_attn_norm) has not been called")
+    alpha, beta, post_w, next_w = state["_ffn_boundary"]
+    _require_cuda(stream1, "stream1")
+    m, d = stream1.shape
+    if stream1.dtype != torch.float32 or not stream1.is_contiguous() or alpha.numel() != d or d % 8 or d > 8192:
+        raise TypeError("stream1 must be contiguous FP32 [m, D], D as prepared, a multiple of 8 and at most 8192")
+    bd = _capi.FfnBoundary()
+    bd.stream1, bd.alpha, bd.beta, bd.post_w, bd.next_w = (stream1.data_ptr(), alpha.data_ptr(), beta.data_ptr(), post_w.data_ptr(),
+                                                           next_w.data_ptr())
+    for name, t, dt in (("stream2", stream2, torch.float32), ("hidden", hidden, torch.bfloat16)):
+        if t is not None:
+            if not t.is_cuda or t.dtype != dt or tuple(t.shape) != (m, d) or not t.is_contiguous():
+                raise TypeError(f"{name} must be a contiguous CUDA {dt} [m, D] tensor")
+            setattr(bd, name, t.data_ptr())
+    return bd
+
+
+def ffn_boundary(stream1: torch.Tensor, f: torch.Tensor, state):
+    """The post-FFN boundary as a kernel of its own (any m): f = the unpooler's BF16 output [m, nf], nf the hidden
+    width or this GPU's slice of it (the other columns count as zero). Returns (stream2 FP32, the next layer's
+    attention input BF16) (best_submissions/muse_decode_layer.py:715-730 and its call at :874-877)."""
+    m, d = stream1.shape
+    _require_cuda(f, "f")
+    if f.dtype != torch.bfloat16 or f.dim() != 2 or f.shape[0] != m or not f.is_contiguous() or f.shape[1] % 8 or f.shape[1] > d:
+        raise TypeError("f must be contiguous BF16 [m, nf] with nf a multiple of 8 and at most D")
+    stream2 = torch.empty_like(stream1)
+    hidden = torch.empty((m, d), device=stream1.device, dtype=torch.bfloat16)
+    bd = _ffn_boundary_args(state, stream1, stream2, hidden)
+    _capi.check(_capi.load().muse_ffn_boundary(ctypes.addressof(bd), f.data_ptr(), m, d, f.shape[1],
+                                               torch.cuda.current_stream(stream1.device).cuda_stream),
+                f"muse_ffn_boundary(m={m}, d={d}, nf={f.shape[1]})")
+    return stream2, hidden
+
+
+def unpooler_ffn_boundary(data, state):
+    """The unpooler projection and the post-FFN boundary as one launch (two in the reference's layer,
+    best_submissions/muse_decode_layer.py:869-877): data = {"x": BF16 [m, K] (the experts' output), "stream1":
+    FP32 [m, D], "config": {"layer": "unpooler", "n": nf, ...}} with m <= 8; nf rows of the unpooler weight are
+    used (the whole weight, or this GPU's slice). Returns (stream2 FP32, next attention input BF16); f itself
+    stays in an FP32 scratch (it is not rounded to BF16 on the way, unlike the two-kernel route)."""
+    cfg = data["config"]
+    layer, nf = cfg.get("layer", "unpooler"), int(cfg["n"])
+    w = state[layer]
+    x, stream1 = data["x"], data["stream1"]
+    _require_cuda(x, "x")
+    m, k = x.shape
+    d = stream1.shape[1]
+    if x.dtype != torch.bfloat16 or k != w.shape[1] or x.stride(1) != 1 or stream1.shape[0] != m:
+        raise ValueError(f"{layer}: x {tuple(x.shape)} {x.dtype} / stream1 {tuple(stream1.shape)} do not fit W {tuple(w.shape)}")
+    if m > BOUNDARY_FUSED_MAX_TOKENS or k > 4096 or k % 32 or nf % 8 or not 8 * m <= nf <= min(w.shape[0], d):
+        raise ValueError(f"the fused form serves m <= {BOUNDARY_FUSED_MAX_TOKENS}, K <= 4096 in whole 32-element pieces and "
+                         f"8 m <= nf <= min(N, D) in multiples of 8; got m={m}, K={k}, nf={nf}")
+    dev = x.device
+    stream2 = torch.empty_like(stream1)
+    hidden = torch.empty((m, d), device=dev, dtype=torch.bfloat16)
+    scratch = torch.empty((m, nf), device=dev, dtype=torch.float32)
+    bd = _ffn_boundary_args(state, stream1, stream2, hidden)
+    _, cnt = _stream_workspace(state, dev)
+    _capi.check(_capi.load().muse_unpooler_ffn_boundary(w.data_ptr(), x.data_ptr(), scratch.data_ptr(), ctypes.addressof(bd), m, nf, k,
+                                                        x.stride(0), d, cnt[16:].data_ptr(), state["_status"].data_ptr(),
+                                                        torch.cuda.current_stream(dev).cuda_stream),
+                f"muse_unpooler_ffn_boundary(m={m}, nf={nf}, k={k}, d={d})")
+    return stream2, hidden
+
+
 def prepare_zip12(state, layers=None) -> dict:
     """The lossless 12-bit form (zip12.encode) of the BF16 weights named in `layers` (default: all of them), kept in
     `state` beside the weights for kernel_fn_zip12(). Returns {layer: exceptions / weights}; a layer the form does

@@ -276,6 +276,37 @@ def attn_boundary(stream: torch.Tensor, attn_out: torch.Tensor, gate: torch.Tens
     return stream1, h
 
 
+def ffn_boundary(stream1: torch.Tensor, f: torch.Tensor, gate: torch.Tensor, post_ffn_norm: torch.Tensor,
+                 next_pre_attn_norm: torch.Tensor):
+    """decode_layer/reference.py:466-476 (the tail of ref_back): the unpooler's output f [m, nf] (nf = the hidden
+    width, or this GPU's first UNPOOL_SLICE columns up to 8 tokens, the other columns being the all-gather's
+    zeros) scaled by (1 + post_ffn_norm), joined to the residual stream, and the next layer's pre-attention norm:
+        f' = pad(f) * (1 + post_ffn_norm);  stream2 = alpha * stream1 + beta * rms(f', 1e-8);
+        hidden = rms(stream2, 1e-5) * (1 + next_pre_attn_norm)           (both returned in FP32).
+    The submission's kernel for it is best_submissions/muse_decode_layer.py:715-730."""
+    m, d = stream1.shape
+    full = torch.zeros((m, d), dtype=torch.float32, device=stream1.device)
+    full[:, : f.shape[1]] = f.float()
+    full = full * (1.0 + post_ffn_norm.float())
+    alpha, beta = residual_coefficients(gate)
+    stream2 = alpha * stream1.float() + beta * rms(full, POST_NORM_EPS)
+    hidden = rms(stream2) * (1.0 + next_pre_attn_norm.float())
+    return stream2, hidden
+
+
+def ffn_boundary_inputs(m: int, d: int, nf: int, seed: int, device: str = "cpu"):
+    """Seeded inputs of the post-FFN boundary: FP32 stream1 with a shared mean direction, the unpooler output
+    f [m, nf] in BF16, a residual gate ~ N(0, 0.3) and the two norm weights ~ N(0, 0.1) in BF16."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    mean = torch.randn((d,), generator=g, device=device)
+    stream1 = 0.7 * mean + torch.randn((m, d), generator=g, device=device)
+    f = (0.4 * torch.randn((m, nf), generator=g, device=device)).to(torch.bfloat16)
+    gate = 0.3 * torch.randn((d,), generator=g, device=device)
+    post_w = (0.1 * torch.randn((d,), generator=g, device=device)).to(torch.bfloat16)
+    next_w = (0.1 * torch.randn((d,), generator=g, device=device)).to(torch.bfloat16)
+    return stream1, f, gate, post_w, next_w
+
+
 def boundary_inputs(m: int, d: int, seed: int, device: str = "cpu"):
     """Seeded inputs of the boundary in the shapes and types the decode layer hands over: FP32 stream with a
     shared mean direction (rows are far from zero-mean, as in decode_layer/reference.py:132-137), BF16

@@ -42,7 +42,7 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     assert _capi.LL_TOKENS == plan.LL_TOKENS == int(re.search(r"MUSE_LL_TOKENS\s+(\d+)", HEADER).group(1))
     assert _capi.RP_TOKENS == int(re.search(r"MUSE_RP_TOKENS\s+(\d+)", HEADER).group(1))
     assert ctypes.sizeof(_capi.PeerSync) == 16 + 3 * 8 * _capi.MAX_WORLD
-    assert ctypes.sizeof(_capi.Boundary) == 8 * 8
+    assert ctypes.sizeof(_capi.Boundary) == 8 * 8 and ctypes.sizeof(_capi.FfnBoundary) == 7 * 8
 
 
 def test_pure_host_entry_points_without_a_gpu():

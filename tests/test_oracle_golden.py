@@ -157,3 +157,14 @@ def test_boundary_restatement_is_bit_identical(oracle, rec):
     stream1, h = oracle.attn_boundary(stream, attn_out, gate, norm_w)
     assert head(stream1) == rec["stream1_head"] and digest(stream1) == rec["stream1_sha256"]
     assert head(h) == rec["h_head"] and digest(h) == rec["h_sha256"]
+
+
+@pytest.mark.parametrize("rec", BOUNDARY["ffn_cases"], ids=lambda r: "m{}_d{}_nf{}".format(r["m"], r["d"], r["nf"]))
+def test_ffn_boundary_restatement_is_bit_identical(oracle, rec):
+    """The post-FFN boundary (the tail of ref_back, decode_layer/reference.py:466-476) as restated in the oracle,
+    on inputs regenerated from the recorded seeds."""
+    stream1, f, gate, post_w, next_w = oracle.ffn_boundary_inputs(rec["m"], rec["d"], rec["nf"], rec["seed"])
+    assert digest(torch.cat([stream1.flatten(), f.float().flatten(), gate, post_w.float(), next_w.float()])) == rec["inputs_sha256"]
+    stream2, hidden = oracle.ffn_boundary(stream1, f, gate, post_w, next_w)
+    assert head(stream2) == rec["stream2_head"] and digest(stream2) == rec["stream2_sha256"]
+    assert head(hidden) == rec["hidden_head"] and digest(hidden) == rec["hidden_sha256"]
