@@ -702,6 +702,10 @@ def run_ours(args) -> None:
 
         dist.init_process_group("nccl", device_id=device)
     h = Harness(device, world, rank)
+    if args.no_programmatic_launch:
+        from llm_inference_engine_b200 import _capi
+
+        _capi.load().muse_set_programmatic_launch(0)
     peak, peak_kind = measured_peak()
     sampler = ClockSampler(physical_gpu_index(local))
     n, k = LAYERS[WORKLOAD_LAYER]
@@ -862,6 +866,8 @@ def main() -> None:
     ap.add_argument("--case", default=None, help="layer:m -- time one case only (the command ncu wraps)")
     ap.add_argument("--no-table", action="store_true", help="skip the per-case table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-programmatic-launch", action="store_true",
+                    help="launch every kernel the ordinary way (no start under the previous kernel's tail): the A/B of that feature")
     ap.add_argument("--boundary-only", action="store_true", help="time only the boundary -> pooler + router table")
     args = ap.parse_args()
     if args.impl == "reference":

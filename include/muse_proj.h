@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define MUSE_PROJ_ABI_VERSION 17
+#define MUSE_PROJ_ABI_VERSION 18
 
 /* Bits a kernel may OR into its status word when one of its bounded waits gives up. */
 #define MUSE_ST_PRODUCER_TIMEOUT 1
@@ -68,6 +68,16 @@ typedef struct muse_peer_sync {
 
 /* ABI version of the loaded library (MUSE_PROJ_ABI_VERSION at build time). */
 int muse_abi_version(void);
+
+/* Programmatic dependent launch (on by default). The single-GPU launches of muse_fewtok_mma, muse_fewtok_f32 and
+ * muse_gemm_tc carry cudaLaunchAttributeProgrammaticStreamSerialization: such a kernel may become resident while the
+ * kernel ahead of it in the stream is still running, and until its griddepcontrol.wait it touches only the weights
+ * (which no kernel writes): its launch latency, set-up and first weight loads run under the previous kernel's tail;
+ * activations, outputs, workspaces and the status word are touched only after every kernel ahead has completed.
+ * Stream order is unchanged for the caller, also under stream capture (the graph gets a programmatic edge).
+ * muse_set_programmatic_launch(0) makes every launch an ordinary one; returns the previous setting. Process-wide:
+ * set it before launching from several threads. */
+int muse_set_programmatic_launch(int enabled);
 
 /* Device facts the host-side planner needs. what: 0 = SM count, 1 = opt-in shared memory per
  * block (bytes), 2 = compute capability major*10+minor, 3 = L2 size (bytes). Negative on error.

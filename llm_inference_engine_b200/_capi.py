@@ -16,6 +16,7 @@ _LIB = None
 # name -> (restype, argtypes); kept in one place so that the symbol-export test can walk it.
 SIGNATURES = {
     "muse_abi_version": (C.c_int, []),
+    "muse_set_programmatic_launch": (C.c_int, [C.c_int]),
     "muse_query": (C.c_int, [C.c_int]),
     "muse_gemv1": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                              C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -66,7 +67,7 @@ SIGNATURES = {
                                          C.c_void_p]),
 }
 
-ABI_VERSION = 17
+ABI_VERSION = 18
 
 
 class MuseError(RuntimeError):

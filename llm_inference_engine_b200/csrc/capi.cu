@@ -8,6 +8,7 @@
 #include "common.cuh"
 
 namespace muse {
+bool g_programmatic_launch = true;
 int gemv1_dispatch(const void* W, const void* x, void* out, int N, int K, int w_is_f32, int wpr, int unroll,
                    int persistent, int* status, const PeerSync* peers, cudaStream_t stream);
 int skinny_tc_dispatch(const CUtensorMap* tw, const CUtensorMap* twlo, const CUtensorMap* tx, void* out, float* ws,
@@ -102,6 +103,12 @@ int muse_nop(void* stream) {
 }
 
 int muse_abi_version(void) { return MUSE_PROJ_ABI_VERSION; }
+
+int muse_set_programmatic_launch(int enabled) {
+  const int was = muse::g_programmatic_launch ? 1 : 0;
+  muse::g_programmatic_launch = enabled != 0;
+  return was;
+}
 
 #ifdef MUSE_TRACE
 // Diagnostic builds only (not part of the ABI in muse_proj.h): the device buffer that the kernels' phase

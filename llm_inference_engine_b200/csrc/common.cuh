@@ -192,6 +192,34 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
          | (static_cast<uint32_t>(M >> 4) << 24);   // M / 16
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with launch_dependent() below may become resident while the kernel before it in the stream is
+// still running (as that kernel's CTAs leave their SMs). Until griddep_wait() returns it may touch only what no
+// kernel ever writes -- the weights -- so its first weight loads, its launch latency and its set-up run under the
+// previous kernel's tail; activations, outputs, workspaces, counters and the status word come after the wait, which
+// returns once every kernel ahead in the stream has completed and its writes are visible. A kernel says with
+// griddep_launch_dependents() that the next one may be brought in; without it that happens when the kernel ends.
+// Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern bool g_programmatic_launch;   // capi.cu; muse_set_programmatic_launch()
+
+template <typename... P, typename... A>
+inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_programmatic_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 // ---------------------------------------------------------------- plain memory helpers
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
   uint4 r;

@@ -216,6 +216,10 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
   // in flight across the reduction below. (A second buffer costs 16 registers the 32-warp CTA does not have.)
   uint4 w[U], xr[U], xh[HI ? U : 1];
   if (my_groups > 0) load(w, 0);
+  // Only the weights have been touched so far: everything below waits for the kernels ahead in the stream (no-ops
+  // unless this launch was allowed to start under the previous kernel's tail).
+  griddep_launch_dependents();
+  griddep_wait();
   if constexpr (BND) {
     // The first weight loads are in flight; every CTA now rebuilds h for all tokens and takes its fragments from it.
     extern __shared__ __align__(16) float bnd_s1[];
@@ -421,6 +425,8 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
     }
   };
   if (my_groups > 0) load(0, 0);
+  griddep_launch_dependents();   // only the weights have been touched so far; the rest waits for the kernels ahead
+  griddep_wait();
   // (a, b) -> BF16 pair of the hi halves (a in the low 16 bits) and of the lo halves.
   auto split = [](uint32_t a_bits, uint32_t b_bits, uint32_t& hi, uint32_t& lo) {
     const float a = __uint_as_float(a_bits), b = __uint_as_float(b_bits);
@@ -564,11 +570,16 @@ static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int
   const int groups = (N + 7) / 8;
   if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
-  kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
-                                               reinterpret_cast<const __nv_bfloat16*>(x),
-                                               reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
-                                               status, ps, BoundaryArgs{});
-  return cudaGetLastError();
+  if constexpr (PEERS) {   // the exchange reads call numbers other kernels advance: launched the ordinary way
+    kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
+                                                 reinterpret_cast<const __nv_bfloat16*>(x),
+                                                 reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
+                                                 status, ps, BoundaryArgs{});
+    return cudaGetLastError();
+  }
+  return launch_dependent(kern, dim3(walkers * tok_split), dim3(NW * 32), 0, s, reinterpret_cast<const __nv_bfloat16*>(W),
+                          reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out,
+                          tok_split, status, ps, BoundaryArgs{});
 }
 
 // Row-parallel launch: the same persistent walk, the all-reduce inside (see RP above).
@@ -646,9 +657,8 @@ static cudaError_t launch_xreg_f32(const void* W, const void* x, void* out, int 
   const int groups = (N + 7) / 8;
   if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
-  kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const float*>(W), x, reinterpret_cast<float*>(out), m, N, K,
-                                               ld_x, ld_out, tok_split, BoundaryArgs{});
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(walkers * tok_split), dim3(NW * 32), 0, s, reinterpret_cast<const float*>(W), x,
+                          reinterpret_cast<float*>(out), m, N, K, ld_x, ld_out, tok_split, BoundaryArgs{});
 }
 
 // FP32 weight and output, 1..8 * tok_split tokens, 16 warps, unroll in {2, 4, 8} with K <= 512 * unroll;

@@ -121,7 +121,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 
   uint64_t pol_w = 0, pol_x = 0;
   int issued = 0;
-  auto issue = [&](int i, int s) {
+  auto issue_w = [&](int i, int s) {   // arms the stage's barrier for all of its bytes, then the weight atoms
     const uint32_t full = smem_u32(&bar_full[s]);
     const uint32_t a = smem_base + static_cast<uint32_t>(s) * stage_bytes;
     mbar_expect_tx(full, stage_bytes);
@@ -130,9 +130,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       tma_load_2d(a + static_cast<uint32_t>(t) * A_BYTES * H, &tm_w, kcol, tile_n * own_rows, full, pol_w);
       if (PAIR) tma_load_2d(a + static_cast<uint32_t>(t) * A_BYTES * H + A_BYTES, &tm_w, kcol, tile_n * own_rows + GT_ROWS, full, pol_w);
     }
+  };
+  auto issue_x = [&](int i, int s) {
+    const uint32_t full = smem_u32(&bar_full[s]);
+    const uint32_t a = smem_base + static_cast<uint32_t>(s) * stage_bytes;
     for (int t = 0; t < katoms; ++t)
       tma_load_2d(a + a_all + static_cast<uint32_t>(t) * b_bytes, &tm_x, ((c0 + i) * katoms + t) * GT_BK, tile_m * ntok, full, pol_x);
     ++issued;
+  };
+  auto issue = [&](int i, int s) {
+    issue_w(i, s);
+    issue_x(i, s);
   };
 
   const int tok0 = tile_m * ntok;
@@ -152,8 +160,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     fence_mbar_init();
     pol_w = l2_policy_evict_first();
     pol_x = l2_policy_evict_last();
+    // The first stages: the weight tiles leave now, the x tiles once the kernels ahead in the stream have completed
+    // (a launch allowed to start under the previous kernel's tail touches only weights until then).
     const int pre = min(stages, nchunks);
-    for (int i = 0; i < pre; ++i) issue(i, i);
+    for (int i = 0; i < pre; ++i) issue_w(i, i);
+    griddep_launch_dependents();
+    griddep_wait();
+    for (int i = 0; i < pre; ++i) issue_x(i, i);
     s_abort = 0;
     s_issued = 0;
     if constexpr (PEERS) {
@@ -166,6 +179,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     tmem_alloc(smem_u32(&tmem_slot), static_cast<uint32_t>(tmem_cols));
     tmem_relinquish();
   }
+  griddep_wait();   // every thread, before the first barrier: what follows reads and writes more than weights
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -508,7 +522,7 @@ static cudaError_t gt_configure(int dev, int* room_out) {
 }
 
 static void gt_fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int m, int n, int ntok, int pair, int cluster,
-                           int split, int warpgroups, int tile_rows, size_t smem, cudaStream_t stream) {
+                           int split, int warpgroups, int tile_rows, size_t smem, cudaStream_t stream, bool pdl) {
   const int rows = pair ? 2 * GT_ROWS : tile_rows;
   *cfg = cudaLaunchConfig_t{};
   cfg->gridDim = dim3((n + rows - 1) / rows, cluster * split, (m + ntok - 1) / ntok);
@@ -519,8 +533,10 @@ static void gt_fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, i
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = static_cast<unsigned>(cluster);
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start under the previous kernel's tail
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg->attrs = attr;
-  cfg->numAttrs = 1;
+  cfg->numAttrs = pdl && g_programmatic_launch ? 2 : 1;
 }
 
 template <bool PAIR, bool PEERS>
@@ -534,8 +550,8 @@ static cudaError_t gt_launch(const CUtensorMap* tw, const CUtensorMap* tx, void*
   const size_t smem = static_cast<size_t>(gemm_tc_smem_bytes(ntok, PAIR, stages, cluster, m, warpgroups, tile_rows, katoms));
   if (smem > static_cast<size_t>(room)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
-  gt_fill_config(&cfg, attr, m, n, ntok, PAIR, cluster, split, warpgroups, tile_rows, smem, stream);
+  cudaLaunchAttribute attr[2];
+  gt_fill_config(&cfg, attr, m, n, ntok, PAIR, cluster, split, warpgroups, tile_rows, smem, stream, !PEERS);
   return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<PAIR, PEERS>, *tw, *tx, reinterpret_cast<__nv_bfloat16*>(out), ws, cnt, status,
                             m, n, chunks, ntok, stages, gt_tmem_cols(ntok, PAIR), ld_out, tile_rows, katoms, ps);
 }
@@ -552,9 +568,9 @@ int gemm_tc_max_clusters(int ntok, int pair, int stages, int cluster, int m, int
   const size_t smem = static_cast<size_t>(gemm_tc_smem_bytes(ntok, pair, stages, cluster, m, warpgroups, tile_rows, katoms));
   if (smem > static_cast<size_t>(room)) return 0;
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   gt_fill_config(&cfg, attr, m < ntok ? m : ntok, pair ? 2 * GT_ROWS : tile_rows, ntok, pair, cluster, 1, warpgroups, tile_rows, smem,
-                 nullptr);
+                 nullptr, false);
   const cudaError_t q = pair ? cudaOccupancyMaxActiveClusters(&num, gemm_tc_kernel<true, false>, &cfg)
                              : cudaOccupancyMaxActiveClusters(&num, gemm_tc_kernel<false, false>, &cfg);
   if (q != cudaSuccess) {

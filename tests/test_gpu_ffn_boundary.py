@@ -107,3 +107,35 @@ def test_one_launch_replays_and_rejections(oracle, proj):
         proj.unpooler_ffn_boundary({"x": x, "stream1": stream1.to(DEV), "config": dict(cfg, n=1004)}, state)
     with pytest.raises(TypeError):
         proj.ffn_boundary(stream1.to(DEV), torch.zeros((8, 1024), device=DEV), state)
+
+
+def test_a_count_that_never_completes_gives_up_and_recovers(oracle, proj):
+    """Failure detection without a fault: the token CTAs wait for every CTA of the launch to count itself. With the
+    counter started three short, the count never completes: the wait is bounded (0.5 s), the kernel comes back by
+    itself, reports ST_X_TIMEOUT and re-arms the counters, and the next call is correct."""
+    import time
+
+    layers = {"unpooler": oracle.TARGET_LAYERS["unpooler"]}
+    n, k = layers["unpooler"]
+    w_cpu = oracle.target_weights(layers=layers)
+    state = proj.prepare({"unpooler": w_cpu["unpooler"].to(DEV)}, warmup=False)
+    stream1, _, gate, post_w, next_w = oracle.ffn_boundary_inputs(2, n, 1024, 95)
+    proj.prepare_ffn_boundary(state, gate.to(DEV), post_w.to(DEV), next_w.to(DEV))
+    x = torch.randn((2, k), generator=torch.Generator().manual_seed(96)).bfloat16().to(DEV)
+    data = {"x": x, "stream1": stream1.to(DEV), "config": {"layer": "unpooler", "m": 2, "n": 1024, "k": k}}
+    good = [t.clone() for t in proj.unpooler_ffn_boundary(data, state)]
+    proj.check_status(state)
+    _, cnt = proj._stream_workspace(state, DEV)
+    cnt[16] = -3
+    torch.cuda.synchronize(DEV)
+    t0 = time.perf_counter()
+    proj.unpooler_ffn_boundary(data, state)
+    torch.cuda.synchronize(DEV)
+    waited = time.perf_counter() - t0
+    assert 0.3 < waited < 5.0, waited                      # the bounded wait, not a hang and not a skip
+    with pytest.raises(Exception, match="timed-out wait"):
+        proj.check_status(state)
+    assert int(cnt[:32].abs().max()) == 0                  # the last token CTA re-armed the counters
+    again = proj.unpooler_ffn_boundary(data, state)
+    proj.check_status(state)
+    assert torch.equal(again[0], good[0]) and torch.equal(again[1], good[1])
