@@ -69,12 +69,15 @@ typedef struct muse_peer_sync {
 /* ABI version of the loaded library (MUSE_PROJ_ABI_VERSION at build time). */
 int muse_abi_version(void);
 
-/* Programmatic dependent launch (on by default). The single-GPU launches of muse_fewtok_mma, muse_fewtok_f32 and
- * muse_gemm_tc carry cudaLaunchAttributeProgrammaticStreamSerialization: such a kernel may become resident while the
+/* Programmatic dependent launch (on by default). The single-GPU launches of every projection kernel (GEMV,
+ * register-MMA walks, TMEM kernels, the fused boundary kernels) carry cudaLaunchAttributeProgrammaticStreamSerialization: such a kernel may become resident while the
  * kernel ahead of it in the stream is still running, and until its griddepcontrol.wait it touches only the weights
  * (which no kernel writes): its launch latency, set-up and first weight loads run under the previous kernel's tail;
  * activations, outputs, workspaces and the status word are touched only after every kernel ahead has completed.
  * Stream order is unchanged for the caller, also under stream capture (the graph gets a programmatic edge).
+ * What this asks of the caller: a weight (and its hi / lo halves, 12-bit planes and tables) must not be the output
+ * of work still in flight on the stream when a projection is launched; weights are static, so one synchronisation
+ * after loading them is enough (the Python prepare() does it).
  * muse_set_programmatic_launch(0) makes every launch an ordinary one; returns the previous setting. Process-wide:
  * set it before launching from several threads. */
 int muse_set_programmatic_launch(int enabled);

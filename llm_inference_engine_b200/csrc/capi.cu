@@ -89,6 +89,7 @@ __global__ void nop_kernel() {}
 // plain loads: for a few KB this is a kernel-to-kernel dependency for the consumer instead of a copy-engine
 // hand-off.
 __global__ void fetch_host_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long vecs) {
+  griddep_launch_dependents();   // the projection behind this kernel may start its weight loads now; it waits for x itself
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
     dst[i] = src[i];

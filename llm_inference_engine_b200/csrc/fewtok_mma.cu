@@ -689,6 +689,8 @@ __global__ void __launch_bounds__(256) attn_boundary_kernel(const __grid_constan
   constexpr int NT = 256, CH = 4;
   __shared__ float red[NT / 32];
   __shared__ float s_inv;
+  griddep_launch_dependents();   // everything here depends on the kernels ahead: only the launch itself overlaps them
+  griddep_wait();
   const int t = blockIdx.x, cpt = D >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   auto block_inv = [&](float v, float eps) {
 #pragma unroll
@@ -862,6 +864,10 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const __nv_bfloat16*
   unsigned long long* const tr = trace && threadIdx.x == 0 ? trace + 16ull * blockIdx.x : nullptr;
 #define FB_STAMP(slot) do { if (tr) tr[slot] = global_ns(); } while (0)
   FB_STAMP(0);
+  // The producers' input is the previous kernel's output and everything here hangs on the producers: only the launch
+  // itself overlaps the kernels ahead in the stream.
+  griddep_launch_dependents();
+  griddep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int kblocks = K >> 5, first = warp * FB_U;
   bool ok;
@@ -1067,8 +1073,7 @@ int attn_boundary_dispatch(const BoundaryArgs& bd, int m, int D, cudaStream_t st
   if (bad) return bad;
   if (D > 8192) return -2;
   if (!bd.stream1 && !bd.h && !bd.h_f32) return -1;
-  attn_boundary_kernel<<<m, 256, 0, stream>>>(bd, D);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_dependent(attn_boundary_kernel, dim3(m), dim3(256), 0, stream, bd, D));
 }
 
 // The projection with the boundary as its prologue: 16 warps x 8 loads (K <= 4096), up to 8 tokens, and at least
@@ -1100,20 +1105,18 @@ static cudaError_t launch_boundary(const void* W, void* out, int m, int N, int K
   const int groups = (N + 7) / 8;
   if (walkers > groups) walkers = groups;
   if constexpr (F32W) {
-    fewtok_xreg_f32_kernel<16, 8, true, true><<<walkers, 512, smem, s>>>(reinterpret_cast<const float*>(W), nullptr,
-                                                                         reinterpret_cast<float*>(out), m, N, K, K, ld_out, 1, bd);
+    return launch_dependent(fewtok_xreg_f32_kernel<16, 8, true, true>, dim3(walkers), dim3(512), smem, s, reinterpret_cast<const float*>(W),
+                            nullptr, reinterpret_cast<float*>(out), m, N, K, K, ld_out, 1, bd);
   } else {
     const bool vec = N % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | (static_cast<uintptr_t>(ld_out) * 2)) & 15) == 0;
     if (vec)
-      fewtok_xreg_kernel<16, 8, false, false, true, true><<<walkers, 512, smem, s>>>(
-          reinterpret_cast<const __nv_bfloat16*>(W), nullptr, reinterpret_cast<__nv_bfloat16*>(out), m, N, K, K, ld_out, 1, status,
-          PeerSync{}, bd);
-    else
-      fewtok_xreg_kernel<16, 8, false, false, false, true><<<walkers, 512, smem, s>>>(
-          reinterpret_cast<const __nv_bfloat16*>(W), nullptr, reinterpret_cast<__nv_bfloat16*>(out), m, N, K, K, ld_out, 1, status,
-          PeerSync{}, bd);
+      return launch_dependent(fewtok_xreg_kernel<16, 8, false, false, true, true>, dim3(walkers), dim3(512), smem, s,
+                              reinterpret_cast<const __nv_bfloat16*>(W), nullptr, reinterpret_cast<__nv_bfloat16*>(out), m, N, K, K, ld_out,
+                              1, status, PeerSync{}, bd);
+    return launch_dependent(fewtok_xreg_kernel<16, 8, false, false, false, true>, dim3(walkers), dim3(512), smem, s,
+                            reinterpret_cast<const __nv_bfloat16*>(W), nullptr, reinterpret_cast<__nv_bfloat16*>(out), m, N, K, K, ld_out, 1,
+                            status, PeerSync{}, bd);
   }
-  return cudaGetLastError();
 }
 
 int fewtok_boundary_dispatch(const void* W, int w_is_f32, const BoundaryArgs& bd, void* out, int m, int N, int K, int ld_out,
@@ -1216,11 +1219,10 @@ int fused_boundary_dispatch(const void* Wp, const void* Wr_hi, const void* Wr_lo
   const int rc = gr < sms[dev] / 4 ? gr : sms[dev] / 4;
   const int pc = sms[dev] - rc < gp ? sms[dev] - rc : gp;
   if (pc < m) return -9;   // one pooler CTA per token publishes it
-  fused_boundary_kernel<<<pc + rc, FB_NT, x_bytes(m, K), stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(Wp), reinterpret_cast<const __nv_bfloat16*>(Wr_hi), reinterpret_cast<const __nv_bfloat16*>(Wr_lo),
-      bd, reinterpret_cast<__nv_bfloat16*>(h_lo), reinterpret_cast<__nv_bfloat16*>(outp), reinterpret_cast<float*>(outr), m, Np, Nr, K,
-      ld_outp, ld_outr, pc, FB_STAGGER_NS, cnt, status);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_dependent(
+      fused_boundary_kernel, dim3(pc + rc), dim3(FB_NT), x_bytes(m, K), stream, reinterpret_cast<const __nv_bfloat16*>(Wp),
+      reinterpret_cast<const __nv_bfloat16*>(Wr_hi), reinterpret_cast<const __nv_bfloat16*>(Wr_lo), bd, reinterpret_cast<__nv_bfloat16*>(h_lo),
+      reinterpret_cast<__nv_bfloat16*>(outp), reinterpret_cast<float*>(outr), m, Np, Nr, K, ld_outp, ld_outr, pc, FB_STAGGER_NS, cnt, status));
 }
 
 }  // namespace muse

@@ -102,6 +102,8 @@ __global__ void __launch_bounds__(NW * 32) fewtok_zip_kernel(const uint8_t* __re
     }
   };
   if (my_groups > 0) load(0);
+  griddep_launch_dependents();   // only the weights so far; the table is the weight's too, x and out are not
+  griddep_wait();
   // One thread per (entry, token): the entry and the activation it multiplies, both fetched now, under the first
   // group's weight loads, so that no epilogue waits for a load.
   for (int v = threadIdx.x; v < my_groups * cap * 8; v += NW * 32) {
@@ -205,11 +207,9 @@ static cudaError_t launch_zip(const void* lo, const void* nib, const void* exc, 
   if (walkers > groups) walkers = groups;
   const size_t table = static_cast<size_t>((groups + walkers - 1) / walkers) * cap * (sizeof(int2) + 8 * sizeof(float));
   if (table > ZIP_TABLE_SMEM) return cudaErrorInvalidConfiguration;
-  kern<<<walkers, NW * 32, RED + table, s>>>(reinterpret_cast<const uint8_t*>(lo), reinterpret_cast<const uint8_t*>(nib),
-                                             reinterpret_cast<const int2*>(exc), cap, base4, coded,
-                                             reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(out), m, N, K,
-                                             ld_x, ld_out);
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(walkers), dim3(NW * 32), RED + table, s, reinterpret_cast<const uint8_t*>(lo),
+                          reinterpret_cast<const uint8_t*>(nib), reinterpret_cast<const int2*>(exc), cap, base4, coded,
+                          reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out);
 }
 
 // 1..8 tokens; warps x unroll in {32 x 4, 16 x 8, 16 x 4}; `reduce_every` = row groups per CTA-wide reduction, 1 or 2. `exc`: per 8-row

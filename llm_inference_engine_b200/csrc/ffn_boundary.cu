@@ -159,6 +159,8 @@ __global__ void __launch_bounds__(256) ffn_boundary_kernel(const __grid_constant
                                                            int nf, int D) {
   __shared__ float red[8];
   __shared__ float bc;
+  griddep_launch_dependents();   // everything here depends on the kernels ahead: only the launch itself overlaps them
+  griddep_wait();
   FfnTokenRegs<4> r;
   ffn_token_fetch<256, 4>(a, static_cast<int>(blockIdx.x), D, r);
   ffn_token_finish<256, 4, false>(a, f, nf, static_cast<int>(blockIdx.x), D, r, red, &bc);
@@ -189,6 +191,8 @@ __global__ void __launch_bounds__(512, 1) unpooler_ffn_kernel(const __nv_bfloat1
     for (int u = 0; u < U; ++u) w[u] = first + u < kblocks ? ldg_stream16(p + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
   };
   if (my_groups > 0) load(0);
+  griddep_launch_dependents();   // only the weights so far: x, stream1, the scratch and the counters wait for the kernels ahead
+  griddep_wait();
   FfnTokenRegs<2> tok;   // CTA t < m: what token t's boundary needs besides f, asked for now
   if (c < m) ffn_token_fetch<512, 2>(a, c, D, tok);
   {
@@ -257,8 +261,7 @@ int ffn_boundary_dispatch(const FfnBoundaryArgs& a, const void* f, int m, int D,
   if (bad) return bad;
   if (!f || D > 8192) return -2;
   if (reinterpret_cast<uintptr_t>(f) & 15) return -2;
-  ffn_boundary_kernel<<<m, 256, 0, stream>>>(a, reinterpret_cast<const __nv_bfloat16*>(f), nf, D);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_dependent(ffn_boundary_kernel, dim3(m), dim3(256), 0, stream, a, reinterpret_cast<const __nv_bfloat16*>(f), nf, D));
 }
 
 // One launch: m <= 8, K <= 4096 in whole 32-element pieces, NF % 8 == 0 with at least m row groups, D <= 8192.
@@ -282,10 +285,10 @@ int unpooler_ffn_dispatch(const void* W, const void* x, void* f_scratch, const F
   const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(W);
   const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
   float* fs = reinterpret_cast<float*>(f_scratch);
-  if (K <= 1024) unpooler_ffn_kernel<2><<<ctas, 512, 0, stream>>>(w, xb, fs, a, m, NF, K, ld_x, D, cnt, status);
-  else if (K <= 2048) unpooler_ffn_kernel<4><<<ctas, 512, 0, stream>>>(w, xb, fs, a, m, NF, K, ld_x, D, cnt, status);
-  else unpooler_ffn_kernel<8><<<ctas, 512, 0, stream>>>(w, xb, fs, a, m, NF, K, ld_x, D, cnt, status);
-  return static_cast<int>(cudaGetLastError());
+  if (K <= 1024) e = launch_dependent(unpooler_ffn_kernel<2>, dim3(ctas), dim3(512), 0, stream, w, xb, fs, a, m, NF, K, ld_x, D, cnt, status);
+  else if (K <= 2048) e = launch_dependent(unpooler_ffn_kernel<4>, dim3(ctas), dim3(512), 0, stream, w, xb, fs, a, m, NF, K, ld_x, D, cnt, status);
+  else e = launch_dependent(unpooler_ffn_kernel<8>, dim3(ctas), dim3(512), 0, stream, w, xb, fs, a, m, NF, K, ld_x, D, cnt, status);
+  return static_cast<int>(e);
 }
 
 }  // namespace muse

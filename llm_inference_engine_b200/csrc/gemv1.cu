@@ -81,6 +81,17 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&xbar), 1);
     fence_mbar_init();
+  }
+  const uint4* wp = reinterpret_cast<const uint4*>(
+      reinterpret_cast<const char*>(W) + (static_cast<size_t>(live ? row : 0) * K + static_cast<size_t>(seg) * ks) * WB);
+  uint4 w[U], wn[U];
+  const int nb = live ? (nvec + 32 * U - 1) / (32 * U) : 0;
+  if (nb > 0) load_batch<U>(w, wp, lane, nvec);
+  // Only the weights have been touched so far: x, the output and the exchange wait for the kernels ahead in the
+  // stream (no-ops unless this launch was allowed to start under the previous kernel's tail).
+  griddep_launch_dependents();
+  griddep_wait();
+  if (threadIdx.x == 0) {
     mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u);
     bulk_load_1d(smem_u32(smem), x, static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
     if (peer_active(ps)) {
@@ -88,12 +99,6 @@ __global__ void __launch_bounds__(256) gemv1_kernel(const void* __restrict__ W, 
       if (blockIdx.x == 0) peer_announce_enter(ps, s_epoch);
     }
   }
-
-  const uint4* wp = reinterpret_cast<const uint4*>(
-      reinterpret_cast<const char*>(W) + (static_cast<size_t>(live ? row : 0) * K + static_cast<size_t>(seg) * ks) * WB);
-  uint4 w[U], wn[U];
-  const int nb = live ? (nvec + 32 * U - 1) / (32 * U) : 0;
-  if (nb > 0) load_batch<U>(w, wp, lane, nvec);
 
   __syncthreads();  // barrier initialised for everyone
   // A CTA-uniform verdict on the copy of x: on a time-out nobody multiplies (x is not there), but every
@@ -173,12 +178,6 @@ __global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict_
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&xbar), 1);
     fence_mbar_init();
-    mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u);
-    bulk_load_1d(smem_u32(smem), x, static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
-    if (peer_active(ps)) {
-      s_epoch = peer_epoch(ps);
-      if (blockIdx.x == 0) peer_announce_enter(ps, s_epoch);
-    }
   }
   auto row_ptr = [&](int r) {
     return reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(W) +
@@ -186,6 +185,16 @@ __global__ void __launch_bounds__(256) gemv1_rows_kernel(const void* __restrict_
   };
   uint4 w[U], wn[U];
   if (steps > 0) load_batch<U>(w, row_ptr(0), lane, nvec);
+  griddep_launch_dependents();   // only the weights so far: see gemv1_kernel
+  griddep_wait();
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(smem_u32(&xbar), static_cast<uint32_t>(K) * 2u);
+    bulk_load_1d(smem_u32(smem), x, static_cast<uint32_t>(K) * 2u, smem_u32(&xbar));
+    if (peer_active(ps)) {
+      s_epoch = peer_epoch(ps);
+      if (blockIdx.x == 0) peer_announce_enter(ps, s_epoch);
+    }
+  }
   __syncthreads();
   // CTA-uniform, and without an early return: see gemv1_kernel.
   const bool x_ok = __syncthreads_and(mbar_wait(smem_u32(&xbar), 0)) != 0;
@@ -260,8 +269,11 @@ static cudaError_t launch_rows(const void* W, const void* x, void* out, int N, i
   int grid = sms[dev] * resident;
   const int need = (N + 7) / 8;
   if (grid > need) grid = need;
-  kern<<<grid, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
-  return cudaGetLastError();
+  if (ps.world > 1) {   // the exchange reads call numbers other kernels advance: launched the ordinary way
+    kern<<<grid, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
+    return cudaGetLastError();
+  }
+  return launch_dependent(kern, dim3(grid), dim3(256), smem, s, W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
 }
 
 template <bool F32W>
@@ -285,8 +297,12 @@ static cudaError_t launch(const void* W, const void* x, void* out, int N, int K,
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
   }
-  kern<<<(N + RPC - 1) / RPC, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
-  return cudaGetLastError();
+  if (ps.world > 1) {
+    kern<<<(N + RPC - 1) / RPC, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
+    return cudaGetLastError();
+  }
+  return launch_dependent(kern, dim3((N + RPC - 1) / RPC), dim3(256), smem, s, W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K,
+                          status, ps);
 }
 
 template <int WPR, bool F32W>

@@ -164,14 +164,22 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   // ---- producer state lives in thread 0 across the set-up barrier
   uint64_t pol_w = 0, pol_x = 0;
   int issued = 0;
-  auto issue = [&](int i, int s) {
+  auto issue_w = [&](int i, int s) {   // arms the stage's barrier for all of its bytes, then the weight tiles
     const uint32_t full = smem_u32(&bar_full[s]);
     const uint32_t a = smem_base + static_cast<uint32_t>(s) * Cfg::STAGE_BYTES;
     mbar_expect_tx(full, Cfg::STAGE_BYTES);
     tma_load_2d(a, &tm_w, (c0 + i) * BK, tile_n * TILE_ROWS, full, pol_w);
     if (HILO) tma_load_2d(a + Cfg::A_BYTES, &tm_wlo, (c0 + i) * BK, tile_n * TILE_ROWS, full, pol_w);
+  };
+  auto issue_x = [&](int i, int s) {
+    const uint32_t full = smem_u32(&bar_full[s]);
+    const uint32_t a = smem_base + static_cast<uint32_t>(s) * Cfg::STAGE_BYTES;
     tma_load_2d(a + Cfg::A_BYTES * (HILO ? 2 : 1), &tm_x, (c0 + i) * BK, tile_m * NTOK, full, pol_x);
     ++issued;
+  };
+  auto issue = [&](int i, int s) {
+    issue_w(i, s);
+    issue_x(i, s);
   };
 
   // The first thing a CTA does is get weight bytes moving: every stage starts empty, so thread 0
@@ -188,8 +196,13 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     MUSE_STAMP(14);
     pol_w = l2_policy_evict_first();  // weights are read once
     pol_x = l2_policy_evict_last();   // every CTA of the same K slice re-reads x
+    // The weight tiles of the first stages leave now, the x tiles once the kernels ahead in the stream have completed
+    // (a launch allowed to start under the previous kernel's tail touches only weights until then).
     const int pre = min(stages, nchunks);
-    for (int i = 0; i < pre; ++i) issue(i, i);
+    for (int i = 0; i < pre; ++i) issue_w(i, i);
+    griddep_launch_dependents();
+    griddep_wait();
+    for (int i = 0; i < pre; ++i) issue_x(i, i);
     s_abort = 0;
     s_issued = 0;
     if constexpr (PEERS) {
@@ -223,6 +236,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     tmem_relinquish();
     if (lane == 0) MUSE_STAMP(12);
   }
+  griddep_wait();   // every thread, before the first barrier: what follows reads and writes more than weights
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -534,7 +548,7 @@ static cudaError_t configure(int dev, int* room_out) {
 
 template <int NTOK, bool HILO>
 static void fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int m, int n, int cluster, int groups,
-                        size_t smem, cudaStream_t stream) {
+                        size_t smem, cudaStream_t stream, bool pdl) {
   *cfg = cudaLaunchConfig_t{};
   cfg->gridDim = dim3((n + TILE_ROWS - 1) / TILE_ROWS, cluster * groups, (m + NTOK - 1) / NTOK);
   cfg->blockDim = dim3(128, 1, 1);
@@ -544,8 +558,10 @@ static void fill_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int 
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = static_cast<unsigned>(cluster);
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start under the previous kernel's tail
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg->attrs = attr;
-  cfg->numAttrs = 1;
+  cfg->numAttrs = pdl && g_programmatic_launch ? 2 : 1;
 }
 
 template <int NTOK, bool HILO, bool PEERS>
@@ -575,8 +591,8 @@ static cudaError_t launch_with(const CUtensorMap* tw, const CUtensorMap* twlo, c
   const size_t smem = static_cast<size_t>(skinny_smem_bytes(NTOK, HILO, stages, cluster, m));
   if (smem > static_cast<size_t>(room)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
-  fill_config<NTOK, HILO>(&cfg, attr, m, n, cluster, groups, smem, stream);
+  cudaLaunchAttribute attr[2];
+  fill_config<NTOK, HILO>(&cfg, attr, m, n, cluster, groups, smem, stream, !PEERS);
   return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<NTOK, HILO, PEERS>, *tw, HILO ? *twlo : *tw, *tx, out, ws, cnt, status, m, n,
                             chunks, cluster * groups, stages, out_f32, ld_out, ps);
 }
@@ -590,9 +606,9 @@ static int max_clusters(int m, int stages, int cluster) {
   const size_t smem = static_cast<size_t>(skinny_smem_bytes(NTOK, HILO, stages, cluster, m));
   if (smem > static_cast<size_t>(room)) return 0;
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   // the grid only has to be a legal multiple of the cluster for the query
-  fill_config<NTOK, HILO>(&cfg, attr, m, TILE_ROWS, cluster, 1, smem, nullptr);
+  fill_config<NTOK, HILO>(&cfg, attr, m, TILE_ROWS, cluster, 1, smem, nullptr, false);
   if (cudaOccupancyMaxActiveClusters(&num, skinny_tc_kernel<NTOK, HILO, false>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;

@@ -116,6 +116,9 @@ def prepare(weights: dict[str, torch.Tensor], warmup: bool = True):
         state["_plans"] = {}
         state["_override"] = {}
         _stream_workspace(state, device)
+        # The kernels read weights before they wait for the work ahead of them in the stream (they may start under
+        # the previous kernel's tail): whatever produced these tensors must have completed before the first call.
+        torch.cuda.synchronize(device)
         if warmup:
             for layer, w in weights.items():
                 n, k = w.shape
@@ -507,6 +510,8 @@ def prepare_zip12(state, layers=None) -> dict:
         if z is not None:
             state.setdefault("_zip12", {})[name] = z
             done[name] = z.exceptions / w.numel()
+    if done:
+        torch.cuda.synchronize(next(iter(state["_zip12"].values())).low.device)   # the planes are weights: complete before the first call
     return done
 
 
