@@ -69,8 +69,8 @@ typedef struct muse_peer_sync {
 /* ABI version of the loaded library (MUSE_PROJ_ABI_VERSION at build time). */
 int muse_abi_version(void);
 
-/* Programmatic dependent launch (on by default). The single-GPU launches of every projection kernel (GEMV,
- * register-MMA walks, TMEM kernels, the fused boundary kernels) carry cudaLaunchAttributeProgrammaticStreamSerialization: such a kernel may become resident while the
+/* Programmatic dependent launch (on by default). The launches of every projection kernel (GEMV, register-MMA
+ * walks, TMEM kernels, the fused boundary kernels; column- and row-parallel forms included) carry cudaLaunchAttributeProgrammaticStreamSerialization: such a kernel may become resident while the
  * kernel ahead of it in the stream is still running, and until its griddepcontrol.wait it touches only the weights
  * (which no kernel writes): its launch latency, set-up and first weight loads run under the previous kernel's tail;
  * activations, outputs, workspaces and the status word are touched only after every kernel ahead has completed.

@@ -75,9 +75,9 @@ __device__ __forceinline__ void boundary_prologue(const BoundaryArgs& bd, int m,
     for (int t = 0; t < BND_TOKENS; ++t) {
       if (t < m) {
         float a[8];
-        bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a);
-        const float4 s0 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c);
-        const float4 s1 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c + 1);
+        bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a);
+        const float4 s0 = __ldcg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c);
+        const float4 s1 = __ldcg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c + 1);
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss[t] = fmaf(a[i], a[i], ss[t]);
         float4* dst = reinterpret_cast<float4*>(s1buf + t * row + c * 8);
@@ -95,7 +95,7 @@ __device__ __forceinline__ void boundary_prologue(const BoundaryArgs& bd, int m,
     for (int t = 0; t < BND_TOKENS; ++t) {
       if (t < m) {
         float a[8];
-        bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a);
+        bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a);
         float4* p = reinterpret_cast<float4*>(s1buf + t * row + c * 8);
         const float r = inv1[t];
         float4 v0 = p[0], v1 = p[1];

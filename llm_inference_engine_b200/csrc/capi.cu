@@ -92,7 +92,7 @@ __global__ void fetch_host_kernel(uint4* __restrict__ dst, const uint4* __restri
   griddep_launch_dependents();   // the projection behind this kernel may start its weight loads now; it waits for x itself
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
-    dst[i] = src[i];
+    dst[i] = __ldcg(src + i);   // never through the non-coherent path: the source is rewritten between launches
 }
 }  // namespace muse
 

@@ -240,12 +240,12 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_kernel(const __nv_bfloat1
     const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+      xr[u] = (g < m && first + u < kblocks) ? __ldcg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
     if constexpr (HI) {
       const uint4* ph = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g + 8 < m ? g + 8 : 0) * ld_x) + q;
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        xh[u] = (g + 8 < m && first + u < kblocks) ? __ldg(ph + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+        xh[u] = (g + 8 < m && first + u < kblocks) ? __ldcg(ph + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
     } else {
       xh[0] = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -459,8 +459,8 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const bool ok = g < m && first + u < kblocks;
-      const uint4 a = ok ? __ldg(px + (first + u) * 8) : make_uint4(0u, 0u, 0u, 0u);
-      const uint4 b = ok ? __ldg(px + (first + u) * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 a = ok ? __ldcg(px + (first + u) * 8) : make_uint4(0u, 0u, 0u, 0u);
+      const uint4 b = ok ? __ldcg(px + (first + u) * 8 + 1) : make_uint4(0u, 0u, 0u, 0u);
       split(a.x, a.y, xr[u].x, xl[u].x);
       split(a.z, a.w, xr[u].y, xl[u].y);
       split(b.x, b.y, xr[u].z, xl[u].z);
@@ -471,7 +471,7 @@ __global__ void __launch_bounds__(NW * 32) fewtok_xreg_f32_kernel(const float* _
     const uint4* px = reinterpret_cast<const uint4*>(xb) + q;
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+      xr[u] = (g < m && first + u < kblocks) ? __ldcg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
     xl[0] = make_uint4(0u, 0u, 0u, 0u);
   }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -570,13 +570,6 @@ static cudaError_t launch_xreg_with(const void* W, const void* x, void* out, int
   const int groups = (N + 7) / 8;
   if (walkers > groups) walkers = groups;
   if (walkers < 1) return cudaErrorInvalidConfiguration;
-  if constexpr (PEERS) {   // the exchange reads call numbers other kernels advance: launched the ordinary way
-    kern<<<walkers * tok_split, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W),
-                                                 reinterpret_cast<const __nv_bfloat16*>(x),
-                                                 reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, tok_split,
-                                                 status, ps, BoundaryArgs{});
-    return cudaGetLastError();
-  }
   return launch_dependent(kern, dim3(walkers * tok_split), dim3(NW * 32), 0, s, reinterpret_cast<const __nv_bfloat16*>(W),
                           reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out,
                           tok_split, status, ps, BoundaryArgs{});
@@ -601,9 +594,9 @@ static cudaError_t launch_xreg_rowpar(const void* W, const void* x, void* out, i
   }
   int walkers = sms[dev] * per_sm[dev];
   if (walkers > N / 8) walkers = N / 8;
-  kern<<<walkers, NW * 32, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(W), reinterpret_cast<const __nv_bfloat16*>(x),
-                                   reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, 1, status, ps, BoundaryArgs{});
-  return cudaGetLastError();
+  return launch_dependent(kern, dim3(walkers), dim3(NW * 32), 0, s, reinterpret_cast<const __nv_bfloat16*>(W),
+                          reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(out), m, N, K, ld_x, ld_out, 1, status, ps,
+                          BoundaryArgs{});
 }
 
 // out[m, N] = sum over ranks of x_r[m, K_r] . W_r[N, K_r]^T, 1..8 tokens; K_r (this rank's slice) <= 4096 in whole
@@ -712,9 +705,9 @@ __global__ void __launch_bounds__(256) attn_boundary_kernel(const __grid_constan
   for (int j = 0; j < CH; ++j) {
     const int c = threadIdx.x + j * NT;
     if (c < cpt) {
-      bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a[j]);
-      const float4 s0 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c);
-      const float4 s1 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c + 1);
+      bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(t) * D) + c), a[j]);
+      const float4 s0 = __ldcg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c);
+      const float4 s1 = __ldcg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(t) * D) + 2 * c + 1);
       const float4 a0 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * c), a1 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * c + 1);
       const float4 b0 = __ldg(reinterpret_cast<const float4*>(bd.beta) + 2 * c), b1 = __ldg(reinterpret_cast<const float4*>(bd.beta) + 2 * c + 1);
       const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
@@ -955,9 +948,9 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const __nv_bfloat16*
     uint4 av = make_uint4(0u, 0u, 0u, 0u), nw = av;
     float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = s0, a0 = s0, a1 = s0, b0 = s0, b1 = s0;
     if (live) {
-      av = __ldg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(tok) * K) + ch);
-      s0 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(tok) * K) + 2 * ch);
-      s4 = __ldg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(tok) * K) + 2 * ch + 1);
+      av = __ldcg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(tok) * K) + ch);
+      s0 = __ldcg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(tok) * K) + 2 * ch);
+      s4 = __ldcg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(tok) * K) + 2 * ch + 1);
       a0 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * ch);
       a1 = __ldg(reinterpret_cast<const float4*>(bd.alpha) + 2 * ch + 1);
       b0 = __ldg(reinterpret_cast<const float4*>(bd.beta) + 2 * ch);

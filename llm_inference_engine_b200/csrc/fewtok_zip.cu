@@ -111,13 +111,15 @@ __global__ void __launch_bounds__(NW * 32) fewtok_zip_kernel(const uint8_t* __re
     const int i = en_i / cap, e = en_i - i * cap;
     const int2 en = __ldg(exc + static_cast<size_t>(c + i * C) * cap + e);
     if (t == 0) exc_s[en_i] = en;
-    xe_s[v] = (en.x >= 0 && t < m) ? __bfloat162float(x[static_cast<size_t>(t) * ld_x + (en.x & 0xffff)]) : 0.f;
+    xe_s[v] = (en.x >= 0 && t < m)
+                  ? __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(x) + static_cast<size_t>(t) * ld_x + (en.x & 0xffff))))
+                  : 0.f;
   }
   uint4 xr[U];   // the A fragments: lane (g, q) holds token g's 8 activations of each of its pieces
   {
     const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
 #pragma unroll
-    for (int u = 0; u < U; ++u) xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    for (int u = 0; u < U; ++u) xr[u] = (g < m && first + u < kblocks) ? __ldcg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
   }
   for (int i0 = 0; i0 < my_groups; i0 += R) {
     float2 part[R];

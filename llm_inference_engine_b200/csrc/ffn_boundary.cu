@@ -53,8 +53,8 @@ __device__ __forceinline__ void ffn_token_fetch(const FfnBoundaryArgs& a, int t,
     if (c < cpt) {
       float wp[8];
       bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(a.post_w) + c), wp);
-      const float4 s0 = __ldg(reinterpret_cast<const float4*>(a.stream1 + static_cast<size_t>(t) * D) + 2 * c);
-      const float4 s1 = __ldg(reinterpret_cast<const float4*>(a.stream1 + static_cast<size_t>(t) * D) + 2 * c + 1);
+      const float4 s0 = __ldcg(reinterpret_cast<const float4*>(a.stream1 + static_cast<size_t>(t) * D) + 2 * c);
+      const float4 s1 = __ldcg(reinterpret_cast<const float4*>(a.stream1 + static_cast<size_t>(t) * D) + 2 * c + 1);
       const float4 a0 = __ldg(reinterpret_cast<const float4*>(a.alpha) + 2 * c), a1 = __ldg(reinterpret_cast<const float4*>(a.alpha) + 2 * c + 1);
       const float4 b0 = __ldg(reinterpret_cast<const float4*>(a.beta) + 2 * c), b1 = __ldg(reinterpret_cast<const float4*>(a.beta) + 2 * c + 1);
       const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
@@ -107,7 +107,7 @@ __device__ __forceinline__ void ffn_token_finish(const FfnBoundaryArgs& a, const
           fv[j][0] = __uint_as_float(f0.x); fv[j][1] = __uint_as_float(f0.y); fv[j][2] = __uint_as_float(f0.z); fv[j][3] = __uint_as_float(f0.w);
           fv[j][4] = __uint_as_float(f1.x); fv[j][5] = __uint_as_float(f1.y); fv[j][6] = __uint_as_float(f1.z); fv[j][7] = __uint_as_float(f1.w);
         } else {
-          bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(f) + static_cast<size_t>(t) * nf) + c), fv[j]);
+          bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(f) + static_cast<size_t>(t) * nf) + c), fv[j]);
         }
       } else {
 #pragma unroll
@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(512, 1) unpooler_ffn_kernel(const __nv_bfloat1
   {
     const uint4* px = reinterpret_cast<const uint4*>(x + static_cast<size_t>(g < m ? g : 0) * ld_x) + q;
 #pragma unroll
-    for (int u = 0; u < U; ++u) xr[u] = (g < m && first + u < kblocks) ? __ldg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
+    for (int u = 0; u < U; ++u) xr[u] = (g < m && first + u < kblocks) ? __ldcg(px + (first + u) * 4) : make_uint4(0u, 0u, 0u, 0u);
   }
   for (int i = 0; i < my_groups; ++i) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};

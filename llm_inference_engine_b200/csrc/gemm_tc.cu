@@ -551,7 +551,7 @@ static cudaError_t gt_launch(const CUtensorMap* tw, const CUtensorMap* tx, void*
   if (smem > static_cast<size_t>(room)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
-  gt_fill_config(&cfg, attr, m, n, ntok, PAIR, cluster, split, warpgroups, tile_rows, smem, stream, !PEERS);
+  gt_fill_config(&cfg, attr, m, n, ntok, PAIR, cluster, split, warpgroups, tile_rows, smem, stream, true);
   return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<PAIR, PEERS>, *tw, *tx, reinterpret_cast<__nv_bfloat16*>(out), ws, cnt, status,
                             m, n, chunks, ntok, stages, gt_tmem_cols(ntok, PAIR), ld_out, tile_rows, katoms, ps);
 }

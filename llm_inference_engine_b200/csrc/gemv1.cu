@@ -269,10 +269,6 @@ static cudaError_t launch_rows(const void* W, const void* x, void* out, int N, i
   int grid = sms[dev] * resident;
   const int need = (N + 7) / 8;
   if (grid > need) grid = need;
-  if (ps.world > 1) {   // the exchange reads call numbers other kernels advance: launched the ordinary way
-    kern<<<grid, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
-    return cudaGetLastError();
-  }
   return launch_dependent(kern, dim3(grid), dim3(256), smem, s, W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
 }
 
@@ -296,10 +292,6 @@ static cudaError_t launch(const void* W, const void* x, void* out, int N, int K,
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-  }
-  if (ps.world > 1) {
-    kern<<<(N + RPC - 1) / RPC, 256, smem, s>>>(W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K, status, ps);
-    return cudaGetLastError();
   }
   return launch_dependent(kern, dim3((N + RPC - 1) / RPC), dim3(256), smem, s, W, reinterpret_cast<const __nv_bfloat16*>(x), out, N, K,
                           status, ps);

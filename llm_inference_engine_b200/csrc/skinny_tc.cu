@@ -592,7 +592,7 @@ static cudaError_t launch_with(const CUtensorMap* tw, const CUtensorMap* twlo, c
   if (smem > static_cast<size_t>(room)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[2];
-  fill_config<NTOK, HILO>(&cfg, attr, m, n, cluster, groups, smem, stream, !PEERS);
+  fill_config<NTOK, HILO>(&cfg, attr, m, n, cluster, groups, smem, stream, true);
   return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<NTOK, HILO, PEERS>, *tw, HILO ? *twlo : *tw, *tx, out, ws, cnt, status, m, n,
                             chunks, cluster * groups, stages, out_f32, ld_out, ps);
 }

@@ -405,6 +405,27 @@ def test_host_buffer_entry_point_matches_device_path(proj, dev, target_setup):
     proj.check_status(state)
 
 
+def test_an_activation_buffer_that_is_rewritten_between_calls(proj, dev, target_setup):
+    """A decode loop hands every call the same x buffer with new contents, written by a kernel just ahead in the
+    stream. The projections may become resident under that kernel's tail (programmatic dependent launch), so they
+    must read x through L2-coherent loads after their grid-dependency wait: 24 rounds per plan, each against the
+    same call on a fresh copy of x, bit for bit; the non-coherent path would serve lines an SM cached rounds ago."""
+    _, state = target_setup
+    g = torch.Generator(device=dev).manual_seed(4242)
+    for layer, m, n, k in (("qkv_gate", 8, 12288, 4096), ("o", 16, 4096, 4096), ("o", 1, 4096, 4096), ("router", 8, 256, 4096),
+                           ("pooler", 32, 1024, 4096), ("unpooler", 4, 4096, 1024), ("o", 32, 4096, 4096), ("o", 100, 4096, 4096)):
+        cfg = {"m": m, "n": n, "k": k, "layer": layer}
+        x = torch.zeros((m, k), device=dev, dtype=torch.bfloat16)
+        src = [torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16) for _ in range(4)]
+        want = [proj.kernel_fn({"x": s.clone(), "config": cfg}, state).clone() for s in src]
+        torch.cuda.synchronize(dev)
+        for r in range(24):
+            x.copy_(src[r % 4])                                     # a kernel rewrites the buffer ...
+            got = proj.kernel_fn({"x": x, "config": cfg}, state)    # ... and the projection is launched right behind it
+            assert torch.equal(got, want[r % 4]), (layer, m, r)
+    proj.check_status(state)
+
+
 FEWTOK_F32_CASES = [  # (m, n, k, unroll, tok_split)
     (8, 256, 4096, 8, 1), (32, 256, 4096, 8, 4), (1, 256, 4096, 8, 1), (5, 100, 1024, 2, 1), (20, 77, 2048, 4, 3), (13, 1003, 512, 2, 2),
 ]

@@ -65,7 +65,11 @@ def main() -> None:
             got = fused.kernel_fn_host({"x": xh, "config": data["config"]}, state, oh).clone()
             want = fused.kernel_fn({"x": xh.to(dev), "config": data["config"]}, state).cpu()
             if not torch.equal(got, want):
-                bad.append(f"kernel_fn_host != kernel_fn: {layer} m={m} rep={rep}")
+                ref = xh.double() @ w_cpu[layer].double().T
+                worst = [float((t.double() - ref).abs().max()) for t in (got, want)]
+                where = (got != want).nonzero()
+                bad.append(f"kernel_fn_host != kernel_fn: {layer} m={m} rep={rep}: max abs error host {worst[0]:.3g} / device {worst[1]:.3g}, "
+                           f"{len(where)} outputs differ, first at {where[0].tolist()}")
     # graph replays of the fused path: every rank replays the same graph the same number of times
     # (m = 64: the TMEM kernel's epilogue exchange; m = 32, 8, 1: the register-MMA kernel's lines, with and without token split)
     stream = torch.cuda.Stream(dev)
