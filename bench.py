@@ -824,6 +824,9 @@ def run_ours(args) -> None:
                                    f"column-parallel x{world} (rows sharded), all-gather fused into the kernel (peer stores over NVLink)"
                                    if h.fused is not None else
                                    f"column-parallel x{world} (rows sharded) + NCCL all-gather in-graph (fused exchange unavailable: {h.fused_error})"),
+                   "launch": ("every launch an ordinary one (--no-programmatic-launch)" if args.no_programmatic_launch else
+                              "programmatic dependent launch: a call may become resident under the previous call's tail and reads only "
+                              "weights until its grid-dependency wait"),
                    "timing": "CUDA events around K graph replays on the replaying stream, max over ranks"},
         "gpu_launches": args.steps * len(WORKLOAD_TOKENS),
         "nop_graph_replay_us": nop_us,

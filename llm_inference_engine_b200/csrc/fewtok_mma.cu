@@ -857,10 +857,7 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const __nv_bfloat16*
   unsigned long long* const tr = trace && threadIdx.x == 0 ? trace + 16ull * blockIdx.x : nullptr;
 #define FB_STAMP(slot) do { if (tr) tr[slot] = global_ns(); } while (0)
   FB_STAMP(0);
-  // The producers' input is the previous kernel's output and everything here hangs on the producers: only the launch
-  // itself overlaps the kernels ahead in the stream.
   griddep_launch_dependents();
-  griddep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int kblocks = K >> 5, first = warp * FB_U;
   bool ok;
@@ -892,6 +889,7 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const __nv_bfloat16*
       }
     };
     if (my_groups > 0) load(0);
+    griddep_wait();   // only weights so far (they may have left under the previous kernel's tail); flags and h come after
     FB_STAMP(1);
     ok = fb_wait_tokens(cnt, m);
     if (threadIdx.x == 0) arrived = atomicAdd(cnt + FB_DONE, 1);   // consumed at the end: the round trip overlaps the walk
@@ -947,6 +945,7 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const __nv_bfloat16*
     const bool live = producer && ch < (K >> 3);
     uint4 av = make_uint4(0u, 0u, 0u, 0u), nw = av;
     float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = s0, a0 = s0, a1 = s0, b0 = s0, b1 = s0;
+    if (producer) griddep_wait();   // its input is the output of the kernels ahead in the stream
     if (live) {
       av = __ldcg(reinterpret_cast<const uint4*>(bd.attn + static_cast<size_t>(tok) * K) + ch);
       s0 = __ldcg(reinterpret_cast<const float4*>(bd.stream + static_cast<size_t>(tok) * K) + 2 * ch);
@@ -969,6 +968,7 @@ fused_boundary_kernel(const __nv_bfloat16* __restrict__ Wp, const __nv_bfloat16*
     if (!producer) {
       if (stagger_ns > 0) __nanosleep(stagger_ns);   // the producers' input goes to the memory system first
       if (my_groups > 0) load(0);
+      griddep_wait();   // only weights so far; flags and h come after
     }
     FB_STAMP(1);
     if (producer) {   // token `tok`'s boundary, one chunk of 8 elements per thread (K / 8 <= 512)
