@@ -426,6 +426,30 @@ def test_an_activation_buffer_that_is_rewritten_between_calls(proj, dev, target_
     proj.check_status(state)
 
 
+def test_ordinary_launches_give_the_same_bits(proj, dev, target_setup):
+    """muse_set_programmatic_launch(0): every launch an ordinary one. Launch ordering is all the switch changes, so
+    every plan family returns the bits it returns as a programmatic dependent; the previous setting comes back."""
+    from llm_inference_engine_b200 import _capi
+
+    lib = _capi.load()
+    _, state = target_setup
+    g = torch.Generator(device=dev).manual_seed(77)
+    cases = (("qkv_gate", 8, 12288, 4096), ("o", 1, 4096, 4096), ("o", 16, 4096, 4096), ("o", 32, 4096, 4096), ("o", 200, 4096, 4096),
+             ("router", 1, 256, 4096), ("router", 8, 256, 4096), ("router", 100, 256, 4096), ("pooler", 256, 1024, 4096))
+    datas = [{"x": torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16), "config": {"m": m, "n": n, "k": k, "layer": layer}}
+             for layer, m, n, k in cases]
+    with_pdl = [proj.kernel_fn(d, state).clone() for d in datas]
+    assert lib.muse_set_programmatic_launch(0) == 1
+    try:
+        plain = [proj.kernel_fn(d, state).clone() for d in datas]
+    finally:
+        assert lib.muse_set_programmatic_launch(1) == 0
+    torch.cuda.synchronize(dev)
+    for d, a, b in zip(datas, with_pdl, plain):
+        assert torch.equal(a, b), d["config"]
+    proj.check_status(state)
+
+
 FEWTOK_F32_CASES = [  # (m, n, k, unroll, tok_split)
     (8, 256, 4096, 8, 1), (32, 256, 4096, 8, 4), (1, 256, 4096, 8, 1), (5, 100, 1024, 2, 1), (20, 77, 2048, 4, 3), (13, 1003, 512, 2, 2),
 ]
