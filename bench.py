@@ -460,7 +460,7 @@ def rowpar_table(h: Harness, steps: int, warmup: int) -> dict:
                     "nccl_us = kernel + NCCL all-reduce of BF16 partials, kernel_us = local kernel alone"}
 
 
-def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = None) -> list[dict]:
+def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = None, only: str = "one_launch") -> list[dict]:
     """The path's first caller beyond the five projections (one GPU): the decode layer's post-attention boundary
     feeding the pooler and, up to 8 tokens in FP32, the router. Per token count, one graph per variant over
     rotating cold weight copies: the boundary as a kernel of its own in front of the two projections, and the
@@ -480,7 +480,7 @@ def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = Non
     side = torch.cuda.Stream(h.device)
     rows = []
     for m in (1, 4, 8):
-        if only_m is not None and m != only_m:   # one case, the one-launch form only: the command ncu wraps
+        if only_m is not None and m != only_m:   # one case, one form (`only`): the command ncu wraps
             continue
         k = LAYERS["pooler"][1]
         g = torch.Generator(device=h.device).manual_seed(50 + m)
@@ -491,7 +491,7 @@ def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = Non
         row = {"m": m, "copies": copies}
         for fused in (False, True):
             for fork in (False, True):
-                if only_m is not None:
+                if only_m is not None and (fork or only != ("fused" if fused else "separate")):
                     continue
                 keep = []
 
@@ -521,7 +521,8 @@ def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = Non
             for st in states:
                 keep.append(proj.boundary_pooler_router({"stream": stream_in, "attn_out": attn_out}, st, stream1=s1))
 
-        row["one_launch_us"] = 1e3 * h.time_graph(one, steps, warmup) / copies
+        if only_m is None or only == "one_launch":
+            row["one_launch_us"] = 1e3 * h.time_graph(one, steps, warmup) / copies
         rows.append(row)
     for st in states:
         proj.check_status(st)
@@ -530,7 +531,7 @@ def boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = Non
     return rows
 
 
-def ffn_boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
+def ffn_boundary_table(h: Harness, steps: int, warmup: int, only_m: int | None = None) -> list[dict]:
     """The other caller-side step (one GPU): the unpooler's 1024-row slice followed by the post-FFN boundary, as two
     kernels (projection, boundary) and as one launch (muse_unpooler_ffn_boundary), per token count over rotating
     cold weight copies."""
@@ -549,6 +550,8 @@ def ffn_boundary_table(h: Harness, steps: int, warmup: int) -> list[dict]:
         states.append(st)
     rows = []
     for m in (1, 4, 8):
+        if only_m is not None and m != only_m:
+            continue
         x = make_x("unpooler", m, h.device, 400 + m)
         stream1 = torch.randn((m, n), device=h.device, generator=gen(80 + m))
         cfg = {"m": m, "n": nf, "k": k, "layer": "unpooler"}
@@ -723,6 +726,10 @@ def run_ours(args) -> None:
         with sampler:
             if layer == "boundary_pooler_router":        # the one-launch boundary + pooler + router at m tokens
                 rows = boundary_table(h, args.steps, args.warmup, only_m=int(m))
+            elif layer in ("boundary_separate", "boundary_fused"):   # boundary kernel + two projections / the prologue form
+                rows = boundary_table(h, args.steps, args.warmup, only_m=int(m), only=layer[9:])
+            elif layer == "unpooler_ffn_boundary":       # unpooler slice + post-FFN boundary: two kernels, and one launch
+                rows = ffn_boundary_table(h, args.steps, args.warmup, only_m=int(m))
             elif layer.startswith("zip12_"):             # zip12_qkv_gate:8, zip12_o:1: plain walk and 12-bit walk
                 rows = zip12_table(h, args.steps, args.warmup, only=(layer[6:], int(m)))
             else:
