@@ -761,6 +761,18 @@ def run_ours(args) -> None:
         ms_per_step = h.time_graph(step, args.steps, args.warmup)
         e2e = run_e2e(h, states, max(3, min(args.steps, 50)), args.warmup)
         nop_us = h.timer.nop_us()
+        # The same step with every launch an ordinary one, reported beside `value`: how much of it is the overlap of
+        # a call's launch and ramp with the previous call's tail (on every rank alike: the exchange kernels too).
+        ordinary_us = None
+        if not args.no_programmatic_launch:
+            from llm_inference_engine_b200 import _capi
+
+            lib = _capi.load()
+            lib.muse_set_programmatic_launch(0)
+            try:
+                ordinary_us = 1e3 * h.time_graph(step, max(3, min(args.steps, 20)), args.warmup) / len(WORKLOAD_TOKENS)
+            finally:
+                lib.muse_set_programmatic_launch(1)
     for s in states:
         h.proj.check_status(s)
     del states, keep
@@ -837,6 +849,7 @@ def run_ours(args) -> None:
                    "timing": "CUDA events around K graph replays on the replaying stream, max over ranks"},
         "gpu_launches": args.steps * len(WORKLOAD_TOKENS),
         "nop_graph_replay_us": nop_us,
+        "value_ordinary_launches": ordinary_us,
         "e2e": e2e,
         "roofline": roofline,
         "clocks": sampler.summary(),
