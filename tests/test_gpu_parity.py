@@ -408,8 +408,10 @@ def test_host_buffer_entry_point_matches_device_path(proj, dev, target_setup):
 def test_an_activation_buffer_that_is_rewritten_between_calls(proj, dev, target_setup):
     """A decode loop hands every call the same x buffer with new contents, written by a kernel just ahead in the
     stream. The projections may become resident under that kernel's tail (programmatic dependent launch), so they
-    must read x through L2-coherent loads after their grid-dependency wait: 24 rounds per plan, each against the
-    same call on a fresh copy of x, bit for bit; the non-coherent path would serve lines an SM cached rounds ago."""
+    read x through L2-coherent loads after their grid-dependency wait: 24 rounds per plan behind a torch copy kernel
+    and 24 behind the library's fetch kernel, each against the same call on a fresh copy of x, bit for bit. (The
+    case that showed stale activations with non-coherent loads is the column-parallel host round trip at 32 tokens
+    in tests/tp_worker.py; this is the one-GPU form of the same contract.)"""
     _, state = target_setup
     g = torch.Generator(device=dev).manual_seed(4242)
     for layer, m, n, k in (("qkv_gate", 8, 12288, 4096), ("o", 16, 4096, 4096), ("o", 1, 4096, 4096), ("router", 8, 256, 4096),
@@ -423,6 +425,17 @@ def test_an_activation_buffer_that_is_rewritten_between_calls(proj, dev, target_
             x.copy_(src[r % 4])                                     # a kernel rewrites the buffer ...
             got = proj.kernel_fn({"x": x, "config": cfg}, state)    # ... and the projection is launched right behind it
             assert torch.equal(got, want[r % 4]), (layer, m, r)
+        # The same with the library's own fetch kernel as the writer: it lets its dependents start at once, so the
+        # projection is resident, weights in flight, while x is still being written.
+        from llm_inference_engine_b200 import _capi
+
+        lib = _capi.load()
+        pinned = [t.cpu().pin_memory() for t in src]
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        for r in range(24):
+            _capi.check(lib.muse_fetch_host(x.data_ptr(), pinned[r % 4].data_ptr(), m * k * 2, stream), "muse_fetch_host")
+            got = proj.kernel_fn({"x": x, "config": cfg}, state)
+            assert torch.equal(got, want[r % 4]), (layer, m, r, "behind the fetch kernel")
     proj.check_status(state)
 
 
