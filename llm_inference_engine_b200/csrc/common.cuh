@@ -201,8 +201,9 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
 // griddep_launch_dependents() that the next one may be brought in; without it that happens when the kernel ends.
 // Both are no-ops for a kernel launched the ordinary way. One more rule follows from the overlap: anything another
 // kernel writes (activations, residual streams) is read with L2-coherent loads (__ldcg, TMA, bulk copies), never
-// through the non-coherent path (__ldg / ld.global.nc), whose L1 lines are only dropped at ordinary kernel
-// boundaries: a kernel that became resident under its predecessor could otherwise see what an SM cached calls ago.
+// through the non-coherent path (__ldg / ld.global.nc): that path is for data that is read-only for the kernel's
+// whole lifetime, which here begins before the predecessor's ends, so such a load may be scheduled above the wait
+// or served from an L1 line cached calls ago.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
